@@ -1,0 +1,133 @@
+/*
+ * llamatov_b200.h -- C ABI of libllamatov_b200.so: the sm_100a kernels of the Q8_0
+ * transformer decode path, as host launchers.
+ *
+ * Conventions
+ *   - every pointer argument is a DEVICE pointer unless its name starts with `h_`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - launchers only enqueue work: no allocation, no synchronisation, no host<->device
+ *     copy, so every one of them may be recorded into a CUDA graph;
+ *   - return value 0 = LT_OK; otherwise an LT_ERR_* code, with text in lt_last_error();
+ *   - Q8_0 data is the split layout of the reference's resident engine: quants
+ *     int8[rows*K] row-major and scales fp16[rows*K/32] (bit patterns, uint16_t);
+ *   - K is always a multiple of 32; Wq and Xq must be 16-byte aligned.
+ *
+ * Each entry point names the reference interface it replaces (path inside the
+ * reference project : line).  The reference launches these as C-linkage kernels
+ * through cuLaunchKernel; here the grid/block/shared-memory choice is inside the launcher.
+ */
+#ifndef LLAMATOV_B200_H
+#define LLAMATOV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LT_OK 0
+#define LT_ERR_INVALID 1     /* bad argument (shape, alignment, null pointer) */
+#define LT_ERR_CUDA 2        /* a CUDA runtime call or launch failed */
+#define LT_ERR_UNSUPPORTED 3 /* valid request this build does not implement */
+
+/* bits of the device status word (lt_device_status) */
+#define LT_STATUS_KV_OVERFLOW 1u  /* append beyond max_seq was skipped */
+#define LT_STATUS_BAD_LENGTH 2u   /* attention saw len < 0 or len > maxt; clamped */
+#define LT_STATUS_BAD_TOKEN 4u    /* embedding gather saw a token id outside [0, V) */
+#define LT_STATUS_WAIT_TIMEOUT 8u /* a bounded on-device wait gave up */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* lt_last_error(void);
+
+/* Library version string. */
+const char* lt_version(void);
+
+/* Kernel launches this library has enqueued so far in this process (captured launches count
+ * once, at capture). */
+unsigned long long lt_launch_count(void);
+
+/* Reads the device status word of the current device into *h_status and clears it.
+ * Synchronises `stream`.  Not capturable. */
+int lt_device_status(unsigned int* h_status, void* stream);
+
+/* ---- activation quantiser --------------------------------------------------------
+ * replaces k_quant_q8 (bpd/lib/dev_residency.py:867-904, _launch_quant).
+ * X f32[rows*K] -> Xq int8[rows*K], Xd fp16[rows*K/32]; one warp per 32-block:
+ * d = fp16(amax/127) (1.0 when amax == 0), q = clamp(rint(v / f32(d)), +-127). */
+int lt_quant_q8(const float* X, int8_t* Xq, uint16_t* Xd, int K, int rows, void* stream);
+
+/* replaces k_silu_mul_quant (bpd/lib/dev_residency.py:573-605, _launch_silu_quant):
+ * v = (g / (1 + expf(-g))) * u, then the quantiser above. */
+int lt_silu_mul_quant(const float* g, const float* u, int8_t* Xq, uint16_t* Xd, int K, int rows,
+                      void* stream);
+
+/* replaces k_silu_mul and k_add (bpd/lib/dev_residency.py:545-566), the unfused forms. */
+int lt_silu_mul(const float* g, const float* u, float* y, int n, void* stream);
+int lt_add(const float* a, const float* b, float* y, int n, void* stream);
+
+/* ---- Q8_0 GEMV / skinny GEMM --------------------------------------------------------
+ * replaces k_q8_0_gemv, mode tiled_v4 (bpd/kernelgen/emitters/q8_0_from_facts.pl:212-253;
+ * launched from bpd/lib/dev_residency.py:953-975,1152-1162) and k_q8_0_gemv_addres
+ * (q8_0_from_facts.pl:374-416; dev_residency.py:1021-1032).
+ * Y[t*M + n] = tree32( lane L: fold over blocks b = L, L+32, ... of
+ *                      fma(f32(Wd[n,b]) * f32(Xd[t,b]), (float)isum(n,b,t), acc) ) (+ Resid[n])
+ * which is the declared reduction_order(q8_gemv_dp4a, lanes(32), strided, accum(fma),
+ * tree(shfl_down,5)) (q8_0_from_facts.pl:476).  T activation columns are reduced
+ * independently (T = 1 is the decode GEMV).  Resid may be NULL; when given it has M
+ * entries and is added to every column (bias or residual stream).  Y must not alias Resid
+ * unless T == 1. */
+int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+               const float* Resid, float* Y, int M, int K, int T, void* stream);
+
+/* ---- RMSNorm --------------------------------------------------------------------------
+ * replaces k_rmsnorm, mode block_row (bpd/kernelgen/emitters/norm_softmax_from_facts.pl:83-108;
+ * launched from bpd/lib/dev_residency.py:757-781): 256 strided lanes fold fma(x,x,.), 8-level
+ * pairwise tree, inv = rsqrtf(ss/N + eps), y = (x*inv)*w.  M rows of N. */
+int lt_rmsnorm(const float* x, const float* w, float* y, int M, int N, float eps, void* stream);
+
+/* ---- RoPE ------------------------------------------------------------------------------
+ * replaces k_rope (bpd/kernelgen/emitters/rope_from_facts.pl:40-69; launched from
+ * bpd/lib/dev_residency.py:701-742).  NeoX half-split rotation in place of X[nrows, n_head*hd]
+ * at the positions pos[nrows] (device ints). */
+int lt_rope(float* X, const int* pos, int nrows, int n_head, int hd, float theta, void* stream);
+
+/* ---- KV cache append ----------------------------------------------------------------
+ * replaces k_append_kv_incr / k_append_kv / k_incr_len (bpd/lib/dev_residency.py:281-316,
+ * 464-521).  Writes ksrc/vsrc[width] at row *len of the position-major caches, then (when
+ * incr != 0) *len += 1.  A row index >= max_seq is skipped and flagged. */
+int lt_append_kv(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int* len,
+                 int width, int max_seq, int incr, void* stream);
+int lt_incr_len(int* len, void* stream);
+
+/* ---- decode attention ------------------------------------------------------------------
+ * replaces k_attn_decode_masked (bpd/lib/dev_residency.py:1955-2031): one query token, GQA,
+ * fp32 position-major cache [t][kvhead][d], valid length read from *len, positions >= len
+ * masked; frozen reduction orders (64-lane max and sum, left-fold V sum).  maxt is the
+ * capacity the reference compiles in as MAXT. */
+int lt_attn_decode_masked(const float* Q, const float* K, const float* V, const int* len,
+                          float* OUT, int hd, int nh, int nkv, float scale, int maxt,
+                          void* stream);
+
+/* ---- argmax ----------------------------------------------------------------------------
+ * replaces k_argmax_s1 + k_argmax_s2 (bpd/lib/dev_residency.py:225-272,1074-1110): index of
+ * the maximum, lowest index on ties.  `partials` is caller scratch of lt_argmax_scratch_bytes()
+ * bytes. */
+int lt_argmax(const float* x, int n, void* partials, int* out_idx, void* stream);
+int lt_argmax_scratch_bytes(void);
+
+/* ---- embedding gather ------------------------------------------------------------------
+ * replaces the host lookup of the dequantised table row (bpd/lib/dev_residency.py:1357-1358,
+ * 1761-1764): out[i] = f32(Wd[tok, i/32]) * Wq[tok, i], token id read from device memory. */
+int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out, int E, int V,
+                void* stream);
+
+/* ---- on-device token loop ---------------------------------------------------------------
+ * no reference counterpart as a kernel: the reference copies the chosen token to the host
+ * after every step (bpd/lib/dev_residency.py:1812-1818).  history[*step] = *tok; *step += 1;
+ * lets a captured step feed its own argmax to the next replay and keeps the token trace. */
+int lt_token_record(const int* tok, int* history, int* step, int capacity, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMATOV_B200_H */

@@ -1,0 +1,85 @@
+"""ctypes binding of libllamatov_b200.so (the C ABI declared in include/llamatov_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails, a RuntimeError
+is raised with the library's own error text.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libllamatov_b200.so")
+_lib = None
+
+LT_OK = 0
+STATUS_BITS = {1: "kv_overflow", 2: "bad_length", 4: "bad_token", 8: "wait_timeout"}
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+# name -> argtypes (all return int unless listed in _RESTYPES)
+SIGNATURES = {
+    "lt_device_status": [ctypes.POINTER(ctypes.c_uint), _vp],
+    "lt_quant_q8": [_vp, _vp, _vp, _i, _i, _vp],
+    "lt_silu_mul_quant": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+    "lt_silu_mul": [_vp, _vp, _vp, _i, _vp],
+    "lt_add": [_vp, _vp, _vp, _i, _vp],
+    "lt_q8_gemv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "lt_rmsnorm": [_vp, _vp, _vp, _i, _i, _f, _vp],
+    "lt_rope": [_vp, _vp, _i, _i, _i, _f, _vp],
+    "lt_append_kv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "lt_incr_len": [_vp, _vp],
+    "lt_attn_decode_masked": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "lt_argmax": [_vp, _i, _vp, _vp, _vp],
+    "lt_argmax_scratch_bytes": [],
+    "lt_embed_q8": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+    "lt_token_record": [_vp, _vp, _vp, _i, _vp],
+}
+_RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
+             "lt_launch_count": ctypes.c_ulonglong}
+
+
+def lib():
+    """The loaded library (loads on first use)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libllamatov_b200.so is not built (%s). Run `python -m llamatov_b200.build`; "
+                "this package has no CPU or PyTorch fallback." % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = ctypes.c_int
+        for name, rt in _RESTYPES.items():
+            fn = getattr(L, name)
+            fn.argtypes = []
+            fn.restype = rt
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return lib().lt_last_error().decode("utf-8", "replace")
+
+
+def check(rc, what=""):
+    """Raise RuntimeError if a launcher returned a non-zero code."""
+    if rc != LT_OK:
+        raise RuntimeError("llamatov_b200 %s failed (code %d): %s" % (what, rc, last_error()))
+
+
+def call(name, *args):
+    check(getattr(lib(), name)(*args), name)
+
+
+def launch_count():
+    return int(lib().lt_launch_count())
+
+
+def device_status(stream=None):
+    """Read and clear the device status word; returns the set of flag names."""
+    v = ctypes.c_uint(0)
+    check(lib().lt_device_status(ctypes.byref(v), stream), "lt_device_status")
+    return {n for bit, n in STATUS_BITS.items() if v.value & bit}

@@ -1,0 +1,209 @@
+// Q8_0 GEMV / skinny GEMM, HBM-bound: the weight matrix is streamed once, the (small)
+// quantised activation sits in shared memory.
+//
+// Arithmetic contract, per output row n and activation column t:
+//   lane L in 0..31:  acc_L = 0;  for b = L, L+32, ... < K/32 (ascending):
+//       isum = sum_i Wq[n, 32b+i] * Xq[t, 32b+i]            (exact int32, dp4a)
+//       acc_L = fma( f32(Wd[n,b]) * f32(Xd[t,b]), (float)isum, acc_L )
+//   Y[t, n] = tree over lanes, s = 16, 8, 4, 2, 1: acc_l += acc_{l+s}   (+ Resid[n])
+// Only the fp32 order is frozen; loads and integer work are scheduled freely.
+//
+// Mapping: one warp owns R consecutive rows at a time and keeps the loads of all R rows
+// in flight together (R * (2 x 128-bit + 1 x 16-bit) per lane), lane = block index mod 32,
+// exactly the lane of the contract, so the per-lane fold and the shuffle tree need no
+// re-association.  Warps walk the matrix with a grid stride sized to the SM count.
+#include "lt_common.cuh"
+
+namespace lt {
+
+constexpr int GEMV_WARPS = 8;      // warps per CTA
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+
+template <int R, int TB>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_q8_gemv(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const int8_t* __restrict__ Xq,
+          const __half* __restrict__ Xd, const float* __restrict__ Resid, float* __restrict__ Y, int M, int K,
+          int T) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nb = K >> 5;
+    // shared: TB columns of (K int8 + nb fp16), each column padded to 16 bytes
+    const int col_stride = ((K + nb * 2 + 15) >> 4) << 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long warps_total = (long)gridDim.x * GEMV_WARPS;
+    const long gwarp = (long)blockIdx.x * GEMV_WARPS + warp;
+
+    {   // T <= TB: one pass over the matrix serves every column
+        const int t0 = 0;
+        const int tcount = T;
+        for (int c = 0; c < tcount; c++) {
+            const int4* src = (const int4*)(Xq + (long)(t0 + c) * K);
+            int4* dst = (int4*)(smem + c * col_stride);
+            for (int i = threadIdx.x; i < (K >> 4); i += GEMV_THREADS) dst[i] = src[i];
+            __half* dsth = (__half*)(smem + c * col_stride + K);
+            const __half* srch = Xd + (long)(t0 + c) * nb;
+            for (int i = threadIdx.x; i < nb; i += GEMV_THREADS) dsth[i] = srch[i];
+        }
+        __syncthreads();
+
+        for (long r0 = gwarp * R; r0 < M; r0 += warps_total * R) {
+            float acc[R][TB];
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int c = 0; c < TB; c++) acc[r][c] = 0.0f;
+
+            for (int b = lane; b < nb; b += 32) {
+                int4 w0[R], w1[R];
+                float wd[R];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    long row = r0 + r;
+                    if (row < M) {
+                        const int8_t* p = Wq + row * K + (long)b * 32;
+                        w0[r] = ld_stream_v4(p);
+                        w1[r] = ld_stream_v4(p + 16);
+                        wd[r] = __half2float(__ushort_as_half(ld_stream_u16(Wd + row * nb + b)));
+                    } else {
+                        w0[r] = make_int4(0, 0, 0, 0);
+                        w1[r] = make_int4(0, 0, 0, 0);
+                        wd[r] = 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < TB; c++) {
+                    if (c < tcount) {
+                        const int4* xp = (const int4*)(smem + c * col_stride + b * 32);
+                        int4 x0 = xp[0], x1 = xp[1];
+                        float xd = __half2float(((const __half*)(smem + c * col_stride + K))[b]);
+#pragma unroll
+                        for (int r = 0; r < R; r++)
+                            acc[r][c] = q8_accum(wd[r], xd, block_dot(w0[r], w1[r], x0, x1), acc[r][c]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+#pragma unroll
+                for (int c = 0; c < TB; c++) {
+                    float v = warp_tree_sum(acc[r][c]);
+                    long row = r0 + r;
+                    if (lane == 0 && row < M && c < tcount) {
+                        if (Resid != nullptr) v = __fadd_rn(v, Resid[row]);
+                        Y[(long)(t0 + c) * M + row] = v;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Wide skinny GEMM (8 < T <= TW): one warp per row, the row's blocks stay in registers while
+// all T columns are folded, so the matrix is still read exactly once.  The activation
+// columns come from global memory through L1/L2 (T*K bytes, cache resident).  Same lane /
+// fold / tree order per (row, column) as the GEMV.  At these widths the integer dot
+// products, not HBM, set the pace.
+template <int TW>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_q8_gemm_wide(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const int8_t* __restrict__ Xq,
+               const __half* __restrict__ Xd, const float* __restrict__ Resid, float* __restrict__ Y, int M, int K,
+               int T) {
+    const int nb = K >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long warps_total = (long)gridDim.x * GEMV_WARPS;
+    for (long row = (long)blockIdx.x * GEMV_WARPS + warp; row < M; row += warps_total) {
+        float acc[TW];
+#pragma unroll
+        for (int c = 0; c < TW; c++) acc[c] = 0.0f;
+        for (int b = lane; b < nb; b += 32) {
+            const int8_t* p = Wq + row * K + (long)b * 32;
+            int4 w0 = ld_stream_v4(p), w1 = ld_stream_v4(p + 16);
+            float wd = __half2float(__ushort_as_half(ld_stream_u16(Wd + row * nb + b)));
+#pragma unroll
+            for (int c = 0; c < TW; c++) {
+                if (c < T) {
+                    const int4* xp = (const int4*)(Xq + (long)c * K + (long)b * 32);
+                    int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                    float xd = __half2float(__ldg(Xd + (long)c * nb + b));
+                    acc[c] = q8_accum(wd, xd, block_dot(w0, w1, x0, x1), acc[c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < TW; c++) {
+            float v = warp_tree_sum(acc[c]);
+            if (lane == 0 && c < T) {
+                if (Resid != nullptr) v = __fadd_rn(v, Resid[row]);
+                Y[(long)c * M + row] = v;
+            }
+        }
+    }
+}
+
+static int gemv_grid(long row_groups) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long ctas = (row_groups + GEMV_WARPS - 1) / GEMV_WARPS;
+    long cap = (long)sms * 8;  // up to 8 resident CTAs of 256 threads per SM
+    return (int)(ctas > cap ? cap : ctas);
+}
+
+template <int TW>
+static int launch_gemm_wide(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                            const float* Resid, float* Y, int M, int K, int T, cudaStream_t s) {
+    k_q8_gemm_wide<TW><<<gemv_grid(M), GEMV_THREADS, 0, s>>>(Wq, (const __half*)Wd, Xq, (const __half*)Xd, Resid, Y,
+                                                            M, K, T);
+    return check_launch("lt_q8_gemv(wide)");
+}
+
+template <int R, int TB>
+static int launch_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                       const float* Resid, float* Y, int M, int K, int T, cudaStream_t s) {
+    const int nb = K / 32;
+    const int col_stride = ((K + nb * 2 + 15) / 16) * 16;
+    const size_t smem = (size_t)col_stride * TB;
+    static bool attr_done = false;
+    if (smem > 48 * 1024 && !attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv<R, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
+    int ctas = gemv_grid(((long)M + R - 1) / R);
+    k_q8_gemv<R, TB><<<(unsigned)ctas, GEMV_THREADS, smem, s>>>(Wq, (const __half*)Wd, Xq, (const __half*)Xd, Resid,
+                                                             Y, M, K, T);
+    return check_launch("lt_q8_gemv");
+}
+
+}  // namespace lt
+
+using namespace lt;
+
+extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                          const float* Resid, float* Y, int M, int K, int T, void* stream) {
+    LT_REQUIRE(Wq && Wd && Xq && Xd && Y, "lt_q8_gemv: null pointer");
+    LT_REQUIRE(M > 0 && T > 0, "lt_q8_gemv: M=%d T=%d must be positive", M, T);
+    LT_REQUIRE(K > 0 && K % 32 == 0, "lt_q8_gemv: K=%d must be a positive multiple of 32", K);
+    LT_REQUIRE(aligned16(Wq) && aligned16(Xq), "lt_q8_gemv: Wq and Xq must be 16-byte aligned");
+    LT_REQUIRE((reinterpret_cast<uintptr_t>(Wd) & 1u) == 0 && (reinterpret_cast<uintptr_t>(Xd) & 1u) == 0,
+               "lt_q8_gemv: scale pointers must be 2-byte aligned");
+    LT_REQUIRE(T == 1 || Resid == nullptr || Y != Resid, "lt_q8_gemv: Y may alias Resid only when T == 1");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (T == 1) return launch_gemv<4, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    if (T <= 2) return launch_gemv<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    if (T <= 4) return launch_gemv<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    if (T <= 8) return launch_gemv<2, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    // wider batches: chunks of up to 64 columns, each chunk one pass over the matrix
+    const int nb = K / 32;
+    for (int t0 = 0; t0 < T; t0 += 64) {
+        int tc = T - t0 < 64 ? T - t0 : 64;
+        const int8_t* xq = Xq + (long)t0 * K;
+        const uint16_t* xd = Xd + (long)t0 * nb;
+        float* y = Y + (long)t0 * M;
+        int rc;
+        if (tc <= 16) rc = launch_gemm_wide<16>(Wq, Wd, xq, xd, Resid, y, M, K, tc, s);
+        else if (tc <= 32) rc = launch_gemm_wide<32>(Wq, Wd, xq, xd, Resid, y, M, K, tc, s);
+        else rc = launch_gemm_wide<64>(Wq, Wd, xq, xd, Resid, y, M, K, tc, s);
+        if (rc != LT_OK) return rc;
+    }
+    return LT_OK;
+}
