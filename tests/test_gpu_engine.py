@@ -51,16 +51,17 @@ def test_eager_decode_matches_oracle(oracle, arch):
     o_logits = []
     # teacher-forced on the GPU's tokens so that one near-tie cannot cascade; token identity is
     # asserted wherever the oracle's top-1 margin exceeds the drift bound
-    for i, t in enumerate(toks[len(prompt) - 1:-1] if n_new else []):
+    for t in toks[len(prompt) - 1:]:
         lg, _ = eng.step(t)
         o_logits.append(lg)
+    assert len(o_logits) == len(logits) == n_new + 1
     for i, (a, b) in enumerate(zip(logits, o_logits)):
         assert np.max(np.abs(a - b)) < LOGIT_TOL, (i, np.max(np.abs(a - b)))
         top2 = np.partition(b, -2)[-2:]
         if top2[1] - top2[0] > 2 * LOGIT_TOL:
             assert int(np.argmax(a)) == int(np.argmax(b))
     # device caches equal the oracle's rows up to the rope tolerance; lengths exact
-    L = len(toks) - 1
+    L = len(toks)
     for il, c in enumerate(kv):
         assert c.length == L == int(eng.lens[il])
         assert int(c._len.item()) == L
@@ -107,7 +108,7 @@ def test_graph_replay_equals_eager_bit_exact():
         nxt = int(np.argmax(lg))
     assert toks == e_toks
     for c, rows in zip(kv, e_rows):
-        assert int(c._len.item()) == c.length == len(toks) - 1
+        assert int(c._len.item()) == c.length == len(toks)
         assert np.array_equal(bits(c.k_slice_host()), bits(rows))
     # replay_token: device argmax == host argmax of the same logits
     t_dev = gr.replay_token(nxt)
