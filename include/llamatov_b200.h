@@ -121,6 +121,24 @@ int lt_argmax_scratch_bytes(void);
 int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out, int E, int V,
                 void* stream);
 
+/* ---- decode linear without caller scratch ----------------------------------------------
+ * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a
+ * slab it owns).  Y[M] = W . quant(X[K]) (+ Resid), the same arithmetic as lt_quant_q8
+ * followed by lt_q8_gemv with T = 1, for callers that may not allocate device memory: the
+ * quantised activation lives in a 17 KiB __device__ array inside the library, which every
+ * GPU that loads the library keeps until the process exits.
+ *   - K must not exceed lt_q8_linear_static_max_k() (16384); larger K is rejected with
+ *     LT_ERR_INVALID and a message, nothing is launched.
+ *   - The first call on each device looks the array's address up; make that call before any
+ *     stream capture begins on that device.
+ *   - The entry point calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - All calls share the one array and it keeps the last call's contents (each call
+ *     overwrites every byte it later reads).  Two calls whose kernels overlap on the GPU
+ *     (different streams, or concurrent graphs) race on it: serialise them. */
+int lt_q8_linear_static(const int8_t* Wq, const uint16_t* Wd, const float* X, const float* Resid,
+                        float* Y, int M, int K, void* stream);
+int lt_q8_linear_static_max_k(void);
+
 /* ---- on-device token loop ---------------------------------------------------------------
  * no reference counterpart as a kernel: the reference copies the chosen token to the host
  * after every step (bpd/lib/dev_residency.py:1812-1818).  history[*step] = *tok; *step += 1;

@@ -34,6 +34,8 @@ SIGNATURES = {
     "lt_argmax_scratch_bytes": [],
     "lt_embed_q8": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_token_record": [_vp, _vp, _vp, _i, _vp],
+    "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "lt_q8_linear_static_max_k": [],
 }
 _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}
