@@ -121,6 +121,65 @@ int lt_argmax_scratch_bytes(void);
 int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out, int E, int V,
                 void* stream);
 
+/* ---- one decode step as one persistent kernel ---------------------------------------------
+ * replaces the captured graph of one token forward, i.e. the whole body of
+ * forward_pass_resident for one token plus _compute_folded_logits and argmax_dev
+ * (bpd/lib/dev_residency.py:1381-1477,1596-1623,1812-1815; ~315 kernel nodes per token in the
+ * reference): per layer rmsnorm+quant -> q|k|v GEMV+bias -> rope -> KV append -> masked
+ * attention -> quant -> o_proj GEMV + residual -> rmsnorm+quant -> gate|up GEMV -> silu*up
+ * quant -> down GEMV + residual; then final rmsnorm+quant -> LM-head GEMV -> argmax.  The
+ * arithmetic of every op is the per-op entry point's, so results are bit-identical to the
+ * chain of per-op launches.  One CTA per SM, cooperative launch, weights streamed through a
+ * shared-memory ring by bulk async copies.  Capturable.
+ *
+ * All pointers are device pointers.  Each Q8_0 matrix must have a scale count (rows*K/32)
+ * that is a multiple of 8 and 16-byte aligned bases.  max_seq must be a multiple of 4. */
+typedef struct lt_decode_layer {
+    const float* attn_norm;    /* [E] */
+    const int8_t* qkv_q;       /* [(nh+2*nkv)*hd, E] rows q|k|v */
+    const uint16_t* qkv_d;
+    const float* qkv_bias;     /* [(nh+2*nkv)*hd] or NULL */
+    const int8_t* o_q;         /* [E, nh*hd] */
+    const uint16_t* o_d;
+    const float* ffn_norm;     /* [E] */
+    const int8_t* gu_q;        /* [2F, E] rows gate|up */
+    const uint16_t* gu_d;
+    const int8_t* down_q;      /* [E, F] */
+    const uint16_t* down_d;
+    float* kcache;             /* [max_seq, nkv*hd] fp32, position-major */
+    float* vcache;
+    int* len;                  /* valid positions; rope position of the new token */
+} lt_decode_layer;
+
+typedef struct lt_decode_desc {
+    int n_layers, E, nh, nkv, hd, F, V, max_seq;
+    float eps, theta, scale;   /* scale = hd^-0.5 as fp32 */
+    int hist_cap;
+    const lt_decode_layer* layers;  /* device array [n_layers] */
+    const float* out_norm;     /* [E] */
+    const int8_t* lm_q;        /* [V, E] */
+    const uint16_t* lm_d;
+    const int8_t* emb_q;       /* [V, E] embedding table (needed when tok != NULL) */
+    const uint16_t* emb_d;
+    float* x;                  /* [E] residual stream; input row when tok == NULL */
+    float* x1;                 /* [E] */
+    float* qkv;                /* [(nh+2*nkv)*hd] */
+    float* att;                /* [nh*hd] */
+    float* gu;                 /* [2F] */
+    float* logits;             /* [V] */
+    int* tok;                  /* device token: read at the start, overwritten with the argmax; NULL = x preloaded */
+    int* out_tok;              /* argmax of the logits */
+    int* history;              /* optional: history[*step] = token; *step += 1 */
+    int* step;
+    unsigned int* sync;        /* [2] grid-barrier counters, zero before the first launch */
+    float* part_val;           /* [lt_decode_num_ctas()] */
+    int* part_idx;             /* [lt_decode_num_ctas()] */
+    int* status;               /* device status word (or any int) */
+} lt_decode_desc;
+
+int lt_decode_step(const lt_decode_desc* h_desc, void* stream);
+int lt_decode_num_ctas(void);
+
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a
  * slab it owns).  Y[M] = W . quant(X[K]) (+ Resid), the same arithmetic as lt_quant_q8

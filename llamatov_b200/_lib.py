@@ -36,6 +36,8 @@ SIGNATURES = {
     "lt_token_record": [_vp, _vp, _vp, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
+    "lt_decode_step": [_vp, _vp],
+    "lt_decode_num_ctas": [],
 }
 _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}

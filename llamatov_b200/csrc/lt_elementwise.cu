@@ -3,6 +3,7 @@
 // sizes; they exist as stand-alone launches for the per-op interface and as building
 // blocks whose arithmetic the fused kernels repeat verbatim.
 #include "lt_common.cuh"
+#include "lt_device_ops.cuh"
 
 namespace lt {
 
@@ -94,15 +95,11 @@ __global__ void k_rope(float* __restrict__ X, const int* __restrict__ pos, int n
     long hr = gid / half;
     int head = hr % n_head;
     int row = hr / n_head;
-    float p = (float)pos[row];
-    float freq = powf(theta, -(2.0f * (float)j) / (float)hd);
-    float ang = p * freq;
-    float c = cosf(ang), s = sinf(ang);
     long base = (long)row * n_head * hd + (long)head * hd;
-    float x1 = X[base + j];
-    float x2 = X[base + j + half];
-    X[base + j] = x1 * c - x2 * s;
-    X[base + j + half] = x1 * s + x2 * c;
+    float o1, o2;
+    rope_pair(X[base + j], X[base + j + half], j, hd, theta, pos[row], o1, o2);
+    X[base + j] = o1;
+    X[base + j + half] = o2;
 }
 
 // ------------------------------------------------------------------ KV append

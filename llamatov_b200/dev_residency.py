@@ -693,6 +693,87 @@ def _compute_folded_logits(w, cfg, E):
     return lbuf
 
 
+# --------------------------------------------------------------------------- fused decode step
+# When True, GraphRunner records the whole token step as ONE persistent kernel
+# (lt_decode_step) instead of ~320 per-op kernel nodes.  Same arithmetic, bit-identical
+# results; the eager forward_pass_resident keeps the per-op launches and is the parity baseline.
+_FUSED_STEP = True
+
+
+class _DecLayer(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in (
+        "attn_norm", "qkv_q", "qkv_d", "qkv_bias", "o_q", "o_d", "ffn_norm", "gu_q", "gu_d",
+        "down_q", "down_d", "kcache", "vcache", "len")]
+
+
+class _DecDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("n_layers", "E", "nh", "nkv", "hd", "F", "V", "max_seq")] + \
+               [(n, ctypes.c_float) for n in ("eps", "theta", "scale")] + [("hist_cap", ctypes.c_int)] + \
+               [(n, ctypes.c_void_p) for n in (
+                   "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "x1", "qkv", "att", "gu",
+                   "logits", "tok", "out_tok", "history", "step", "sync", "part_val", "part_idx", "status")]
+
+
+class FusedDecodeStep:
+    """Descriptor + workspace of lt_decode_step for one model and its KV caches.  Every weight
+    pointer comes from the same upload caches the per-op path uses (no second copy)."""
+
+    def __init__(self, w, cfg, kv, tok_ptr=None, history=None, step=None, hist_cap=0):
+        nh, nkv, E = cfg["n_head"], cfg["n_head_kv"], cfg["n_embd"]
+        hd = E // nh
+        L = cfg["n_layers"]
+        self._keep = []
+        layers = (_DecLayer * L)()
+        F = None
+        for il in range(L):
+            p = f"blk.{il}"
+            Wqkv, bcat, _ = _fused_qkv_weight(w, p)
+            Wgu, _, (ng, _nu) = _fused_gateup_weight(w, p)
+            F = ng
+            qq, qd, _, _ = _weights(Wqkv)
+            oq, od, _, _ = _weights(w[f"{p}.attn_output.weight"])
+            gq, gd, _, _ = _weights(Wgu)
+            dq, dd, _, _ = _weights(w[f"{p}.ffn_down.weight"])
+            c = kv[il]
+            if c is None:
+                raise RuntimeError("FusedDecodeStep: KV caches must exist (run seed() first)")
+            c._ensure_len_ptr(seed=False)
+            layers[il] = _DecLayer(_addr(_dev_const(_np(w[f"{p}.attn_norm.weight"]))), _addr(qq), _addr(qd),
+                                   _addr(_dev_const(bcat)) if bcat is not None else None, _addr(oq), _addr(od),
+                                   _addr(_dev_const(_np(w[f"{p}.ffn_norm.weight"]))), _addr(gq), _addr(gd),
+                                   _addr(dq), _addr(dd), _addr(c.k_ptr), _addr(c.v_ptr), _addr(c.len_ptr))
+        raw = np.frombuffer(bytes(layers), dtype=np.uint8).copy()
+        self._layers_dev = torch.from_numpy(raw).cuda()
+        lq, ld, V, _ = _weights(_lm_head(w))
+        eq, ed = None, None
+        if tok_ptr is not None:
+            eq, ed, _, _ = _weights(_np(w["token_embd.weight"]))
+        nq, nk = nh * hd, nkv * hd
+        nct = _lib.lib().lt_decode_num_ctas()
+        f32 = dict(dtype=torch.float32, device="cuda")
+        self.x1 = torch.zeros(E, **f32); self.qkv = torch.zeros(nq + 2 * nk, **f32)
+        self.att = torch.zeros(nq, **f32); self.gu = torch.zeros(2 * F, **f32)
+        self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+        self.part_val = torch.zeros(nct, **f32); self.part_idx = torch.zeros(nct, dtype=torch.int32, device="cuda")
+        resid_in, _ = _ensure_resid(E)
+        lbuf = _ensure_logits_buf(E, w)
+        out_tok = _ensure_argmax_buf()
+        max_seq = kv[0].max_seq
+        self.desc = _DecDesc(L, E, nh, nkv, hd, F, V, max_seq, float(cfg["norm_eps"]), float(cfg["rope_theta"]),
+                             float(np.float32(hd ** -0.5)), int(hist_cap),
+                             self._layers_dev.data_ptr(), _addr(_dev_const(_np(w["output_norm.weight"]))),
+                             _addr(lq), _addr(ld), None if eq is None else _addr(eq), None if ed is None else _addr(ed),
+                             _addr(resid_in.ptr), self.x1.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(),
+                             self.gu.data_ptr(), _addr(lbuf.ptr), None if tok_ptr is None else int(tok_ptr),
+                             _addr(out_tok), None if history is None else int(history),
+                             None if step is None else int(step), self.sync.data_ptr(), self.part_val.data_ptr(),
+                             self.part_idx.data_ptr(), None)
+
+    def launch(self):
+        rc = _lib.lib().lt_decode_step(ctypes.byref(self.desc), _stream())
+        _lib.check(rc, "lt_decode_step")
+
+
 class GraphRunner:
     """Captures one decode step into a CUDA graph and replays it per token
     (bpd/lib/dev_residency.py:1626-1818): seed() runs the prompt eagerly and settles every
@@ -744,8 +825,14 @@ class GraphRunner:
         g = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         n0 = _lib.launch_count()
-        with torch.cuda.graph(g, stream=self.stream):
-            forward_pass_resident(self.w, self.cfg, tok, pos, self.kv)
+        self.fused = bool(_FUSED_STEP)
+        if self.fused:
+            self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv)
+            with torch.cuda.graph(g, stream=self.stream):
+                self._step_host.launch()
+        else:
+            with torch.cuda.graph(g, stream=self.stream):
+                forward_pass_resident(self.w, self.cfg, tok, pos, self.kv)
         self.launches_per_token = _lib.launch_count() - n0
         for c, n in zip(self.kv, lens):
             c.length = n
@@ -791,15 +878,22 @@ class GraphRunner:
         g = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         n0 = _lib.launch_count()
-        _DEVICE_EMBED = (dWq, dWd, ctypes.c_void_p(self._tok_dev.data_ptr()), V)
-        try:
+        if _FUSED_STEP:
+            self._step_dev = FusedDecodeStep(self.w, self.cfg, self.kv, tok_ptr=self._tok_dev.data_ptr(),
+                                             history=self._hist.data_ptr(), step=self._step.data_ptr(),
+                                             hist_cap=capacity)
             with torch.cuda.graph(g, stream=self.stream):
-                forward_pass_resident(self.w, self.cfg, torch.tensor([0]), torch.tensor([0]), self.kv)
-                argmax_dev(_LOGITS_BUF.ptr, _LOGITS_BUF.n, self._tok_dev.data_ptr())
-                _lib.call("lt_token_record", self._tok_dev.data_ptr(), self._hist.data_ptr(),
-                          self._step.data_ptr(), capacity, _stream())
-        finally:
-            _DEVICE_EMBED = None
+                self._step_dev.launch()
+        else:
+            _DEVICE_EMBED = (dWq, dWd, ctypes.c_void_p(self._tok_dev.data_ptr()), V)
+            try:
+                with torch.cuda.graph(g, stream=self.stream):
+                    forward_pass_resident(self.w, self.cfg, torch.tensor([0]), torch.tensor([0]), self.kv)
+                    argmax_dev(_LOGITS_BUF.ptr, _LOGITS_BUF.n, self._tok_dev.data_ptr())
+                    _lib.call("lt_token_record", self._tok_dev.data_ptr(), self._hist.data_ptr(),
+                              self._step.data_ptr(), capacity, _stream())
+            finally:
+                _DEVICE_EMBED = None
         self.launches_per_step = _lib.launch_count() - n0
         for c, n in zip(self.kv, lens):
             c.length = n
@@ -829,8 +923,10 @@ class GraphRunner:
         """Replay, device argmax, 4 bytes back to the host."""
         assert _LOGITS_BUF is not None, "replay_token requires device logits"
         self._launch(tok)
-        with torch.cuda.stream(self.stream):
-            ab = argmax_dev(_LOGITS_BUF.ptr, _LOGITS_BUF.n, _ensure_argmax_buf())
+        ab = _ensure_argmax_buf()
+        if not self.fused:          # the fused step already left the argmax in the buffer
+            with torch.cuda.stream(self.stream):
+                argmax_dev(_LOGITS_BUF.ptr, _LOGITS_BUF.n, ab)
         self.stream.synchronize()
         idx = np.empty(1, np.int32)
         _memcpy_dtoh(idx, ab, 4)

@@ -83,9 +83,20 @@ def test_fp32_weight_boundary_equals_q8_boundary():
         assert np.array_equal(bits(x), bits(y))
 
 
-def test_graph_replay_equals_eager_bit_exact():
-    # the reference's graph referee contract (bpd/kernelgen/referee/gr_referee.py:11-18,184-215)
-    m, w, cfg = _fresh("tiny", seed=3)
+@pytest.fixture(params=[True, False], ids=["fused-step", "per-op-graph"])
+def fused(request):
+    old = dr._FUSED_STEP
+    dr._FUSED_STEP = request.param
+    yield request.param
+    dr._FUSED_STEP = old
+
+
+@pytest.mark.parametrize("arch", ["tiny", "tiny-llama"])
+def test_graph_replay_equals_eager_bit_exact(fused, arch):
+    # the reference's graph referee contract (bpd/kernelgen/referee/gr_referee.py:11-18,184-215);
+    # with the fused step this is also the bit-exactness test of the persistent decode kernel
+    # against the chain of per-op kernels
+    m, w, cfg = _fresh(arch, seed=3)
     V = m["cfg"]["vocab"]
     prompt = _prompt(V, 6, seed=1)
     n_new = 10
@@ -113,6 +124,60 @@ def test_graph_replay_equals_eager_bit_exact():
     # replay_token: device argmax == host argmax of the same logits
     t_dev = gr.replay_token(nxt)
     assert t_dev == int(np.argmax(dr._LOGITS_BUF.to_host()))
+    assert gr.launches_per_token == (1 if fused else gr.launches_per_token)
+    assert dr._lib.device_status() == set()
+
+
+@pytest.mark.parametrize("arch", ["tiny", "tiny-llama"])
+def test_device_token_loop_equals_host_driven_loop(fused, arch):
+    m, w, cfg = _fresh(arch, seed=6)
+    prompt = _prompt(m["cfg"]["vocab"], 5, seed=2)
+    n_new = 14
+    kv = [None] * cfg["n_layers"]
+    gr = dr.GraphRunner(w, cfg, kv)
+    lg = gr.seed(torch.tensor(prompt), torch.arange(len(prompt)))
+    first = int(np.argmax(lg.reshape(-1).numpy()))
+    gr.capture(torch.tensor([first]), torch.tensor([len(prompt)]))
+    tok, host_toks = first, []
+    for _ in range(n_new):
+        tok = gr.replay_token(tok)
+        host_toks.append(tok)
+    rows = [c.k_slice_host().copy() for c in kv]
+    # rewind the caches to the end of the prompt and run the same steps with no host in the loop
+    for c in kv:
+        c.length = len(prompt); c._len.fill_(len(prompt))
+    gr.capture_device_loop(first, capacity=8)      # history shorter than the run: must not overflow
+    gr.replay_device(n_new)
+    got = gr.device_tokens()
+    assert got == host_toks[:8]
+    assert int(gr._tok_dev.item()) == host_toks[-1]
+    for c, r in zip(kv, rows):
+        assert int(c._len.item()) == c.length == len(prompt) + n_new
+        assert np.array_equal(bits(c.k_slice_host()), bits(r))
+    assert dr._lib.device_status() == set()
+
+
+def test_fused_step_kv_overflow_is_flagged_not_faulted():
+    m, w, cfg = _fresh("tiny", seed=7)
+    dr._KV_MAX_SEQ = 8
+    old = dr._FUSED_STEP
+    dr._FUSED_STEP = True
+    try:
+        kv = [None] * cfg["n_layers"]
+        gr = dr.GraphRunner(w, cfg, kv)
+        gr.seed(torch.tensor([1, 2, 3]), torch.arange(3))
+        gr.capture(torch.tensor([4]), torch.tensor([3]))
+        t = 4
+        for _ in range(5):
+            t = gr.replay_token(t)
+        assert dr._lib.device_status() == set()
+        assert int(kv[0]._len.item()) == 8
+        gr.replay_token(t)                           # ninth position: refused, flagged
+        assert "kv_overflow" in dr._lib.device_status()
+        assert int(kv[0]._len.item()) == 8
+    finally:
+        dr._FUSED_STEP = old
+        dr.apply_production_profile()
 
 
 def test_capture_preconditions_are_loud():
@@ -138,3 +203,39 @@ def test_kv_overflow_is_flagged():
         assert "kv_overflow" in dr._lib.device_status()
     finally:
         dr.apply_production_profile()
+
+
+def test_qwen05b_greedy_128_tokens_vs_oracle(oracle):
+    """Full-size configuration: Qwen2.5-0.5B architecture, 32-token prompt, 128 greedy tokens
+    with the token loop on the device, against the CPU oracle engine.  The oracle is
+    teacher-forced on the GPU's tokens; tokens must agree wherever the oracle's top-1 margin
+    exceeds twice the logit tolerance, and the number of such decisive steps is reported."""
+    m, w, cfg = _fresh("qwen2.5-0.5b", seed=0)
+    V = m["cfg"]["vocab"]
+    prompt = _prompt(V, 32)
+    n_new = 128
+    kv = [None] * cfg["n_layers"]
+    gr = dr.GraphRunner(w, cfg, kv)
+    lg = gr.seed(torch.tensor(prompt), torch.arange(32)).reshape(-1).numpy()
+    first = int(np.argmax(lg))
+    gr.capture_device_loop(first, capacity=256)
+    gr.replay_device(n_new)
+    toks = gr.device_tokens()
+    assert len(toks) == n_new and dr._lib.device_status() == set()
+    last_logits = dr._LOGITS_BUF.to_host().reshape(-1)
+    eng = oracle.OracleEngine(synth.oracle_model(m), max_seq=dr._KV_MAX_SEQ)
+    for t in prompt:
+        ol, _ = eng.step(t)
+    assert np.max(np.abs(ol - lg)) < LOGIT_TOL
+    decisive = agree = 0
+    seq = [first] + toks
+    for i in range(n_new):
+        ol, onext = eng.step(seq[i])
+        top2 = np.partition(ol, -2)[-2:]
+        if top2[1] - top2[0] > 2 * LOGIT_TOL:
+            decisive += 1
+            assert onext == seq[i + 1], (i, onext, seq[i + 1])
+        agree += int(onext == seq[i + 1])
+    assert np.max(np.abs(ol - last_logits)) < LOGIT_TOL
+    print(f"qwen2.5-0.5b: {agree}/{n_new} tokens identical to the oracle, {decisive} decisive steps")
+    assert agree >= n_new - 2
