@@ -174,7 +174,9 @@ typedef struct lt_decode_desc {
     unsigned int* sync;        /* [2] grid-barrier counters, zero before the first launch */
     float* part_val;           /* [lt_decode_num_ctas()] */
     int* part_idx;             /* [lt_decode_num_ctas()] */
-    int* status;               /* device status word (or any int) */
+    int* status;               /* device status word; NULL = the library's own */
+    long long* trace;          /* optional [2][16*n_layers+8] SM-clock stamps of CTA 0 and the last CTA at
+                                  every phase boundary (diagnostics); NULL in production */
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);

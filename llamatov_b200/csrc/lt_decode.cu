@@ -128,6 +128,22 @@ __device__ __forceinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsign
     consumer_sync();
 }
 
+// optional phase-boundary time stamps (thread 0 of CTA 0 and of the last CTA)
+struct Tracer {
+    long long* buf;
+    int n;
+    __device__ __forceinline__ void init(const lt_decode_desc& P) {
+        buf = nullptr; n = 0;
+        if (P.trace != nullptr && threadIdx.x == 0) {
+            if (blockIdx.x == 0) buf = P.trace;
+            else if (blockIdx.x == gridDim.x - 1) buf = P.trace + (16 * P.n_layers + 8);
+        }
+    }
+    __device__ __forceinline__ void stamp() {
+        if (buf != nullptr) buf[n++] = clock64();
+    }
+};
+
 struct GemvDesc {
     const int8_t* Wq;
     const __half* Wd;
@@ -482,6 +498,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
     int besti = 2147483647;
     float dummy_v = 0.0f;
     int dummy_i = 0;
+    Tracer tr;
+    tr.init(P);
+    tr.stamp();
 
     // x for layer 0: gathered from the Q8_0 table by the device token, or preloaded by the host
     if (P.tok != nullptr) {
@@ -507,38 +526,54 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
         // P1: rmsnorm + quant -> q|k|v
         if (il > 0) stage_vector(P.x, sF, E);
         prologue_rms_quant(sF, ly->attn_norm, E, P.eps, sXq, sXd, S);
+        tr.stamp();
         consume_gemv<EPI_BIAS>(P, phase_desc(P, 4 * il + 0), ring, nstages, cnt, S, sXq, sXd, ly->qkv_bias, P.qkv,
                                dummy_v, dummy_i);
+        tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
         // P2: rope + append + attention
         if ((int)blockIdx.x < P.nh) attention_phase(P, ly, sAtt, vcap, S);
+        tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
         // P3: o_proj + residual; the cache length advances now that every head has read it
         if (blockIdx.x == 0 && tid == 0) {
             int p = __ldcg(ly->len);
             if (p >= 0 && p < P.max_seq) *ly->len = p + 1;
         }
         prologue_quant(P.att, nq, sXq, sXd);
+        tr.stamp();
         consume_gemv<EPI_RESID>(P, phase_desc(P, 4 * il + 1), ring, nstages, cnt, S, sXq, sXd, P.x, P.x1, dummy_v,
                                 dummy_i);
+        tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
         // P4: rmsnorm + quant -> gate|up
         stage_vector(P.x1, sF, E);
         prologue_rms_quant(sF, ly->ffn_norm, E, P.eps, sXq, sXd, S);
+        tr.stamp();
         consume_gemv<EPI_NONE>(P, phase_desc(P, 4 * il + 2), ring, nstages, cnt, S, sXq, sXd, nullptr, P.gu, dummy_v,
                                dummy_i);
+        tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
         // P5: silu*up + quant -> down + residual
         prologue_silu_quant(P.gu, P.gu + F, F, sXq, sXd);
+        tr.stamp();
         consume_gemv<EPI_RESID>(P, phase_desc(P, 4 * il + 3), ring, nstages, cnt, S, sXq, sXd, P.x1, P.x, dummy_v,
                                 dummy_i);
+        tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
     }
     // LM head + argmax
     stage_vector(P.x, sF, E);
     prologue_rms_quant(sF, P.out_norm, E, P.eps, sXq, sXd, S);
+    tr.stamp();
     consume_gemv<EPI_LOGITS>(P, phase_desc(P, 4 * P.n_layers), ring, nstages, cnt, S, sXq, sXd, nullptr, P.logits,
                              bestv, besti);
+    tr.stamp();
     if ((tid & 31) == 0) { S->best_v[warp] = bestv; S->best_i[warp] = besti; }
     consumer_sync();
     if (tid == 0) {

@@ -711,7 +711,8 @@ class _DecDesc(ctypes.Structure):
                [(n, ctypes.c_float) for n in ("eps", "theta", "scale")] + [("hist_cap", ctypes.c_int)] + \
                [(n, ctypes.c_void_p) for n in (
                    "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "x1", "qkv", "att", "gu",
-                   "logits", "tok", "out_tok", "history", "step", "sync", "part_val", "part_idx", "status")]
+                   "logits", "tok", "out_tok", "history", "step", "sync", "part_val", "part_idx", "status",
+                   "trace")]
 
 
 class FusedDecodeStep:
@@ -767,7 +768,14 @@ class FusedDecodeStep:
                              self.gu.data_ptr(), _addr(lbuf.ptr), None if tok_ptr is None else int(tok_ptr),
                              _addr(out_tok), None if history is None else int(history),
                              None if step is None else int(step), self.sync.data_ptr(), self.part_val.data_ptr(),
-                             self.part_idx.data_ptr(), None)
+                             self.part_idx.data_ptr(), None, None)
+
+    def enable_trace(self):
+        """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""
+        n = 16 * self.desc.n_layers + 8
+        self.trace = torch.zeros(2 * n, dtype=torch.int64, device="cuda")
+        self.desc.trace = self.trace.data_ptr()
+        return n
 
     def launch(self):
         rc = _lib.lib().lt_decode_step(ctypes.byref(self.desc), _stream())
@@ -858,6 +866,9 @@ class GraphRunner:
         global _DEVICE_EMBED
         self._assert_weight_cache_frozen()
         emb = _np(self.w["token_embd.weight"])
+        _weights(emb)       # an untied table is not used by the host-driven step: upload it now
+        self._weight_cache_frozen = (frozenset(_DEV_CONST.keys()), frozenset(fd._DEV_WEIGHT_CACHE.keys()),
+                                     frozenset(fd._Q8_WEIGHT_CACHE.keys()))
         Wq, Wd, V, K = fd._quantize_weight_q8_0(emb)
         if K != self.E:
             raise RuntimeError("token_embd.weight must be [n_embd, vocab]")
