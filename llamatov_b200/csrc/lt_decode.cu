@@ -7,14 +7,16 @@
 // producer warp per CTA runs ahead of the chain and keeps a ring of shared-memory stages
 // filled with the weight rows this CTA will need next (bulk async copies, global -> shared,
 // completion on an mbarrier; no multicast), across phase and layer boundaries.  The consumer
-// warps wait at a grid barrier only for the small activation vectors.
+// warps wait at a grid barrier only for the small activation vectors, and every phase issues
+// all of its global loads at once before it computes.
 //
 // Arithmetic is the per-op kernels' arithmetic, repeated verbatim (same device functions):
 //   P1  x -> rmsnorm(attn_norm) -> quant -> [q|k|v] GEMV + bias
 //   P2  rope(q,k at *len) -> append k,v at *len -> masked attention (one CTA per query head)
 //   P3  quant(att) -> o_proj GEMV + x -> x1            (*len += 1)
-//   P4  rmsnorm(ffn_norm)(x1) -> quant -> [gate|up] GEMV
-//   P5  silu(gate)*up -> quant -> down GEMV + x1 -> x
+//   P4  rmsnorm(ffn_norm)(x1) -> quant -> gate rows, then up rows of the same indices;
+//       v = silu(gate)*up is formed in the CTA that holds both
+//   P5  quant(v) -> down GEMV + x1 -> x
 //   LM  rmsnorm(out_norm)(x) -> quant -> LM-head GEMV -> logits, argmax
 // so the step is bit-identical to the chain of per-op launches.
 //
@@ -30,6 +32,9 @@ constexpr int DEC_CWARPS = 15;                  // consumer warps; warp 15 is th
 constexpr int DEC_CTHREADS = DEC_CWARPS * 32;
 constexpr int DEC_STAGE_BYTES = 32768;          // weight rows per stage (quants + scales)
 constexpr int DEC_STAGE_STRIDE = DEC_STAGE_BYTES + 128;
+constexpr int DEC_ILP = 4;                      // rows one warp folds together
+constexpr int DEC_MAX_LAYERS = 128;
+constexpr int DEC_ROWBUF = DEC_CTHREADS;        // per-CTA rows whose epilogue operand is staged
 constexpr long long DEC_WAIT_CLOCKS = 2000000000LL;   // ~1 s at 2 GHz
 
 // ---------------------------------------------------------------- PTX helpers
@@ -62,6 +67,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// 16-byte asynchronous copy global -> shared (no register staging)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_CTHREADS) : "memory"); }
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -75,10 +86,12 @@ struct Shared {
     unsigned long long empty[8];
     float sred[256];
     float red64[64];
+    float add[DEC_ROWBUF];      // epilogue operand (bias / residual) of this CTA's rows
+    float gate[DEC_ROWBUF];     // gate results of this CTA's rows, until the up rows arrive
+    int lens[DEC_MAX_LAYERS];   // cache lengths at kernel entry (attention CTAs)
     float best_v[DEC_CWARPS];
     int best_i[DEC_CWARPS];
     volatile int abort_flag;
-    int pos;
 };
 
 // bounded wait on an mbarrier phase; returns false (and raises the abort flag) on expiry
@@ -144,6 +157,12 @@ struct Tracer {
     }
 };
 
+// ---------------------------------------------------------------- phases
+// Five weight phases per layer (q|k|v, o, gate, up, down) and the LM head.  The gate and up
+// matrices are the two halves of the concatenated [2F, E] matrix; a CTA takes the same row
+// range of both halves.
+enum { PH_QKV = 0, PH_O = 1, PH_GATE = 2, PH_UP = 3, PH_DOWN = 4, PH_PER_LAYER = 5 };
+
 struct GemvDesc {
     const int8_t* Wq;
     const __half* Wd;
@@ -154,15 +173,20 @@ __device__ __forceinline__ GemvDesc phase_desc(const lt_decode_desc& P, int idx)
     GemvDesc d;
     const int L = P.n_layers;
     const int nq = P.nh * P.hd, nk = P.nkv * P.hd;
-    if (idx >= 4 * L) {
+    if (idx >= PH_PER_LAYER * L) {
         d.Wq = P.lm_q; d.Wd = (const __half*)P.lm_d; d.M = P.V; d.K = P.E;
         return d;
     }
-    const lt_decode_layer* ly = P.layers + (idx >> 2);
-    switch (idx & 3) {
-        case 0: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.M = nq + 2 * nk; d.K = P.E; break;
-        case 1: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.M = P.E; d.K = nq; break;
-        case 2: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.M = 2 * P.F; d.K = P.E; break;
+    const lt_decode_layer* ly = P.layers + idx / PH_PER_LAYER;
+    switch (idx % PH_PER_LAYER) {
+        case PH_QKV: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.M = nq + 2 * nk; d.K = P.E; break;
+        case PH_O: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.M = P.E; d.K = nq; break;
+        case PH_GATE: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.M = P.F; d.K = P.E; break;
+        case PH_UP:
+            d.Wq = ly->gu_q + (size_t)P.F * P.E;
+            d.Wd = (const __half*)ly->gu_d + (size_t)P.F * (P.E >> 5);
+            d.M = P.F; d.K = P.E;
+            break;
         default: d.Wq = ly->down_q; d.Wd = (const __half*)ly->down_d; d.M = P.E; d.K = P.F; break;
     }
     return d;
@@ -172,15 +196,17 @@ __device__ __forceinline__ void cta_rows(int M, int& r0, int& r1) {
     r0 = (int)(((long long)M * blockIdx.x) / gridDim.x);
     r1 = (int)(((long long)M * (blockIdx.x + 1)) / gridDim.x);
 }
+// rows per ring stage: as many as fit, at most DEC_ILP per consumer warp
 __device__ __forceinline__ int rows_per_chunk(int K) {
     int rc = DEC_STAGE_BYTES / (K + (K >> 4));
+    if (rc > DEC_CWARPS * DEC_ILP) rc = DEC_CWARPS * DEC_ILP;
     return rc < 1 ? 1 : rc;
 }
 
 // ---------------------------------------------------------------- producer
 __device__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
     unsigned cnt = 0;
-    const int nphases = 4 * P.n_layers + 1;
+    const int nphases = PH_PER_LAYER * P.n_layers + 1;
     for (int idx = 0; idx < nphases; idx++) {
         GemvDesc d = phase_desc(P, idx);
         int r0, r1;
@@ -195,25 +221,90 @@ __device__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int 
             }
             unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
             const unsigned qbytes = (unsigned)n * d.K;
-            const size_t d0 = ((size_t)r * nb * 2) & ~(size_t)15;
-            const size_t d1 = (((size_t)(r + n) * nb * 2) + 15) & ~(size_t)15;
+            // the scale rows are fetched as the enclosing 16-byte aligned window
+            const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb));
+            const size_t d0 = a0 & ~(size_t)15;
+            const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
             const unsigned dbytes = (unsigned)(d1 - d0);
             mbar_expect_tx(&S->full[stage], qbytes + dbytes);
             bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
-            bulk_g2s(dst + qbytes, (const unsigned char*)d.Wd + d0, dbytes, &S->full[stage]);
+            bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
         }
     }
 }
 
 // ---------------------------------------------------------------- consumer: GEMV phase
-enum { EPI_BIAS = 0, EPI_RESID = 1, EPI_NONE = 2, EPI_LOGITS = 3 };
+enum { EPI_ADD = 0, EPI_GATE = 1, EPI_UP = 2, EPI_LOGITS = 3 };
 
+// Fold the rows of one chunk that belong to this warp (rows warp, warp+15, ... of the chunk),
+// ILP of them together: the block loop is outermost, so every row keeps its own
+// ascending-block fma chain and its own 5-level shuffle tree, while the chains of different
+// rows overlap in the pipeline.  Lane k then finishes row k.
+template <int EPI, int ILP>
+__device__ __forceinline__ void fold_rows(const unsigned char* base, const __half* wdbase, int n, int K, int nb,
+                                          int r, int r0, Shared* S, const int8_t* sXq, const __half* sXd,
+                                          bool add_staged, const float* add_g, float* out, float& bestv, int& besti) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp >= n) return;
+    float acc[ILP];
+    const unsigned char* wq[ILP];
+    const __half* wd[ILP];
+#pragma unroll
+    for (int k = 0; k < ILP; k++) {
+        const int i = warp + k * DEC_CWARPS;
+        const int ii = i < n ? i : warp;      // an out-of-range slot repeats a valid row; its result is dropped
+        wq[k] = base + (size_t)ii * K;
+        wd[k] = wdbase + (size_t)ii * nb;
+        acc[k] = 0.0f;
+    }
+    for (int b = lane; b < nb; b += 32) {
+        const int4* xp = (const int4*)(sXq + b * 32);
+        const int4 x0 = xp[0], x1 = xp[1];
+        const float xd = __half2float(sXd[b]);
+#pragma unroll
+        for (int k = 0; k < ILP; k++) {
+            const int4* wp = (const int4*)(wq[k] + b * 32);
+            const int4 w0 = wp[0], w1 = wp[1];
+            acc[k] = q8_accum(__half2float(wd[k][b]), xd, block_dot(w0, w1, x0, x1), acc[k]);
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+        for (int k = 0; k < ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
+    }
+    float v = acc[0];
+#pragma unroll
+    for (int k = 1; k < ILP; k++) {
+        const float t = __shfl_sync(0xffffffffu, acc[k], 0);
+        if (lane == k) v = t;
+    }
+    const int i = warp + lane * DEC_CWARPS;
+    if (lane < ILP && i < n) {
+        const int row = r + i;
+        const int li = row - r0;
+        if (EPI == EPI_ADD) {
+            if (add_staged) v = __fadd_rn(v, S->add[li]);
+            else if (add_g != nullptr) v = __fadd_rn(v, __ldcg(add_g + row));
+            out[row] = v;
+        } else if (EPI == EPI_GATE) {
+            S->gate[li] = v;
+        } else if (EPI == EPI_UP) {
+            out[row] = silu_mul(S->gate[li], v);
+        } else {
+            out[row] = v;
+            if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
+        }
+    }
+}
+
+// One weight phase for this CTA's rows.
 template <int EPI>
 __device__ __forceinline__ void consume_gemv(const lt_decode_desc& P, const GemvDesc& d, unsigned char* ring,
                                              int nstages, unsigned& cnt, Shared* S, const int8_t* sXq,
-                                             const __half* sXd, const float* add, float* out, float& bestv,
-                                             int& besti) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+                                             const __half* sXd, bool add_staged, const float* add_g, float* out,
+                                             float& bestv, int& besti) {
+    const int lane = threadIdx.x & 31;
     int r0, r1;
     cta_rows(d.M, r0, r1);
     const int K = d.K, nb = K >> 5;
@@ -223,34 +314,17 @@ __device__ __forceinline__ void consume_gemv(const lt_decode_desc& P, const Gemv
         const unsigned stage = cnt % nstages;
         const bool ok = mbar_wait(&S->full[stage], (cnt / nstages) & 1, S, P.status);
         const unsigned char* base = ring + (size_t)stage * DEC_STAGE_STRIDE;
-        const size_t doff = ((size_t)r * nb * 2) & 15;
+        const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb)) & 15;
         const __half* wdbase = (const __half*)(base + (size_t)n * K + doff);
         if (ok) {
-            for (int i = warp; i < n; i += DEC_CWARPS) {
-                const unsigned char* wq = base + (size_t)i * K;
-                const __half* wd = wdbase + (size_t)i * nb;
-                float acc = 0.0f;
-                for (int b = lane; b < nb; b += 32) {
-                    const int4* wp = (const int4*)(wq + b * 32);
-                    const int4* xp = (const int4*)(sXq + b * 32);
-                    int4 w0 = wp[0], w1 = wp[1];
-                    int4 x0 = xp[0], x1 = xp[1];
-                    acc = q8_accum(__half2float(wd[b]), __half2float(sXd[b]), block_dot(w0, w1, x0, x1), acc);
-                }
-                float v = warp_tree_sum(acc);
-                if (lane == 0) {
-                    const int row = r + i;
-                    if (EPI == EPI_BIAS) {
-                        if (add != nullptr) v = __fadd_rn(v, __ldg(add + row));
-                    } else if (EPI == EPI_RESID) {
-                        v = __fadd_rn(v, __ldcg(add + row));
-                    }
-                    out[row] = v;
-                    if (EPI == EPI_LOGITS) {
-                        if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
-                    }
-                }
-            }
+            if (n > 3 * DEC_CWARPS)
+                fold_rows<EPI, 4>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
+            else if (n > 2 * DEC_CWARPS)
+                fold_rows<EPI, 3>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
+            else if (n > DEC_CWARPS)
+                fold_rows<EPI, 2>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
+            else
+                fold_rows<EPI, 1>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&S->empty[stage]);
@@ -258,6 +332,45 @@ __device__ __forceinline__ void consume_gemv(const lt_decode_desc& P, const Gemv
 }
 
 // ---------------------------------------------------------------- consumer: prologues
+// Copy up to two global vectors into shared memory with all loads in flight together.
+// `coherent` vectors were written by other CTAs during this launch and bypass L1.
+template <int B>
+__device__ __forceinline__ void stage_vectors(const float* __restrict__ ga, float* sa, int na, bool coherent_a,
+                                              const float* __restrict__ gb, float* sb, int nb_) {
+    for (int base = 0; base < na || base < nb_; base += B * DEC_CTHREADS) {
+        float a[B], b[B];
+#pragma unroll
+        for (int k = 0; k < B; k++) {
+            const int j = base + k * DEC_CTHREADS + threadIdx.x;
+            a[k] = 0.0f; b[k] = 0.0f;
+            if (j < na) a[k] = coherent_a ? __ldcg(ga + j) : __ldg(ga + j);
+            if (gb != nullptr && j < nb_) b[k] = __ldg(gb + j);
+        }
+#pragma unroll
+        for (int k = 0; k < B; k++) {
+            const int j = base + k * DEC_CTHREADS + threadIdx.x;
+            if (j < na) sa[j] = a[k];
+            if (gb != nullptr && j < nb_) sb[j] = b[k];
+        }
+    }
+}
+
+// Epilogue operand (bias or residual) of this CTA's rows: the load is issued early, into a
+// register, and parked in shared memory once the phase's other loads are on their way.
+// Returns whether the operand is staged (it is not when the CTA has more rows than threads).
+__device__ __forceinline__ bool add_load(const float* __restrict__ add, int M, float& v) {
+    v = 0.0f;
+    if (add == nullptr) return false;
+    int r0, r1;
+    cta_rows(M, r0, r1);
+    if (r1 - r0 > DEC_ROWBUF) return false;
+    if ((int)threadIdx.x < r1 - r0) v = __ldcg(add + r0 + threadIdx.x);
+    return true;
+}
+__device__ __forceinline__ void add_store(bool staged, float v, Shared* S) {
+    if (staged && threadIdx.x < DEC_ROWBUF) S->add[threadIdx.x] = v;
+}
+
 // sum of squares in the declared 256-lane order over a vector staged in shared memory
 __device__ __forceinline__ float cta_rms_sumsq(const float* sF, int N, Shared* S) {
     const int t = threadIdx.x;
@@ -280,15 +393,15 @@ __device__ __forceinline__ float cta_rms_sumsq(const float* sF, int N, Shared* S
     return S->sred[0];
 }
 
-// sF holds x; writes quant(rmsnorm(x) * w) into sXq / sXd
-__device__ __forceinline__ void prologue_rms_quant(const float* sF, const float* __restrict__ normw, int N, float eps,
-                                                   int8_t* sXq, __half* sXd, Shared* S) {
+// sF holds x and sW the norm weight; writes quant(rmsnorm(x) * w) into sXq / sXd
+__device__ __forceinline__ void rms_quant_from_smem(const float* sF, const float* sW, int N, float eps, int8_t* sXq,
+                                                    __half* sXd, Shared* S) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float ss = cta_rms_sumsq(sF, N, S);
     const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)N), eps));
     for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
         const int j = b * 32 + lane;
-        float v = __fmul_rn(__fmul_rn(sF[j], inv), __ldg(normw + j));
+        float v = __fmul_rn(__fmul_rn(sF[j], inv), sW[j]);
         __half dh;
         int q = quant_lane(v, &dh);
         sXq[j] = (int8_t)q;
@@ -297,31 +410,12 @@ __device__ __forceinline__ void prologue_rms_quant(const float* sF, const float*
     consumer_sync();
 }
 
-__device__ __forceinline__ void stage_vector(const float* __restrict__ g, float* sF, int N) {
-    for (int j = threadIdx.x; j < N; j += DEC_CTHREADS) sF[j] = __ldcg(g + j);
-    consumer_sync();
-}
-
-__device__ __forceinline__ void prologue_quant(const float* __restrict__ g, int N, int8_t* sXq, __half* sXd) {
+__device__ __forceinline__ void quant_from_smem(const float* sF, int N, int8_t* sXq, __half* sXd) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
         const int j = b * 32 + lane;
         __half dh;
-        int q = quant_lane(__ldcg(g + j), &dh);
-        sXq[j] = (int8_t)q;
-        if (lane == 0) sXd[b] = dh;
-    }
-    consumer_sync();
-}
-
-__device__ __forceinline__ void prologue_silu_quant(const float* __restrict__ g, const float* __restrict__ u, int N,
-                                                    int8_t* sXq, __half* sXd) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
-        const int j = b * 32 + lane;
-        float v = silu_mul(__ldcg(g + j), __ldcg(u + j));
-        __half dh;
-        int q = quant_lane(v, &dh);
+        int q = quant_lane(sF[j], &dh);
         sXq[j] = (int8_t)q;
         if (lane == 0) sXd[b] = dh;
     }
@@ -329,13 +423,16 @@ __device__ __forceinline__ void prologue_silu_quant(const float* __restrict__ g,
 }
 
 // ---------------------------------------------------------------- consumer: attention phase
-// One CTA per query head.  sAtt: [maxt] probabilities, then hd (q) + hd (new k) + hd (new v)
-// floats, then the V staging area of vcap rows.
-__device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, float* sAtt, int vcap,
+// One CTA per query head.  Every global load of the phase is issued before the first use:
+// the head's q / k / v slices, one K row per thread into registers, and all V rows into
+// shared memory by 16-byte asynchronous copies.
+// sAtt: [maxt] probabilities, hd (q) + hd (new k) + hd (new v) floats, then vcap V rows.
+template <int HD4>      // hd / 4
+__device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int pos, float* sAtt, int vcap,
                                 Shared* S) {
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
-    const int hd = P.hd, nh = P.nh, nkv = P.nkv, maxt = P.max_seq;
+    const int hd = HD4 * 4, nh = P.nh, nkv = P.nkv, maxt = P.max_seq;
     const int nq = nh * hd, nk = nkv * hd;
     const int rep = nh / nkv, hk = h / rep;
     float* sh = sAtt;
@@ -344,43 +441,94 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
     float* sVn = sKn + hd;
     float* sV = sVn + hd;
 
-    int pos = __ldcg(ly->len);
     const bool room = (pos >= 0 && pos < maxt);
     if (!room) {
         if (tid == 0) atomicOr(P.status, (int)LT_STATUS_KV_OVERFLOW);
         pos = pos < 0 ? 0 : maxt;
     }
     const int L = room ? pos + 1 : pos;      // attention length after the append
-    // rope of this head's q and of the kv head's k at position pos; v is copied
+    const int Lc = room ? pos : L;           // rows that already live in the cache
+    const bool staged = (L <= vcap);
+    // (1) V rows of the cache -> shared memory, asynchronously
+    if (staged) {
+        for (int e = tid; e < Lc * HD4; e += DEC_CTHREADS) {
+            const int t = e / HD4, c = e - t * HD4;
+            cp_async16(sV + (size_t)t * hd + c * 4, ly->vcache + ((size_t)t * nkv + hk) * hd + c * 4);
+        }
+    }
+    // (2) this thread's K row (t = tid) into registers; (3) the q / k / v slices of the new token
+    constexpr int KB = HD4 > 16 ? 16 : HD4;     // float4s of the row held in registers
+    float4 kreg[KB];
+    const bool mine = (tid < Lc);
+    const float4* Krow = (const float4*)(ly->kcache + ((size_t)(mine ? tid : 0) * nkv + hk) * hd);
+    if (mine) {
+#pragma unroll
+        for (int i = 0; i < KB; i++) kreg[i] = Krow[i];
+    }
     const int half = hd >> 1;
-    if (tid < half) {
+    float a1 = 0.0f, a2 = 0.0f;
+    int role = -1, j = 0;
+    if (tid >= 256 && tid < 256 + half) { role = 0; j = tid - 256; a1 = __ldcg(P.qkv + h * hd + j); a2 = __ldcg(P.qkv + h * hd + j + half); }
+    else if (tid >= 320 && tid < 320 + half) { role = 1; j = tid - 320; a1 = __ldcg(P.qkv + nq + hk * hd + j); a2 = __ldcg(P.qkv + nq + hk * hd + j + half); }
+    else if (tid >= 384 && tid < 384 + half) { role = 2; j = tid - 384; a1 = __ldcg(P.qkv + nq + nk + hk * hd + j); a2 = __ldcg(P.qkv + nq + nk + hk * hd + j + half); }
+    if (role == 0) {
         float o1, o2;
-        rope_pair(__ldcg(P.qkv + h * hd + tid), __ldcg(P.qkv + h * hd + tid + half), tid, hd, P.theta, pos, o1, o2);
-        sQ[tid] = o1; sQ[tid + half] = o2;
-    } else if (tid >= 64 && tid < 64 + half) {
-        const int j = tid - 64;
+        rope_pair(a1, a2, j, hd, P.theta, pos, o1, o2);
+        sQ[j] = o1; sQ[j + half] = o2;
+    } else if (role == 1) {
         float o1, o2;
-        rope_pair(__ldcg(P.qkv + nq + hk * hd + j), __ldcg(P.qkv + nq + hk * hd + j + half), j, hd, P.theta, pos, o1, o2);
+        rope_pair(a1, a2, j, hd, P.theta, pos, o1, o2);
         sKn[j] = o1; sKn[j + half] = o2;
-    } else if (tid >= 256 && tid < 256 + hd) {
-        sVn[tid - 256] = __ldcg(P.qkv + nq + nk + hk * hd + (tid - 256));
+    } else if (role == 2) {
+        sVn[j] = a1; sVn[j + half] = a2;
     }
     consumer_sync();
-    if (room && (h % rep) == 0 && tid < hd) {
-        ly->kcache[((size_t)pos * nkv + hk) * hd + tid] = sKn[tid];
-        ly->vcache[((size_t)pos * nkv + hk) * hd + tid] = sVn[tid];
+    if (room && tid < hd) {
+        if ((h % rep) == 0) {
+            ly->kcache[((size_t)pos * nkv + hk) * hd + tid] = sKn[tid];
+            ly->vcache[((size_t)pos * nkv + hk) * hd + tid] = sVn[tid];
+        }
+        if (staged) sV[(size_t)pos * hd + tid] = sVn[tid];
     }
-    // scores
-    for (int t = tid; t < maxt; t += DEC_CTHREADS) {
+    // scores: thread t owns position t (positions beyond the thread count loop below)
+    {
+        float v = -1e30f;
+        if (tid < L) {
+            const float4* q4 = (const float4*)sQ;
+            const float4* kn4 = (const float4*)sKn;
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < KB; i++) {
+                const float4 kk = mine ? kreg[i] : kn4[i];
+                const float4 qq = q4[i];
+                s = __fmaf_rn(qq.x, kk.x, s);
+                s = __fmaf_rn(qq.y, kk.y, s);
+                s = __fmaf_rn(qq.z, kk.z, s);
+                s = __fmaf_rn(qq.w, kk.w, s);
+            }
+#pragma unroll
+            for (int i = KB; i < HD4; i++) {      // rows longer than the register window: second fetch
+                const float4 kk = mine ? Krow[i] : kn4[i];
+                const float4 qq = q4[i];
+                s = __fmaf_rn(qq.x, kk.x, s);
+                s = __fmaf_rn(qq.y, kk.y, s);
+                s = __fmaf_rn(qq.z, kk.z, s);
+                s = __fmaf_rn(qq.w, kk.w, s);
+            }
+            v = __fmul_rn(s, P.scale);
+        }
+        if (tid < maxt) sh[tid] = v;
+    }
+    for (int t = tid + DEC_CTHREADS; t < maxt; t += DEC_CTHREADS) {
         float v = -1e30f;
         if (t < L) {
-            const float* Kt = (room && t == pos) ? sKn : ly->kcache + ((size_t)t * nkv + hk) * hd;
-            const float4* K4 = (const float4*)Kt;
+            const float4* K4 = (room && t == pos) ? (const float4*)sKn : (const float4*)(ly->kcache + ((size_t)t * nkv + hk) * hd);
             const float4* q4 = (const float4*)sQ;
             float s = 0.0f;
-            for (int i = 0; i < (hd >> 2); i++) {
-                float4 kk = K4[i];
-                float4 qq = q4[i];
+#pragma unroll
+            for (int i = 0; i < HD4; i++) {
+                const float4 kk = K4[i];
+                const float4 qq = q4[i];
                 s = __fmaf_rn(qq.x, kk.x, s);
                 s = __fmaf_rn(qq.y, kk.y, s);
                 s = __fmaf_rn(qq.z, kk.z, s);
@@ -389,16 +537,6 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
             v = __fmul_rn(s, P.scale);
         }
         sh[t] = v;
-    }
-    // stage V rows (independent of the scores) while the scores settle
-    const bool staged = (L <= vcap);
-    if (staged) {
-        const int hq = hd >> 2;
-        for (int e = tid; e < L * hq; e += DEC_CTHREADS) {
-            const int t = e / hq, c = e - t * hq;
-            const float4* src = (room && t == pos) ? (const float4*)sVn : (const float4*)(ly->vcache + ((size_t)t * nkv + hk) * hd);
-            ((float4*)sV)[(size_t)t * hq + c] = src[c];
-        }
     }
     consumer_sync();
     // max over the frozen 64-lane layout (exact in any order)
@@ -412,11 +550,10 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
         float v = fmaxf(S->red64[tid], S->red64[tid + 32]);
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
-        if (tid == 0) S->red64[0] = v;
+        if (tid == 0) S->sred[0] = v;
     }
     consumer_sync();
-    const float mx = S->red64[0];
-    consumer_sync();
+    const float mx = S->sred[0];
     for (int t = tid; t < maxt; t += DEC_CTHREADS) sh[t] = __expf(__fsub_rn(sh[t], mx));
     consumer_sync();
     if (tid < 64) {
@@ -424,14 +561,15 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
         for (int t = tid; t < maxt; t += 64) ls = __fadd_rn(ls, sh[t]);
         S->red64[tid] = ls;
     }
+    cp_async_wait_all();
     consumer_sync();
     if (tid < 32) {
         float v = __fadd_rn(S->red64[tid], S->red64[tid + 32]);
         v = warp_tree_sum(v);
-        if (tid == 0) S->red64[0] = v;
+        if (tid == 0) S->sred[1] = v;
     }
     consumer_sync();
-    const float Z = S->red64[0];
+    const float Z = S->sred[1];
     if (tid < hd) {
         float acc = 0.0f;
         if (staged) {
@@ -439,7 +577,6 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
         } else {
             const float* Vd = ly->vcache + (size_t)hk * hd + tid;
             const size_t stride = (size_t)nkv * hd;
-            const int Lc = room ? pos : L;      // rows that live in the cache
             int t = 0;
             for (; t + 8 <= Lc; t += 8) {
                 float v[8];
@@ -458,7 +595,7 @@ __device__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* 
 
 // ---------------------------------------------------------------- the kernel
 __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_desc P, int nstages, int kmax,
-                                                                int fmax, int vcap) {
+                                                                int fmax, int vcap, int uarea) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     size_t off = (size_t)nstages * DEC_STAGE_STRIDE;
@@ -470,7 +607,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
     off += ((size_t)(kmax >> 5) * 2 + 127) & ~(size_t)127;
     float* sF = (float*)(smem + off);
     off += ((size_t)fmax * 4 + 127) & ~(size_t)127;
-    float* sAtt = (float*)(smem + off);
+    float* sW = (float*)(smem + off);
+    off += ((size_t)fmax * 4 + 127) & ~(size_t)127;
+    float* sAtt = (float*)(smem + off);      // attention area; doubles as the staging area of v in P5
+    (void)uarea;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -493,7 +633,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
     // ------------------------------------------------------------ consumers
     const unsigned nctas = gridDim.x;
     unsigned epoch = 0, cnt = 0;
-    const int E = P.E, F = P.F, nq = P.nh * P.hd;
+    const int E = P.E, F = P.F, nq = P.nh * P.hd, nqkv = nq + 2 * P.nkv * P.hd;
     float bestv = -3.4e38f;
     int besti = 2147483647;
     float dummy_v = 0.0f;
@@ -502,7 +642,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
     tr.init(P);
     tr.stamp();
 
+    // cache lengths of all layers (they only change by this kernel's own increment)
+    if ((int)blockIdx.x < P.nh)
+        for (int l = tid; l < P.n_layers; l += DEC_CTHREADS) S->lens[l] = __ldcg(P.layers[l].len);
+
     // x for layer 0: gathered from the Q8_0 table by the device token, or preloaded by the host
+    const lt_decode_layer* ly0 = P.layers;
     if (P.tok != nullptr) {
         int t = *P.tok;
         if (t < 0 || t >= P.V) {
@@ -511,29 +656,41 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
         }
         const int nbE = E >> 5;
         for (int j = tid; j < E; j += DEC_CTHREADS) {
-            float v = __fmul_rn(__half2float(((const __half*)P.emb_d)[(size_t)t * nbE + (j >> 5)]),
-                                (float)P.emb_q[(size_t)t * E + j]);
+            const __half dh = ((const __half*)P.emb_d)[(size_t)t * nbE + (j >> 5)];
+            const int8_t q = P.emb_q[(size_t)t * E + j];
+            const float nw = __ldg(ly0->attn_norm + j);
+            const float v = __fmul_rn(__half2float(dh), (float)q);
             sF[j] = v;
+            sW[j] = nw;
             if (blockIdx.x == 0) P.x[j] = v;
         }
-        consumer_sync();
     } else {
-        stage_vector(P.x, sF, E);
+        stage_vectors<4>(P.x, sF, E, true, ly0->attn_norm, sW, E);
     }
 
     for (int il = 0; il < P.n_layers; il++) {
         const lt_decode_layer* ly = P.layers + il;
-        // P1: rmsnorm + quant -> q|k|v
-        if (il > 0) stage_vector(P.x, sF, E);
-        prologue_rms_quant(sF, ly->attn_norm, E, P.eps, sXq, sXd, S);
+        const int pbase = PH_PER_LAYER * il;
+        // P1: rmsnorm + quant -> q|k|v (+bias)
+        float addv;
+        bool staged = add_load(ly->qkv_bias, nqkv, addv);
+        if (il > 0) stage_vectors<4>(P.x, sF, E, true, ly->attn_norm, sW, E);
+        add_store(staged, addv, S);
+        consumer_sync();
+        rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
         tr.stamp();
-        consume_gemv<EPI_BIAS>(P, phase_desc(P, 4 * il + 0), ring, nstages, cnt, S, sXq, sXd, ly->qkv_bias, P.qkv,
-                               dummy_v, dummy_i);
+        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_QKV), ring, nstages, cnt, S, sXq, sXd, staged, ly->qkv_bias,
+                              P.qkv, dummy_v, dummy_i);
         tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
         tr.stamp();
         // P2: rope + append + attention
-        if ((int)blockIdx.x < P.nh) attention_phase(P, ly, sAtt, vcap, S);
+        if ((int)blockIdx.x < P.nh) {
+            const int pos = S->lens[il];
+            if (P.hd == 64) attention_phase<16>(P, ly, pos, sAtt, vcap, S);
+            else if (P.hd == 128) attention_phase<32>(P, ly, pos, sAtt, vcap, S);
+            else attention_phase<8>(P, ly, pos, sAtt, vcap, S);
+        }
         tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
         tr.stamp();
@@ -542,38 +699,58 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
             int p = __ldcg(ly->len);
             if (p >= 0 && p < P.max_seq) *ly->len = p + 1;
         }
-        prologue_quant(P.att, nq, sXq, sXd);
+        staged = add_load(P.x, E, addv);
+        stage_vectors<4>(P.att, sF, nq, true, nullptr, nullptr, 0);
+        add_store(staged, addv, S);
+        consumer_sync();
+        quant_from_smem(sF, nq, sXq, sXd);
         tr.stamp();
-        consume_gemv<EPI_RESID>(P, phase_desc(P, 4 * il + 1), ring, nstages, cnt, S, sXq, sXd, P.x, P.x1, dummy_v,
-                                dummy_i);
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
-        // P4: rmsnorm + quant -> gate|up
-        stage_vector(P.x1, sF, E);
-        prologue_rms_quant(sF, ly->ffn_norm, E, P.eps, sXq, sXd, S);
-        tr.stamp();
-        consume_gemv<EPI_NONE>(P, phase_desc(P, 4 * il + 2), ring, nstages, cnt, S, sXq, sXd, nullptr, P.gu, dummy_v,
-                               dummy_i);
+        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_O), ring, nstages, cnt, S, sXq, sXd, staged, P.x, P.x1,
+                              dummy_v, dummy_i);
         tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
         tr.stamp();
-        // P5: silu*up + quant -> down + residual
-        prologue_silu_quant(P.gu, P.gu + F, F, sXq, sXd);
+        // P4: rmsnorm + quant -> gate rows, up rows, v = silu(gate) * up
+        stage_vectors<4>(P.x1, sF, E, true, ly->ffn_norm, sW, E);
+        consumer_sync();
+        rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
         tr.stamp();
-        consume_gemv<EPI_RESID>(P, phase_desc(P, 4 * il + 3), ring, nstages, cnt, S, sXq, sXd, P.x1, P.x, dummy_v,
-                                dummy_i);
+        consume_gemv<EPI_GATE>(P, phase_desc(P, pbase + PH_GATE), ring, nstages, cnt, S, sXq, sXd, false, nullptr,
+                               nullptr, dummy_v, dummy_i);
+        consumer_sync();
+        consume_gemv<EPI_UP>(P, phase_desc(P, pbase + PH_UP), ring, nstages, cnt, S, sXq, sXd, false, nullptr, P.gu,
+                             dummy_v, dummy_i);
+        tr.stamp();
+        grid_sync(P.sync, epoch, nctas, S, P.status);
+        tr.stamp();
+        // P5: quant(v) -> down + residual
+        staged = add_load(P.x1, E, addv);
+        stage_vectors<12>(P.gu, sAtt, F, true, nullptr, nullptr, 0);
+        add_store(staged, addv, S);
+        consumer_sync();
+        quant_from_smem(sAtt, F, sXq, sXd);
+        tr.stamp();
+        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_DOWN), ring, nstages, cnt, S, sXq, sXd, staged, P.x1, P.x,
+                              dummy_v, dummy_i);
         tr.stamp();
         grid_sync(P.sync, epoch, nctas, S, P.status);
         tr.stamp();
     }
     // LM head + argmax
-    stage_vector(P.x, sF, E);
-    prologue_rms_quant(sF, P.out_norm, E, P.eps, sXq, sXd, S);
+    stage_vectors<4>(P.x, sF, E, true, P.out_norm, sW, E);
+    consumer_sync();
+    rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
     tr.stamp();
-    consume_gemv<EPI_LOGITS>(P, phase_desc(P, 4 * P.n_layers), ring, nstages, cnt, S, sXq, sXd, nullptr, P.logits,
-                             bestv, besti);
+    consume_gemv<EPI_LOGITS>(P, phase_desc(P, PH_PER_LAYER * P.n_layers), ring, nstages, cnt, S, sXq, sXd, false,
+                             nullptr, P.logits, bestv, besti);
     tr.stamp();
+    // lanes 0..DEC_ILP-1 of every warp hold candidates
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bestv, s);
+        int oi = __shfl_xor_sync(0xffffffffu, besti, s);
+        if (ov > bestv || (ov == bestv && oi < besti)) { bestv = ov; besti = oi; }
+    }
     if ((tid & 31) == 0) { S->best_v[warp] = bestv; S->best_i[warp] = besti; }
     consumer_sync();
     if (tid == 0) {
@@ -613,6 +790,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
             }
         }
     }
+    tr.stamp();
     // the last CTA to get here resets the barrier counters for the next launch
     if (tid == 0) {
         __threadfence();
@@ -625,7 +803,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
 }
 
 struct DecodeGeometry {
-    int nstages, kmax, fmax, vcap;
+    int nstages, kmax, fmax, vcap, uarea;
     size_t smem;
     int ctas;
 };
@@ -639,30 +817,35 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
     g->kmax = d->E > d->F ? d->E : d->F;
     if (nq > g->kmax) g->kmax = nq;
     g->fmax = d->E > nq ? d->E : nq;
-    size_t fixed = ((sizeof(Shared) + 127) & ~(size_t)127) + (((size_t)g->kmax + 127) & ~(size_t)127) +
-                   (((size_t)(g->kmax >> 5) * 2 + 127) & ~(size_t)127) + (((size_t)g->fmax * 4 + 127) & ~(size_t)127);
-    size_t att_fixed = ((size_t)d->max_seq + 3 * d->hd) * 4;
-    // at least 3 stages for the ring; the rest goes to V staging (up to max_seq rows)
-    size_t avail = (size_t)smem_max - 1024;
-    if (fixed + att_fixed + 3 * (size_t)DEC_STAGE_STRIDE > avail) {
+    const size_t r128 = 127;
+    size_t fixed = ((sizeof(Shared) + r128) & ~r128) + (((size_t)g->kmax + r128) & ~r128) +
+                   (((size_t)(g->kmax >> 5) * 2 + r128) & ~r128) + 2 * (((size_t)g->fmax * 4 + r128) & ~r128);
+    const size_t att_fixed = ((size_t)d->max_seq + 3 * d->hd) * 4;
+    const size_t vrow = (size_t)d->hd * 4;
+    const size_t v_stage = (size_t)d->F * 4;      // P5 stages v in the attention area
+    const size_t avail = (size_t)smem_max - 1024;
+    const size_t min_area = att_fixed > v_stage ? att_fixed : v_stage;
+    if (fixed + min_area + 2 * (size_t)DEC_STAGE_STRIDE > avail) {
         set_error("lt_decode_step: model dimensions need more shared memory than one SM has");
         return LT_ERR_UNSUPPORTED;
     }
-    size_t left = avail - fixed - att_fixed;
-    size_t vrow = (size_t)d->hd * 4;
-    size_t vwant = (size_t)d->max_seq * vrow;
+    // ring first (up to 4 stages), then as many staged V rows as fit (up to max_seq)
+    size_t left = avail - fixed;
     int nst = 4;
-    if (left >= 4 * (size_t)DEC_STAGE_STRIDE + vwant) {
-        g->vcap = d->max_seq;
-        nst = (int)((left - vwant) / DEC_STAGE_STRIDE);
-    } else {
-        nst = (int)(left / DEC_STAGE_STRIDE);
-        if (nst > 4) nst = 4;
-        g->vcap = (int)((left - (size_t)nst * DEC_STAGE_STRIDE) / vrow);
+    while (nst > 2 && (size_t)nst * DEC_STAGE_STRIDE + min_area > left) nst--;
+    size_t area = left - (size_t)nst * DEC_STAGE_STRIDE;
+    size_t want = att_fixed + (size_t)d->max_seq * vrow;
+    if (want < v_stage) want = v_stage;
+    if (area > want) {
+        // spare room: deepen the ring
+        while (nst < 8 && area >= want + (size_t)DEC_STAGE_STRIDE) { nst++; area -= DEC_STAGE_STRIDE; }
+        area = want;
     }
-    if (nst > 8) nst = 8;
     g->nstages = nst;
-    g->smem = (size_t)nst * DEC_STAGE_STRIDE + fixed + att_fixed + (size_t)g->vcap * vrow + 128;
+    g->uarea = (int)area;
+    g->vcap = area > att_fixed ? (int)((area - att_fixed) / vrow) : 0;
+    if (g->vcap > d->max_seq) g->vcap = d->max_seq;
+    g->smem = (size_t)nst * DEC_STAGE_STRIDE + fixed + area + 128;
     g->ctas = sms;
     return LT_OK;
 }
@@ -677,18 +860,20 @@ extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
                    d->logits && d->out_tok && d->sync && d->part_val && d->part_idx,
                "lt_decode_step: null pointer in descriptor");
     LT_REQUIRE(d->tok == nullptr || (d->emb_q && d->emb_d), "lt_decode_step: device token loop needs the embedding table");
-    LT_REQUIRE(d->n_layers > 0 && d->E > 0 && d->F > 0 && d->V > 0 && d->max_seq > 0, "lt_decode_step: bad dimensions");
+    LT_REQUIRE(d->n_layers > 0 && d->n_layers <= DEC_MAX_LAYERS && d->E > 0 && d->F > 0 && d->V > 0 && d->max_seq > 0,
+               "lt_decode_step: bad dimensions");
     LT_REQUIRE(d->E % 32 == 0 && d->F % 32 == 0 && (d->nh * d->hd) % 32 == 0, "lt_decode_step: E, F and nh*hd must be multiples of 32");
-    LT_REQUIRE(d->hd % 4 == 0 && d->hd <= 128, "lt_decode_step: hd=%d must be a multiple of 4, at most 128", d->hd);
+    LT_REQUIRE(d->hd == 32 || d->hd == 64 || d->hd == 128, "lt_decode_step: hd=%d must be 32, 64 or 128", d->hd);
     LT_REQUIRE(d->nkv > 0 && d->nh % d->nkv == 0, "lt_decode_step: nh must be a multiple of nkv");
     LT_REQUIRE(d->max_seq % 4 == 0, "lt_decode_step: max_seq=%d must be a multiple of 4", d->max_seq);
     const int nq = d->nh * d->hd, nk = d->nkv * d->hd;
-    // the scale rows of each matrix are fetched in 16-byte windows: the array must end on one
-    const long long ms[5] = {(long long)(nq + 2 * nk) * (d->E / 32), (long long)d->E * (nq / 32),
-                             (long long)2 * d->F * (d->E / 32), (long long)d->E * (d->F / 32),
-                             (long long)d->V * (d->E / 32)};
-    for (int i = 0; i < 5; i++)
-        LT_REQUIRE(ms[i] % 8 == 0, "lt_decode_step: a weight matrix has M*K/32 = %lld scales, not a multiple of 8", ms[i]);
+    // scale rows are fetched in 16-byte windows: every matrix (and the up half of gate|up) must
+    // hold a multiple of 8 scales so that no window crosses the end of its array
+    const long long ms[6] = {(long long)(nq + 2 * nk) * (d->E / 32), (long long)d->E * (nq / 32),
+                             (long long)d->F * (d->E / 32), (long long)2 * d->F * (d->E / 32),
+                             (long long)d->E * (d->F / 32), (long long)d->V * (d->E / 32)};
+    for (int i = 0; i < 6; i++)
+        LT_REQUIRE(ms[i] % 8 == 0, "lt_decode_step: a weight matrix has %lld scales, not a multiple of 8", ms[i]);
     DecodeGeometry g;
     int rc = decode_geometry(d, &g);
     if (rc != LT_OK) return rc;
@@ -697,8 +882,8 @@ extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
     lt_decode_desc P = *d;
     if (P.status == nullptr) P.status = device_status_ptr();
     LT_REQUIRE(P.status != nullptr, "lt_decode_step: status word unavailable");
-    int nstages = g.nstages, kmax = g.kmax, fmax = g.fmax, vcap = g.vcap;
-    void* args[] = {&P, &nstages, &kmax, &fmax, &vcap};
+    int nstages = g.nstages, kmax = g.kmax, fmax = g.fmax, vcap = g.vcap, uarea = g.uarea;
+    void* args[] = {&P, &nstages, &kmax, &fmax, &vcap, &uarea};
     // cooperative launch: all CTAs are resident together, which the grid barrier relies on
     LT_CUDA(cudaLaunchCooperativeKernel((const void*)k_decode_step, dim3(g.ctas), dim3(DEC_THREADS), args, g.smem,
                                         (cudaStream_t)stream));
