@@ -175,8 +175,8 @@ typedef struct lt_decode_desc {
     float* part_val;           /* [lt_decode_num_ctas()] */
     int* part_idx;             /* [lt_decode_num_ctas()] */
     int* status;               /* device status word; NULL = the library's own */
-    long long* trace;          /* optional [2][16*n_layers+8] SM-clock stamps of CTA 0 and the last CTA at
-                                  every phase boundary (diagnostics); NULL in production */
+    long long* trace;          /* optional [2][8192][2] (id, SM clock) stamps of CTA 0 and of the last CTA
+                                  (diagnostics); NULL in production */
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);

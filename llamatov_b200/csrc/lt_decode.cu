@@ -81,6 +81,8 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     return v;
 }
 
+enum { KIND_QKV = 0, KIND_O = 1, KIND_GU = 2, KIND_DOWN = 3, KIND_LM = 4, KIND_COUNT = 5 };
+
 struct Shared {
     unsigned long long full[8];
     unsigned long long empty[8];
@@ -89,14 +91,15 @@ struct Shared {
     float add[DEC_ROWBUF];      // epilogue operand (bias / residual) of this CTA's rows
     float gate[DEC_ROWBUF];     // gate results of this CTA's rows, until the up rows arrive
     int lens[DEC_MAX_LAYERS];   // cache lengths at kernel entry (attention CTAs)
+    lt_decode_layer ly[2];      // descriptor of the current and of the next layer
+    int row0[KIND_COUNT], row1[KIND_COUNT];   // this CTA's row range per matrix kind
     float best_v[DEC_CWARPS];
     int best_i[DEC_CWARPS];
     volatile int abort_flag;
 };
 
 // bounded wait on an mbarrier phase; returns false (and raises the abort flag) on expiry
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
     long long t0 = clock64();
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -113,15 +116,39 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     }
     return true;
 }
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, S, status);
+}
+
+// optional time stamps (thread 0 of CTA 0 and of the last CTA): pairs (id, SM clock)
+constexpr int DEC_TRACE_CAP = 8192;      // entries per traced CTA
+struct Tracer {
+    long long* buf;
+    int n;
+    __device__ __forceinline__ void init(const lt_decode_desc& P) {
+        buf = nullptr; n = 0;
+        if (P.trace != nullptr && threadIdx.x == 0) {
+            if (blockIdx.x == 0) buf = P.trace;
+            else if (blockIdx.x == gridDim.x - 1) buf = P.trace + 2 * DEC_TRACE_CAP;
+        }
+    }
+    __device__ __forceinline__ void stamp(int id) {
+        if (buf != nullptr && n < DEC_TRACE_CAP) { buf[2 * n] = id; buf[2 * n + 1] = clock64(); n++; }
+    }
+};
 
 // Grid barrier for the consumer warps of all CTAs.  `epoch` counts barriers of this launch;
 // the counter is monotonic within a launch and reset by the last CTA to leave the kernel.
-__device__ __forceinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsigned nctas, Shared* S, int* status) {
+__device__ __noinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsigned nctas, Shared* S, int* status,
+                                       Tracer& tr) {
     consumer_sync();
+    tr.stamp(90);
     epoch += 1;
     if (threadIdx.x == 0 && !S->abort_flag) {
         __threadfence();
         atomicAdd(ctr, 1u);
+        tr.stamp(91);
         const unsigned target = epoch * nctas;
         long long t0 = clock64();
         unsigned spins = 0;
@@ -141,22 +168,6 @@ __device__ __forceinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsign
     consumer_sync();
 }
 
-// optional phase-boundary time stamps (thread 0 of CTA 0 and of the last CTA)
-struct Tracer {
-    long long* buf;
-    int n;
-    __device__ __forceinline__ void init(const lt_decode_desc& P) {
-        buf = nullptr; n = 0;
-        if (P.trace != nullptr && threadIdx.x == 0) {
-            if (blockIdx.x == 0) buf = P.trace;
-            else if (blockIdx.x == gridDim.x - 1) buf = P.trace + (16 * P.n_layers + 8);
-        }
-    }
-    __device__ __forceinline__ void stamp() {
-        if (buf != nullptr) buf[n++] = clock64();
-    }
-};
-
 // ---------------------------------------------------------------- phases
 // Five weight phases per layer (q|k|v, o, gate, up, down) and the LM head.  The gate and up
 // matrices are the two halves of the concatenated [2F, E] matrix; a CTA takes the same row
@@ -166,29 +177,28 @@ enum { PH_QKV = 0, PH_O = 1, PH_GATE = 2, PH_UP = 3, PH_DOWN = 4, PH_PER_LAYER =
 struct GemvDesc {
     const int8_t* Wq;
     const __half* Wd;
-    int M, K;
+    int M, K, kind;
 };
 
-__device__ __forceinline__ GemvDesc phase_desc(const lt_decode_desc& P, int idx) {
+__device__ __forceinline__ GemvDesc layer_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int ph) {
     GemvDesc d;
-    const int L = P.n_layers;
     const int nq = P.nh * P.hd, nk = P.nkv * P.hd;
-    if (idx >= PH_PER_LAYER * L) {
-        d.Wq = P.lm_q; d.Wd = (const __half*)P.lm_d; d.M = P.V; d.K = P.E;
-        return d;
-    }
-    const lt_decode_layer* ly = P.layers + idx / PH_PER_LAYER;
-    switch (idx % PH_PER_LAYER) {
-        case PH_QKV: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.M = nq + 2 * nk; d.K = P.E; break;
-        case PH_O: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.M = P.E; d.K = nq; break;
-        case PH_GATE: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.M = P.F; d.K = P.E; break;
+    switch (ph) {
+        case PH_QKV: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.M = nq + 2 * nk; d.K = P.E; d.kind = KIND_QKV; break;
+        case PH_O: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.M = P.E; d.K = nq; d.kind = KIND_O; break;
+        case PH_GATE: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.M = P.F; d.K = P.E; d.kind = KIND_GU; break;
         case PH_UP:
             d.Wq = ly->gu_q + (size_t)P.F * P.E;
             d.Wd = (const __half*)ly->gu_d + (size_t)P.F * (P.E >> 5);
-            d.M = P.F; d.K = P.E;
+            d.M = P.F; d.K = P.E; d.kind = KIND_GU;
             break;
-        default: d.Wq = ly->down_q; d.Wd = (const __half*)ly->down_d; d.M = P.E; d.K = P.F; break;
+        default: d.Wq = ly->down_q; d.Wd = (const __half*)ly->down_d; d.M = P.E; d.K = P.F; d.kind = KIND_DOWN; break;
     }
+    return d;
+}
+__device__ __forceinline__ GemvDesc lm_phase(const lt_decode_desc& P) {
+    GemvDesc d;
+    d.Wq = P.lm_q; d.Wd = (const __half*)P.lm_d; d.M = P.V; d.K = P.E; d.kind = KIND_LM;
     return d;
 }
 
@@ -204,146 +214,151 @@ __device__ __forceinline__ int rows_per_chunk(int K) {
 }
 
 // ---------------------------------------------------------------- producer
-__device__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
-    unsigned cnt = 0;
-    const int nphases = PH_PER_LAYER * P.n_layers + 1;
-    for (int idx = 0; idx < nphases; idx++) {
-        GemvDesc d = phase_desc(P, idx);
-        int r0, r1;
-        cta_rows(d.M, r0, r1);
-        const int nb = d.K >> 5;
-        const int RC = rows_per_chunk(d.K);
-        for (int r = r0; r < r1; r += RC, cnt++) {
-            const int n = (r1 - r < RC) ? (r1 - r) : RC;
-            const unsigned stage = cnt % nstages;
-            if (cnt >= (unsigned)nstages) {
-                if (!mbar_wait(&S->empty[stage], ((cnt / nstages) - 1) & 1, S, P.status)) return;
-            }
-            unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
-            const unsigned qbytes = (unsigned)n * d.K;
-            // the scale rows are fetched as the enclosing 16-byte aligned window
-            const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb));
-            const size_t d0 = a0 & ~(size_t)15;
-            const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
-            const unsigned dbytes = (unsigned)(d1 - d0);
-            mbar_expect_tx(&S->full[stage], qbytes + dbytes);
-            bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
-            bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
+__device__ __forceinline__ void produce_phase(const lt_decode_desc& P, const GemvDesc& d, unsigned char* ring,
+                                              int nstages, unsigned& cnt, Shared* S, bool& alive) {
+    const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
+    const int nb = d.K >> 5;
+    const int RC = rows_per_chunk(d.K);
+    for (int r = r0; r < r1 && alive; r += RC, cnt++) {
+        const int n = (r1 - r < RC) ? (r1 - r) : RC;
+        const unsigned stage = cnt % nstages;
+        if (cnt >= (unsigned)nstages) {
+            if (!mbar_wait(&S->empty[stage], ((cnt / nstages) - 1) & 1, S, P.status)) { alive = false; return; }
         }
+        unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
+        const unsigned qbytes = (unsigned)n * d.K;
+        // the scale rows are fetched as the enclosing 16-byte aligned window
+        const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb));
+        const size_t d0 = a0 & ~(size_t)15;
+        const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
+        const unsigned dbytes = (unsigned)(d1 - d0);
+        mbar_expect_tx(&S->full[stage], qbytes + dbytes);
+        bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
+        bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
     }
+}
+
+__device__ __noinline__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
+    unsigned cnt = 0;
+    bool alive = true;
+    for (int il = 0; il < P.n_layers && alive; il++) {
+        const lt_decode_layer* ly = P.layers + il;      // read from global: the producer runs ahead of the consumers
+        for (int ph = 0; ph < PH_PER_LAYER && alive; ph++) produce_phase(P, layer_phase(P, ly, ph), ring, nstages, cnt, S, alive);
+    }
+    if (alive) produce_phase(P, lm_phase(P), ring, nstages, cnt, S, alive);
 }
 
 // ---------------------------------------------------------------- consumer: GEMV phase
 enum { EPI_ADD = 0, EPI_GATE = 1, EPI_UP = 2, EPI_LOGITS = 3 };
 
-// Fold the rows of one chunk that belong to this warp (rows warp, warp+15, ... of the chunk),
-// ILP of them together: the block loop is outermost, so every row keeps its own
-// ascending-block fma chain and its own 5-level shuffle tree, while the chains of different
-// rows overlap in the pipeline.  Lane k then finishes row k.
-template <int EPI, int ILP>
-__device__ __forceinline__ void fold_rows(const unsigned char* base, const __half* wdbase, int n, int K, int nb,
-                                          int r, int r0, Shared* S, const int8_t* sXq, const __half* sXd,
-                                          bool add_staged, const float* add_g, float* out, float& bestv, int& besti) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp >= n) return;
-    float acc[ILP];
-    const unsigned char* wq[ILP];
-    const __half* wd[ILP];
-#pragma unroll
-    for (int k = 0; k < ILP; k++) {
-        const int i = warp + k * DEC_CWARPS;
-        const int ii = i < n ? i : warp;      // an out-of-range slot repeats a valid row; its result is dropped
-        wq[k] = base + (size_t)ii * K;
-        wd[k] = wdbase + (size_t)ii * nb;
-        acc[k] = 0.0f;
-    }
-    for (int b = lane; b < nb; b += 32) {
-        const int4* xp = (const int4*)(sXq + b * 32);
-        const int4 x0 = xp[0], x1 = xp[1];
-        const float xd = __half2float(sXd[b]);
-#pragma unroll
-        for (int k = 0; k < ILP; k++) {
-            const int4* wp = (const int4*)(wq[k] + b * 32);
-            const int4 w0 = wp[0], w1 = wp[1];
-            acc[k] = q8_accum(__half2float(wd[k][b]), xd, block_dot(w0, w1, x0, x1), acc[k]);
-        }
-    }
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-#pragma unroll
-        for (int k = 0; k < ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
-    }
-    float v = acc[0];
-#pragma unroll
-    for (int k = 1; k < ILP; k++) {
-        const float t = __shfl_sync(0xffffffffu, acc[k], 0);
-        if (lane == k) v = t;
-    }
-    const int i = warp + lane * DEC_CWARPS;
-    if (lane < ILP && i < n) {
-        const int row = r + i;
-        const int li = row - r0;
-        if (EPI == EPI_ADD) {
-            if (add_staged) v = __fadd_rn(v, S->add[li]);
-            else if (add_g != nullptr) v = __fadd_rn(v, __ldcg(add_g + row));
-            out[row] = v;
-        } else if (EPI == EPI_GATE) {
-            S->gate[li] = v;
-        } else if (EPI == EPI_UP) {
-            out[row] = silu_mul(S->gate[li], v);
-        } else {
-            out[row] = v;
-            if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
-        }
-    }
-}
+struct Epilogue {
+    int kind;               // EPI_*
+    bool add_staged;        // operand in Shared::add
+    const float* add_g;     // operand in global memory (used when not staged), or NULL
+    float* out;
+};
 
-// One weight phase for this CTA's rows.
-template <int EPI>
-__device__ __forceinline__ void consume_gemv(const lt_decode_desc& P, const GemvDesc& d, unsigned char* ring,
-                                             int nstages, unsigned& cnt, Shared* S, const int8_t* sXq,
-                                             const __half* sXd, bool add_staged, const float* add_g, float* out,
-                                             float& bestv, int& besti) {
-    const int lane = threadIdx.x & 31;
-    int r0, r1;
-    cta_rows(d.M, r0, r1);
+// One weight phase for this CTA's rows.  A warp folds up to DEC_ILP rows of a chunk together
+// (rows warp, warp+15, ... of the chunk): the block loop is outermost, so every row keeps its
+// own ascending-block fma chain and its own 5-level shuffle tree, while the chains of
+// different rows overlap in the pipeline.  Lane k then finishes row k.  One copy of this code
+// serves every phase (the epilogue is selected at run time) so that the whole step stays
+// resident in the instruction cache.
+__device__ __noinline__ void consume_gemv(const lt_decode_desc& P, const GemvDesc& d, const Epilogue& ep,
+                                          unsigned char* ring, int nstages, unsigned& cnt, Shared* S,
+                                          const int8_t* sXq, const __half* sXd, float& bestv, int& besti,
+                                          Tracer& tr) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
     const int K = d.K, nb = K >> 5;
     const int RC = rows_per_chunk(K);
+    tr.stamp(20);
     for (int r = r0; r < r1; r += RC, cnt++) {
         const int n = (r1 - r < RC) ? (r1 - r) : RC;
         const unsigned stage = cnt % nstages;
         const bool ok = mbar_wait(&S->full[stage], (cnt / nstages) & 1, S, P.status);
+        tr.stamp(21);
         const unsigned char* base = ring + (size_t)stage * DEC_STAGE_STRIDE;
         const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb)) & 15;
         const __half* wdbase = (const __half*)(base + (size_t)n * K + doff);
-        if (ok) {
-            if (n > 3 * DEC_CWARPS)
-                fold_rows<EPI, 4>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
-            else if (n > 2 * DEC_CWARPS)
-                fold_rows<EPI, 3>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
-            else if (n > DEC_CWARPS)
-                fold_rows<EPI, 2>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
-            else
-                fold_rows<EPI, 1>(base, wdbase, n, K, nb, r, r0, S, sXq, sXd, add_staged, add_g, out, bestv, besti);
+        const int nv = (n - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // rows of this chunk that are this warp's (<= DEC_ILP)
+        if (ok && nv > 0) {
+            float acc[DEC_ILP];
+#pragma unroll
+            for (int k = 0; k < DEC_ILP; k++) acc[k] = 0.0f;
+            for (int b = lane; b < nb; b += 32) {
+                const int4* xp = (const int4*)(sXq + b * 32);
+                const int4 x0 = xp[0], x1 = xp[1];
+                const float xd = __half2float(sXd[b]);
+#pragma unroll
+                for (int k = 0; k < DEC_ILP; k++) {
+                    if (k < nv) {       // warp-uniform
+                        const int i = warp + k * DEC_CWARPS;
+                        const int4* wp = (const int4*)(base + (size_t)i * K + b * 32);
+                        const int4 w0 = wp[0], w1 = wp[1];
+                        const float wd = __half2float(wdbase[(size_t)i * nb + b]);
+                        acc[k] = q8_accum(wd, xd, block_dot(w0, w1, x0, x1), acc[k]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+                for (int k = 0; k < DEC_ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
+            }
+            float v = acc[0];
+#pragma unroll
+            for (int k = 1; k < DEC_ILP; k++) {
+                const float t = __shfl_sync(0xffffffffu, acc[k], 0);
+                if (lane == k) v = t;
+            }
+            if (lane < nv) {
+                const int row = r + warp + lane * DEC_CWARPS;
+                const int li = row - r0;
+                if (ep.kind == EPI_ADD) {
+                    if (ep.add_staged) v = __fadd_rn(v, S->add[li]);
+                    else if (ep.add_g != nullptr) v = __fadd_rn(v, __ldcg(ep.add_g + row));
+                    ep.out[row] = v;
+                } else if (ep.kind == EPI_GATE) {
+                    S->gate[li] = v;
+                } else if (ep.kind == EPI_UP) {
+                    ep.out[row] = silu_mul(S->gate[li], v);
+                } else {
+                    ep.out[row] = v;
+                    if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
+                }
+            }
         }
         __syncwarp();
+        tr.stamp(22);
         if (lane == 0) mbar_arrive(&S->empty[stage]);
     }
 }
 
 // ---------------------------------------------------------------- consumer: prologues
-// Copy up to two global vectors into shared memory with all loads in flight together.
-// `coherent` vectors were written by other CTAs during this launch and bypass L1.
+// Copy up to two global vectors into shared memory with all loads in flight together, plus
+// (optionally) the epilogue operand of this CTA's rows.  `ga` was written by other CTAs during
+// this launch and bypasses L1; `gb` is a constant of the model.
+// Returns whether the epilogue operand was staged.
 template <int B>
-__device__ __forceinline__ void stage_vectors(const float* __restrict__ ga, float* sa, int na, bool coherent_a,
-                                              const float* __restrict__ gb, float* sb, int nb_) {
+__device__ __forceinline__ bool stage_impl(const float* __restrict__ ga, float* sa, int na, const float* __restrict__ gb,
+                                           float* sb, int nb_, const float* __restrict__ add, int kind, Shared* S) {
+    float addv = 0.0f;
+    bool staged = false;
+    if (add != nullptr) {
+        const int r0 = S->row0[kind], n = S->row1[kind] - r0;
+        if (n <= DEC_ROWBUF) {
+            staged = true;
+            if ((int)threadIdx.x < n) addv = __ldcg(add + r0 + threadIdx.x);
+        }
+    }
     for (int base = 0; base < na || base < nb_; base += B * DEC_CTHREADS) {
         float a[B], b[B];
 #pragma unroll
         for (int k = 0; k < B; k++) {
             const int j = base + k * DEC_CTHREADS + threadIdx.x;
             a[k] = 0.0f; b[k] = 0.0f;
-            if (j < na) a[k] = coherent_a ? __ldcg(ga + j) : __ldg(ga + j);
+            if (j < na) a[k] = __ldcg(ga + j);
             if (gb != nullptr && j < nb_) b[k] = __ldg(gb + j);
         }
 #pragma unroll
@@ -353,69 +368,49 @@ __device__ __forceinline__ void stage_vectors(const float* __restrict__ ga, floa
             if (gb != nullptr && j < nb_) sb[j] = b[k];
         }
     }
+    if (staged) S->add[threadIdx.x] = addv;
+    consumer_sync();
+    return staged;
+}
+__device__ __noinline__ bool stage_vectors(const float* ga, float* sa, int na, const float* gb, float* sb, int nb_,
+                                           const float* add, int kind, Shared* S) {
+    return stage_impl<4>(ga, sa, na, gb, sb, nb_, add, kind, S);
+}
+__device__ __noinline__ bool stage_long_vector(const float* ga, float* sa, int na, const float* add, int kind, Shared* S) {
+    return stage_impl<12>(ga, sa, na, nullptr, nullptr, 0, add, kind, S);
 }
 
-// Epilogue operand (bias or residual) of this CTA's rows: the load is issued early, into a
-// register, and parked in shared memory once the phase's other loads are on their way.
-// Returns whether the operand is staged (it is not when the CTA has more rows than threads).
-__device__ __forceinline__ bool add_load(const float* __restrict__ add, int M, float& v) {
-    v = 0.0f;
-    if (add == nullptr) return false;
-    int r0, r1;
-    cta_rows(M, r0, r1);
-    if (r1 - r0 > DEC_ROWBUF) return false;
-    if ((int)threadIdx.x < r1 - r0) v = __ldcg(add + r0 + threadIdx.x);
-    return true;
-}
-__device__ __forceinline__ void add_store(bool staged, float v, Shared* S) {
-    if (staged && threadIdx.x < DEC_ROWBUF) S->add[threadIdx.x] = v;
-}
-
-// sum of squares in the declared 256-lane order over a vector staged in shared memory
-__device__ __forceinline__ float cta_rms_sumsq(const float* sF, int N, Shared* S) {
-    const int t = threadIdx.x;
-    if (t < 256) {
-        float local = 0.0f;
-        for (int j = t; j < N; j += 256) local = __fmaf_rn(sF[j], sF[j], local);
-        S->sred[t] = local;
+// quant(rmsnorm(x) * w) (sW != NULL) or quant(x) (sW == NULL) of a vector staged in shared memory
+// into sXq / sXd.  The sum of squares follows the declared 256-lane order.
+__device__ __noinline__ void quant_from_smem(const float* sF, const float* sW, int N, float eps, int8_t* sXq,
+                                             __half* sXd, Shared* S) {
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    float inv = 1.0f;
+    if (sW != nullptr) {
+        if (t < 256) {
+            float local = 0.0f;
+            for (int j = t; j < N; j += 256) local = __fmaf_rn(sF[j], sF[j], local);
+            S->sred[t] = local;
+        }
+        consumer_sync();
+        if (t < 128) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 128]);
+        consumer_sync();
+        if (t < 64) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 64]);
+        consumer_sync();
+        if (t < 32) {
+            float v = __fadd_rn(S->sred[t], S->sred[t + 32]);
+            v = warp_tree_sum(v);
+            if (t == 0) S->sred[0] = v;
+        }
+        consumer_sync();
+        inv = rsqrtf(__fadd_rn(__fdiv_rn(S->sred[0], (float)N), eps));
     }
-    consumer_sync();
-    if (t < 128) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 128]);
-    consumer_sync();
-    if (t < 64) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 64]);
-    consumer_sync();
-    if (t < 32) {
-        float v = __fadd_rn(S->sred[t], S->sred[t + 32]);
-        v = warp_tree_sum(v);
-        if (t == 0) S->sred[0] = v;
-    }
-    consumer_sync();
-    return S->sred[0];
-}
-
-// sF holds x and sW the norm weight; writes quant(rmsnorm(x) * w) into sXq / sXd
-__device__ __forceinline__ void rms_quant_from_smem(const float* sF, const float* sW, int N, float eps, int8_t* sXq,
-                                                    __half* sXd, Shared* S) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float ss = cta_rms_sumsq(sF, N, S);
-    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)N), eps));
     for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
         const int j = b * 32 + lane;
-        float v = __fmul_rn(__fmul_rn(sF[j], inv), sW[j]);
+        float v = sF[j];
+        if (sW != nullptr) v = __fmul_rn(__fmul_rn(v, inv), sW[j]);
         __half dh;
         int q = quant_lane(v, &dh);
-        sXq[j] = (int8_t)q;
-        if (lane == 0) sXd[b] = dh;
-    }
-    consumer_sync();
-}
-
-__device__ __forceinline__ void quant_from_smem(const float* sF, int N, int8_t* sXq, __half* sXd) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
-        const int j = b * 32 + lane;
-        __half dh;
-        int q = quant_lane(sF[j], &dh);
         sXq[j] = (int8_t)q;
         if (lane == 0) sXd[b] = dh;
     }
@@ -594,8 +589,8 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
 }
 
 // ---------------------------------------------------------------- the kernel
-__global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_desc P, int nstages, int kmax,
-                                                                int fmax, int vcap, int uarea) {
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, int fmax, int vcap, int uarea) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     size_t off = (size_t)nstages * DEC_STAGE_STRIDE;
@@ -614,6 +609,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
+    const int E = P.E, F = P.F, nq = P.nh * P.hd, nqkv = nq + 2 * P.nkv * P.hd;
     if (tid == 0) {
         for (int s = 0; s < nstages; s++) {
             mbar_init(&S->full[s], 1);
@@ -622,6 +618,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
         S->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (tid < KIND_COUNT) {
+        const int Ms[KIND_COUNT] = {nqkv, E, F, E, P.V};
+        int a, b;
+        cta_rows(Ms[tid], a, b);
+        S->row0[tid] = a; S->row1[tid] = b;
     }
     __syncthreads();
 
@@ -633,21 +635,23 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
     // ------------------------------------------------------------ consumers
     const unsigned nctas = gridDim.x;
     unsigned epoch = 0, cnt = 0;
-    const int E = P.E, F = P.F, nq = P.nh * P.hd, nqkv = nq + 2 * P.nkv * P.hd;
     float bestv = -3.4e38f;
     int besti = 2147483647;
     float dummy_v = 0.0f;
     int dummy_i = 0;
     Tracer tr;
     tr.init(P);
-    tr.stamp();
+    tr.stamp(101);
 
-    // cache lengths of all layers (they only change by this kernel's own increment)
+    // descriptor of layer 0, and the cache lengths of all layers (they only change by this
+    // kernel's own increment)
+    constexpr int LY_WORDS = (int)(sizeof(lt_decode_layer) / 8);
+    if (tid < LY_WORDS) ((unsigned long long*)&S->ly[0])[tid] = ((const unsigned long long*)P.layers)[tid];
     if ((int)blockIdx.x < P.nh)
         for (int l = tid; l < P.n_layers; l += DEC_CTHREADS) S->lens[l] = __ldcg(P.layers[l].len);
 
     // x for layer 0: gathered from the Q8_0 table by the device token, or preloaded by the host
-    const lt_decode_layer* ly0 = P.layers;
+    bool staged;
     if (P.tok != nullptr) {
         int t = *P.tok;
         if (t < 0 || t >= P.V) {
@@ -655,35 +659,39 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
             t = t < 0 ? 0 : P.V - 1;
         }
         const int nbE = E >> 5;
+        const float* nw0 = P.layers[0].attn_norm;
         for (int j = tid; j < E; j += DEC_CTHREADS) {
             const __half dh = ((const __half*)P.emb_d)[(size_t)t * nbE + (j >> 5)];
             const int8_t q = P.emb_q[(size_t)t * E + j];
-            const float nw = __ldg(ly0->attn_norm + j);
+            const float nw = __ldg(nw0 + j);
             const float v = __fmul_rn(__half2float(dh), (float)q);
             sF[j] = v;
             sW[j] = nw;
             if (blockIdx.x == 0) P.x[j] = v;
         }
+        consumer_sync();
+        staged = stage_vectors(nullptr, nullptr, 0, nullptr, nullptr, 0, S->ly[0].qkv_bias, KIND_QKV, S);
     } else {
-        stage_vectors<4>(P.x, sF, E, true, ly0->attn_norm, sW, E);
+        consumer_sync();
+        staged = stage_vectors(P.x, sF, E, S->ly[0].attn_norm, sW, E, S->ly[0].qkv_bias, KIND_QKV, S);
     }
 
     for (int il = 0; il < P.n_layers; il++) {
-        const lt_decode_layer* ly = P.layers + il;
-        const int pbase = PH_PER_LAYER * il;
+        const lt_decode_layer* ly = &S->ly[il & 1];
+        // prefetch the next layer's descriptor (visible after the barriers of this layer)
+        if (il + 1 < P.n_layers && tid < LY_WORDS)
+            ((unsigned long long*)&S->ly[(il + 1) & 1])[tid] = ((const unsigned long long*)(P.layers + il + 1))[tid];
+        Epilogue ep;
         // P1: rmsnorm + quant -> q|k|v (+bias)
-        float addv;
-        bool staged = add_load(ly->qkv_bias, nqkv, addv);
-        if (il > 0) stage_vectors<4>(P.x, sF, E, true, ly->attn_norm, sW, E);
-        add_store(staged, addv, S);
-        consumer_sync();
-        rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-        tr.stamp();
-        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_QKV), ring, nstages, cnt, S, sXq, sXd, staged, ly->qkv_bias,
-                              P.qkv, dummy_v, dummy_i);
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
+        if (il > 0) staged = stage_vectors(P.x, sF, E, ly->attn_norm, sW, E, ly->qkv_bias, KIND_QKV, S);
+        tr.stamp(11);
+        quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
+        tr.stamp(102);
+        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = ly->qkv_bias; ep.out = P.qkv;
+        consume_gemv(P, layer_phase(P, ly, PH_QKV), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
+        tr.stamp(103);
+        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+        tr.stamp(104);
         // P2: rope + append + attention
         if ((int)blockIdx.x < P.nh) {
             const int pos = S->lens[il];
@@ -691,59 +699,54 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
             else if (P.hd == 128) attention_phase<32>(P, ly, pos, sAtt, vcap, S);
             else attention_phase<8>(P, ly, pos, sAtt, vcap, S);
         }
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
+        tr.stamp(105);
+        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+        tr.stamp(106);
         // P3: o_proj + residual; the cache length advances now that every head has read it
         if (blockIdx.x == 0 && tid == 0) {
             int p = __ldcg(ly->len);
             if (p >= 0 && p < P.max_seq) *ly->len = p + 1;
         }
-        staged = add_load(P.x, E, addv);
-        stage_vectors<4>(P.att, sF, nq, true, nullptr, nullptr, 0);
-        add_store(staged, addv, S);
-        consumer_sync();
-        quant_from_smem(sF, nq, sXq, sXd);
-        tr.stamp();
-        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_O), ring, nstages, cnt, S, sXq, sXd, staged, P.x, P.x1,
-                              dummy_v, dummy_i);
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
+        staged = stage_vectors(P.att, sF, nq, nullptr, nullptr, 0, P.x, KIND_O, S);
+        quant_from_smem(sF, nullptr, nq, 0.0f, sXq, sXd, S);
+        tr.stamp(107);
+        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = P.x; ep.out = P.x1;
+        consume_gemv(P, layer_phase(P, ly, PH_O), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
+        tr.stamp(108);
+        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+        tr.stamp(109);
         // P4: rmsnorm + quant -> gate rows, up rows, v = silu(gate) * up
-        stage_vectors<4>(P.x1, sF, E, true, ly->ffn_norm, sW, E);
+        stage_vectors(P.x1, sF, E, ly->ffn_norm, sW, E, nullptr, KIND_GU, S);
+        quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
+        tr.stamp(110);
+        ep.kind = EPI_GATE; ep.add_staged = false; ep.add_g = nullptr; ep.out = nullptr;
+        consume_gemv(P, layer_phase(P, ly, PH_GATE), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
         consumer_sync();
-        rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-        tr.stamp();
-        consume_gemv<EPI_GATE>(P, phase_desc(P, pbase + PH_GATE), ring, nstages, cnt, S, sXq, sXd, false, nullptr,
-                               nullptr, dummy_v, dummy_i);
-        consumer_sync();
-        consume_gemv<EPI_UP>(P, phase_desc(P, pbase + PH_UP), ring, nstages, cnt, S, sXq, sXd, false, nullptr, P.gu,
-                             dummy_v, dummy_i);
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
+        ep.kind = EPI_UP; ep.out = P.gu;
+        consume_gemv(P, layer_phase(P, ly, PH_UP), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
+        tr.stamp(111);
+        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+        tr.stamp(112);
         // P5: quant(v) -> down + residual
-        staged = add_load(P.x1, E, addv);
-        stage_vectors<12>(P.gu, sAtt, F, true, nullptr, nullptr, 0);
-        add_store(staged, addv, S);
-        consumer_sync();
-        quant_from_smem(sAtt, F, sXq, sXd);
-        tr.stamp();
-        consume_gemv<EPI_ADD>(P, phase_desc(P, pbase + PH_DOWN), ring, nstages, cnt, S, sXq, sXd, staged, P.x1, P.x,
-                              dummy_v, dummy_i);
-        tr.stamp();
-        grid_sync(P.sync, epoch, nctas, S, P.status);
-        tr.stamp();
+        staged = stage_long_vector(P.gu, sAtt, F, P.x1, KIND_DOWN, S);
+        quant_from_smem(sAtt, nullptr, F, 0.0f, sXq, sXd, S);
+        tr.stamp(113);
+        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = P.x1; ep.out = P.x;
+        consume_gemv(P, layer_phase(P, ly, PH_DOWN), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
+        tr.stamp(114);
+        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+        tr.stamp(115);
     }
     // LM head + argmax
-    stage_vectors<4>(P.x, sF, E, true, P.out_norm, sW, E);
-    consumer_sync();
-    rms_quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-    tr.stamp();
-    consume_gemv<EPI_LOGITS>(P, phase_desc(P, PH_PER_LAYER * P.n_layers), ring, nstages, cnt, S, sXq, sXd, false,
-                             nullptr, P.logits, bestv, besti);
-    tr.stamp();
+    stage_vectors(P.x, sF, E, P.out_norm, sW, E, nullptr, KIND_LM, S);
+    quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
+    tr.stamp(116);
+    {
+        Epilogue ep;
+        ep.kind = EPI_LOGITS; ep.add_staged = false; ep.add_g = nullptr; ep.out = P.logits;
+        consume_gemv(P, lm_phase(P), ep, ring, nstages, cnt, S, sXq, sXd, bestv, besti, tr);
+    }
+    tr.stamp(117);
     // lanes 0..DEC_ILP-1 of every warp hold candidates
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) {
@@ -764,7 +767,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
         P.part_val[blockIdx.x] = bv;
         P.part_idx[blockIdx.x] = bi;
     }
-    grid_sync(P.sync, epoch, nctas, S, P.status);
+    grid_sync(P.sync, epoch, nctas, S, P.status, tr);
     if (blockIdx.x == 0 && warp == 0) {
         const int lane = tid & 31;
         float bv = -3.4e38f;
@@ -790,7 +793,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(const lt_decode_
             }
         }
     }
-    tr.stamp();
+    tr.stamp(118);
     // the last CTA to get here resets the barrier counters for the next launch
     if (tid == 0) {
         __threadfence();

@@ -772,8 +772,8 @@ class FusedDecodeStep:
 
     def enable_trace(self):
         """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""
-        n = 16 * self.desc.n_layers + 8
-        self.trace = torch.zeros(2 * n, dtype=torch.int64, device="cuda")
+        n = 8192                     # (id, clock) pairs per traced CTA
+        self.trace = torch.zeros(2 * 2 * n, dtype=torch.int64, device="cuda")
         self.desc.trace = self.trace.data_ptr()
         return n
 
