@@ -130,7 +130,9 @@ int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out
  * quant -> down GEMV + residual; then final rmsnorm+quant -> LM-head GEMV -> argmax.  The
  * arithmetic of every op is the per-op entry point's, so results are bit-identical to the
  * chain of per-op launches.  One CTA per SM, cooperative launch, weights streamed through a
- * shared-memory ring by bulk async copies.  Capturable.
+ * shared-memory ring by bulk async copies; phases are chained through tagged activation words
+ * in the workspaces instead of grid barriers.  Capturable.  Launches that share workspaces must
+ * not overlap on the GPU.
  *
  * All pointers are device pointers.  Each Q8_0 matrix must have a scale count (rows*K/32)
  * that is a multiple of 8 and 16-byte aligned bases.  max_seq must be a multiple of 4. */
@@ -161,17 +163,20 @@ typedef struct lt_decode_desc {
     const uint16_t* lm_d;
     const int8_t* emb_q;       /* [V, E] embedding table (needed when tok != NULL) */
     const uint16_t* emb_d;
-    float* x;                  /* [E] residual stream; input row when tok == NULL */
-    float* x1;                 /* [E] */
-    float* qkv;                /* [(nh+2*nkv)*hd] */
-    float* att;                /* [nh*hd] */
-    float* gu;                 /* [2F] */
+    const float* x;            /* [E] input embedding row, read when tok == NULL (plain fp32, written by the host) */
+    void* ws_x;                /* tagged workspaces, 8 bytes per element {fp32 value, u32 tag}, zero before first use: [E] */
+    void* ws_x1;               /* [E] */
+    void* ws_qkv;              /* [(nh+2*nkv)*hd] */
+    void* ws_att;              /* [nh*hd] */
+    void* ws_v;                /* [F] silu(gate)*up */
     float* logits;             /* [V] */
     int* tok;                  /* device token: read at the start, overwritten with the argmax; NULL = x preloaded */
     int* out_tok;              /* argmax of the logits */
     int* history;              /* optional: history[*step] = token; *step += 1 */
     int* step;
     unsigned int* sync;        /* [2] grid-barrier counters, zero before the first launch */
+    unsigned int* epoch;       /* [1] token counter that stamps the workspaces, zero before the first launch;
+                                  advanced by every launch (wraps after 2^32/(n_layers+1) tokens) */
     float* part_val;           /* [lt_decode_num_ctas()] */
     int* part_idx;             /* [lt_decode_num_ctas()] */
     int* status;               /* device status word; NULL = the library's own */

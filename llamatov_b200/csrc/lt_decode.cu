@@ -3,12 +3,21 @@
 //
 // Why: at batch 1 a 0.5B model streams ~525 MB per token (80 us at HBM speed) but the step
 // is a chain of ~120 dependent phases; as separate launches each phase costs microseconds of
-// launch latency during which HBM idles.  Weights do not depend on activations, so here a
-// producer warp per CTA runs ahead of the chain and keeps a ring of shared-memory stages
-// filled with the weight rows this CTA will need next (bulk async copies, global -> shared,
-// completion on an mbarrier; no multicast), across phase and layer boundaries.  The consumer
-// warps wait at a grid barrier only for the small activation vectors, and every phase issues
-// all of its global loads at once before it computes.
+// launch latency during which HBM idles.  Two things are done about that here.
+//
+// (1) Weights do not depend on activations, so a producer warp per CTA runs ahead of the
+//     chain and keeps a ring of shared-memory stages filled with the weight rows this CTA
+//     will need next (bulk async copies global -> shared, completion on an mbarrier, no
+//     multicast), across phase and layer boundaries.
+// (2) The phases are chained by DATA, not by grid barriers.  Every activation element that
+//     crosses CTAs is stored as one 8-byte word {fp32 value, 32-bit tag}; the tag names the
+//     token and layer that produced it.  A consumer simply loads the vector it needs and
+//     retries the elements whose tag is not yet the expected one, so the cost of a phase
+//     boundary is one L2 round trip after the last producer's store, with no fence, no
+//     counter and no second round trip.  Value and tag travel in the same naturally aligned
+//     store, so they can never be seen apart.  Buffer reuse is safe without barriers because
+//     every rewrite of a buffer is separated from its last read by a full all-to-all phase
+//     (nobody can produce layer l+1's q|k|v before every CTA has finished layer l).
 //
 // Arithmetic is the per-op kernels' arithmetic, repeated verbatim (same device functions):
 //   P1  x -> rmsnorm(attn_norm) -> quant -> [q|k|v] GEMV + bias
@@ -20,8 +29,9 @@
 //   LM  rmsnorm(out_norm)(x) -> quant -> LM-head GEMV -> logits, argmax
 // so the step is bit-identical to the chain of per-op launches.
 //
-// Every wait (grid barrier, mbarrier) is bounded by a clock limit; on expiry the kernel sets
-// LT_STATUS_WAIT_TIMEOUT, stops waiting anywhere, drains its copies and returns.
+// Every wait (data tags, mbarriers, the one grid barrier before the argmax) is bounded by a
+// clock limit; on expiry the kernel sets LT_STATUS_WAIT_TIMEOUT, stops waiting anywhere,
+// drains its copies and returns.
 #include "lt_common.cuh"
 #include "lt_device_ops.cuh"
 
@@ -74,12 +84,28 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_CTHREADS) : "memory"); }
+// barrier of the consumer warps that also ANDs a predicate over them
+__device__ __forceinline__ bool consumer_all(bool pred) {
+    unsigned r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((unsigned)pred), "n"(DEC_CTHREADS)
+        : "memory");
+    return r != 0;
+}
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+
+// tagged activation element: {value, tag} in one 8-byte word
+__device__ __forceinline__ void st_tagged(float2* p, float v, unsigned tag) { __stcg(p, make_float2(v, __uint_as_float(tag))); }
 
 enum { KIND_QKV = 0, KIND_O = 1, KIND_GU = 2, KIND_DOWN = 3, KIND_LM = 4, KIND_COUNT = 5 };
 
@@ -88,7 +114,7 @@ struct Shared {
     unsigned long long empty[8];
     float sred[256];
     float red64[64];
-    float add[DEC_ROWBUF];      // epilogue operand (bias / residual) of this CTA's rows
+    float add[DEC_ROWBUF];      // bias of this CTA's q|k|v rows
     float gate[DEC_ROWBUF];     // gate results of this CTA's rows, until the up rows arrive
     int lens[DEC_MAX_LAYERS];   // cache lengths at kernel entry (attention CTAs)
     lt_decode_layer ly[2];      // descriptor of the current and of the next layer
@@ -98,22 +124,25 @@ struct Shared {
     volatile int abort_flag;
 };
 
-// bounded wait on an mbarrier phase; returns false (and raises the abort flag) on expiry
-__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
-    long long t0 = clock64();
-    unsigned spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if (S->abort_flag) return false;
-        if ((++spins & 1023u) == 0 && (*(volatile int*)status & (int)LT_STATUS_WAIT_TIMEOUT)) {
-            S->abort_flag = 1;      // another CTA gave up: do not wait for it
-            return false;
-        }
+__device__ __forceinline__ bool wait_expired(long long t0, unsigned& spins, Shared* S, int* status) {
+    if (S->abort_flag) return true;
+    if ((++spins & 63u) == 0) {
+        if (*(volatile int*)status & (int)LT_STATUS_WAIT_TIMEOUT) { S->abort_flag = 1; return true; }   // another CTA gave up
         if (clock64() - t0 > DEC_WAIT_CLOCKS) {
             S->abort_flag = 1;
             atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
-            return false;
+            return true;
         }
     }
+    return false;
+}
+
+// bounded wait on an mbarrier phase; returns false on expiry
+__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity))
+        if (wait_expired(t0, spins, S, status)) return false;
     return true;
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
@@ -138,32 +167,17 @@ struct Tracer {
     }
 };
 
-// Grid barrier for the consumer warps of all CTAs.  `epoch` counts barriers of this launch;
-// the counter is monotonic within a launch and reset by the last CTA to leave the kernel.
-__device__ __noinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsigned nctas, Shared* S, int* status,
-                                       Tracer& tr) {
+// The one grid barrier of the step (before the final argmax); counter reset by the last CTA to
+// leave the kernel.
+__device__ __forceinline__ void grid_sync_once(unsigned* ctr, unsigned nctas, Shared* S, int* status) {
     consumer_sync();
-    tr.stamp(90);
-    epoch += 1;
     if (threadIdx.x == 0 && !S->abort_flag) {
         __threadfence();
         atomicAdd(ctr, 1u);
-        tr.stamp(91);
-        const unsigned target = epoch * nctas;
-        long long t0 = clock64();
+        const long long t0 = clock64();
         unsigned spins = 0;
-        while (ld_acquire_u32(ctr) < target) {
-            if ((++spins & 255u) == 0 && (*(volatile int*)status & (int)LT_STATUS_WAIT_TIMEOUT)) {
-                S->abort_flag = 1;  // another CTA gave up: do not wait for it
-                break;
-            }
-            if (clock64() - t0 > DEC_WAIT_CLOCKS) {
-                S->abort_flag = 1;
-                atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
-                break;
-            }
-        }
-        __threadfence();
+        while (ld_acquire_u32(ctr) < nctas)
+            if (wait_expired(t0, spins, S, status)) break;
     }
     consumer_sync();
 }
@@ -172,33 +186,28 @@ __device__ __noinline__ void grid_sync(unsigned* ctr, unsigned& epoch, unsigned 
 // Five weight phases per layer (q|k|v, o, gate, up, down) and the LM head.  The gate and up
 // matrices are the two halves of the concatenated [2F, E] matrix; a CTA takes the same row
 // range of both halves.
-enum { PH_QKV = 0, PH_O = 1, PH_GATE = 2, PH_UP = 3, PH_DOWN = 4, PH_PER_LAYER = 5 };
+enum { PH_QKV = 0, PH_O = 1, PH_GATE = 2, PH_UP = 3, PH_DOWN = 4, PH_PER_LAYER = 5, PH_LM = 5 };
 
 struct GemvDesc {
     const int8_t* Wq;
     const __half* Wd;
-    int M, K, kind;
+    int K, kind;
 };
 
-__device__ __forceinline__ GemvDesc layer_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int ph) {
+__device__ __forceinline__ GemvDesc phase_desc(const lt_decode_desc& P, const lt_decode_layer* ly, int ph) {
     GemvDesc d;
-    const int nq = P.nh * P.hd, nk = P.nkv * P.hd;
     switch (ph) {
-        case PH_QKV: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.M = nq + 2 * nk; d.K = P.E; d.kind = KIND_QKV; break;
-        case PH_O: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.M = P.E; d.K = nq; d.kind = KIND_O; break;
-        case PH_GATE: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.M = P.F; d.K = P.E; d.kind = KIND_GU; break;
+        case PH_QKV: d.Wq = ly->qkv_q; d.Wd = (const __half*)ly->qkv_d; d.K = P.E; d.kind = KIND_QKV; break;
+        case PH_O: d.Wq = ly->o_q; d.Wd = (const __half*)ly->o_d; d.K = P.nh * P.hd; d.kind = KIND_O; break;
+        case PH_GATE: d.Wq = ly->gu_q; d.Wd = (const __half*)ly->gu_d; d.K = P.E; d.kind = KIND_GU; break;
         case PH_UP:
             d.Wq = ly->gu_q + (size_t)P.F * P.E;
             d.Wd = (const __half*)ly->gu_d + (size_t)P.F * (P.E >> 5);
-            d.M = P.F; d.K = P.E; d.kind = KIND_GU;
+            d.K = P.E; d.kind = KIND_GU;
             break;
-        default: d.Wq = ly->down_q; d.Wd = (const __half*)ly->down_d; d.M = P.E; d.K = P.F; d.kind = KIND_DOWN; break;
+        case PH_DOWN: d.Wq = ly->down_q; d.Wd = (const __half*)ly->down_d; d.K = P.F; d.kind = KIND_DOWN; break;
+        default: d.Wq = P.lm_q; d.Wd = (const __half*)P.lm_d; d.K = P.E; d.kind = KIND_LM; break;
     }
-    return d;
-}
-__device__ __forceinline__ GemvDesc lm_phase(const lt_decode_desc& P) {
-    GemvDesc d;
-    d.Wq = P.lm_q; d.Wd = (const __half*)P.lm_d; d.M = P.V; d.K = P.E; d.kind = KIND_LM;
     return d;
 }
 
@@ -214,176 +223,75 @@ __device__ __forceinline__ int rows_per_chunk(int K) {
 }
 
 // ---------------------------------------------------------------- producer
-__device__ __forceinline__ void produce_phase(const lt_decode_desc& P, const GemvDesc& d, unsigned char* ring,
-                                              int nstages, unsigned& cnt, Shared* S, bool& alive) {
-    const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
-    const int nb = d.K >> 5;
-    const int RC = rows_per_chunk(d.K);
-    for (int r = r0; r < r1 && alive; r += RC, cnt++) {
-        const int n = (r1 - r < RC) ? (r1 - r) : RC;
-        const unsigned stage = cnt % nstages;
-        if (cnt >= (unsigned)nstages) {
-            if (!mbar_wait(&S->empty[stage], ((cnt / nstages) - 1) & 1, S, P.status)) { alive = false; return; }
-        }
-        unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
-        const unsigned qbytes = (unsigned)n * d.K;
-        // the scale rows are fetched as the enclosing 16-byte aligned window
-        const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb));
-        const size_t d0 = a0 & ~(size_t)15;
-        const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
-        const unsigned dbytes = (unsigned)(d1 - d0);
-        mbar_expect_tx(&S->full[stage], qbytes + dbytes);
-        bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
-        bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
-    }
-}
-
 __device__ __noinline__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
     unsigned cnt = 0;
-    bool alive = true;
-    for (int il = 0; il < P.n_layers && alive; il++) {
-        const lt_decode_layer* ly = P.layers + il;      // read from global: the producer runs ahead of the consumers
-        for (int ph = 0; ph < PH_PER_LAYER && alive; ph++) produce_phase(P, layer_phase(P, ly, ph), ring, nstages, cnt, S, alive);
-    }
-    if (alive) produce_phase(P, lm_phase(P), ring, nstages, cnt, S, alive);
-}
-
-// ---------------------------------------------------------------- consumer: GEMV phase
-enum { EPI_ADD = 0, EPI_GATE = 1, EPI_UP = 2, EPI_LOGITS = 3 };
-
-struct Epilogue {
-    int kind;               // EPI_*
-    bool add_staged;        // operand in Shared::add
-    const float* add_g;     // operand in global memory (used when not staged), or NULL
-    float* out;
-};
-
-// One weight phase for this CTA's rows.  A warp folds up to DEC_ILP rows of a chunk together
-// (rows warp, warp+15, ... of the chunk): the block loop is outermost, so every row keeps its
-// own ascending-block fma chain and its own 5-level shuffle tree, while the chains of
-// different rows overlap in the pipeline.  Lane k then finishes row k.  One copy of this code
-// serves every phase (the epilogue is selected at run time) so that the whole step stays
-// resident in the instruction cache.
-__device__ __noinline__ void consume_gemv(const lt_decode_desc& P, const GemvDesc& d, const Epilogue& ep,
-                                          unsigned char* ring, int nstages, unsigned& cnt, Shared* S,
-                                          const int8_t* sXq, const __half* sXd, float& bestv, int& besti,
-                                          Tracer& tr) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
-    const int K = d.K, nb = K >> 5;
-    const int RC = rows_per_chunk(K);
-    tr.stamp(20);
-    for (int r = r0; r < r1; r += RC, cnt++) {
-        const int n = (r1 - r < RC) ? (r1 - r) : RC;
-        const unsigned stage = cnt % nstages;
-        const bool ok = mbar_wait(&S->full[stage], (cnt / nstages) & 1, S, P.status);
-        tr.stamp(21);
-        const unsigned char* base = ring + (size_t)stage * DEC_STAGE_STRIDE;
-        const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb)) & 15;
-        const __half* wdbase = (const __half*)(base + (size_t)n * K + doff);
-        const int nv = (n - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // rows of this chunk that are this warp's (<= DEC_ILP)
-        if (ok && nv > 0) {
-            float acc[DEC_ILP];
-#pragma unroll
-            for (int k = 0; k < DEC_ILP; k++) acc[k] = 0.0f;
-            for (int b = lane; b < nb; b += 32) {
-                const int4* xp = (const int4*)(sXq + b * 32);
-                const int4 x0 = xp[0], x1 = xp[1];
-                const float xd = __half2float(sXd[b]);
-#pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) {
-                    if (k < nv) {       // warp-uniform
-                        const int i = warp + k * DEC_CWARPS;
-                        const int4* wp = (const int4*)(base + (size_t)i * K + b * 32);
-                        const int4 w0 = wp[0], w1 = wp[1];
-                        const float wd = __half2float(wdbase[(size_t)i * nb + b]);
-                        acc[k] = q8_accum(wd, xd, block_dot(w0, w1, x0, x1), acc[k]);
-                    }
-                }
+    const int nphases = PH_PER_LAYER * P.n_layers + 1;
+    for (int idx = 0; idx < nphases; idx++) {
+        const int il = idx / PH_PER_LAYER;
+        const bool lm = (il >= P.n_layers);
+        // descriptors are read from global memory: the producer runs ahead of the consumers
+        const GemvDesc d = phase_desc(P, lm ? P.layers : P.layers + il, lm ? PH_LM : idx - il * PH_PER_LAYER);
+        const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
+        const int nb = d.K >> 5;
+        const int RC = rows_per_chunk(d.K);
+        for (int r = r0; r < r1; r += RC, cnt++) {
+            const int n = (r1 - r < RC) ? (r1 - r) : RC;
+            const unsigned stage = cnt % nstages;
+            if (cnt >= (unsigned)nstages) {
+                if (!mbar_wait(&S->empty[stage], ((cnt / nstages) - 1) & 1, S, P.status)) return;
             }
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) {
-#pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
-            }
-            float v = acc[0];
-#pragma unroll
-            for (int k = 1; k < DEC_ILP; k++) {
-                const float t = __shfl_sync(0xffffffffu, acc[k], 0);
-                if (lane == k) v = t;
-            }
-            if (lane < nv) {
-                const int row = r + warp + lane * DEC_CWARPS;
-                const int li = row - r0;
-                if (ep.kind == EPI_ADD) {
-                    if (ep.add_staged) v = __fadd_rn(v, S->add[li]);
-                    else if (ep.add_g != nullptr) v = __fadd_rn(v, __ldcg(ep.add_g + row));
-                    ep.out[row] = v;
-                } else if (ep.kind == EPI_GATE) {
-                    S->gate[li] = v;
-                } else if (ep.kind == EPI_UP) {
-                    ep.out[row] = silu_mul(S->gate[li], v);
-                } else {
-                    ep.out[row] = v;
-                    if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
-                }
-            }
+            unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
+            const unsigned qbytes = (unsigned)n * d.K;
+            // the scale rows are fetched as the enclosing 16-byte aligned window
+            const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb));
+            const size_t d0 = a0 & ~(size_t)15;
+            const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
+            const unsigned dbytes = (unsigned)(d1 - d0);
+            mbar_expect_tx(&S->full[stage], qbytes + dbytes);
+            bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
+            bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
         }
-        __syncwarp();
-        tr.stamp(22);
-        if (lane == 0) mbar_arrive(&S->empty[stage]);
     }
 }
 
-// ---------------------------------------------------------------- consumer: prologues
-// Copy up to two global vectors into shared memory with all loads in flight together, plus
-// (optionally) the epilogue operand of this CTA's rows.  `ga` was written by other CTAs during
-// this launch and bypasses L1; `gb` is a constant of the model.
-// Returns whether the epilogue operand was staged.
+// ---------------------------------------------------------------- consumer helpers
+// Load n tagged elements into shared memory (values only), retrying the ones whose tag is not
+// yet `want`.  All loads of a round are in flight together; one consumer barrier per round.
 template <int B>
-__device__ __forceinline__ bool stage_impl(const float* __restrict__ ga, float* sa, int na, const float* __restrict__ gb,
-                                           float* sb, int nb_, const float* __restrict__ add, int kind, Shared* S) {
-    float addv = 0.0f;
-    bool staged = false;
-    if (add != nullptr) {
-        const int r0 = S->row0[kind], n = S->row1[kind] - r0;
-        if (n <= DEC_ROWBUF) {
-            staged = true;
-            if ((int)threadIdx.x < n) addv = __ldcg(add + r0 + threadIdx.x);
-        }
-    }
-    for (int base = 0; base < na || base < nb_; base += B * DEC_CTHREADS) {
-        float a[B], b[B];
+__device__ __forceinline__ void wait_vector(const float2* __restrict__ g, float* s, int n, unsigned want, Shared* S,
+                                            int* status) {
+    float2 v[B];
+    bool have[B];
+#pragma unroll
+    for (int k = 0; k < B; k++) have[k] = (k * DEC_CTHREADS + (int)threadIdx.x >= n);
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    for (;;) {
+#pragma unroll
+        for (int k = 0; k < B; k++)
+            if (!have[k]) v[k] = __ldcg(g + k * DEC_CTHREADS + threadIdx.x);
+        bool ok = true;
 #pragma unroll
         for (int k = 0; k < B; k++) {
-            const int j = base + k * DEC_CTHREADS + threadIdx.x;
-            a[k] = 0.0f; b[k] = 0.0f;
-            if (j < na) a[k] = __ldcg(ga + j);
-            if (gb != nullptr && j < nb_) b[k] = __ldg(gb + j);
+            if (!have[k]) have[k] = (__float_as_uint(v[k].y) == want);
+            ok = ok && have[k];
         }
-#pragma unroll
-        for (int k = 0; k < B; k++) {
-            const int j = base + k * DEC_CTHREADS + threadIdx.x;
-            if (j < na) sa[j] = a[k];
-            if (gb != nullptr && j < nb_) sb[j] = b[k];
-        }
+        if (consumer_all(ok)) break;
+        if (threadIdx.x == 0) wait_expired(t0, spins, S, status);
+        if (S->abort_flag) break;
     }
-    if (staged) S->add[threadIdx.x] = addv;
-    consumer_sync();
-    return staged;
-}
-__device__ __noinline__ bool stage_vectors(const float* ga, float* sa, int na, const float* gb, float* sb, int nb_,
-                                           const float* add, int kind, Shared* S) {
-    return stage_impl<4>(ga, sa, na, gb, sb, nb_, add, kind, S);
-}
-__device__ __noinline__ bool stage_long_vector(const float* ga, float* sa, int na, const float* add, int kind, Shared* S) {
-    return stage_impl<12>(ga, sa, na, nullptr, nullptr, 0, add, kind, S);
+#pragma unroll
+    for (int k = 0; k < B; k++) {
+        const int j = k * DEC_CTHREADS + threadIdx.x;
+        if (j < n) s[j] = v[k].x;
+    }
 }
 
 // quant(rmsnorm(x) * w) (sW != NULL) or quant(x) (sW == NULL) of a vector staged in shared memory
-// into sXq / sXd.  The sum of squares follows the declared 256-lane order.
-__device__ __noinline__ void quant_from_smem(const float* sF, const float* sW, int N, float eps, int8_t* sXq,
-                                             __half* sXd, Shared* S) {
+// into sXq / sXd.  The sum of squares follows the declared 256-lane order.  Each warp quantises
+// up to four 32-blocks together so that their dependent chains overlap.
+__device__ __forceinline__ void quant_from_smem(const float* sF, const float* sW, int N, float eps, int8_t* sXq,
+                                                __half* sXd, Shared* S) {
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     float inv = 1.0f;
     if (sW != nullptr) {
@@ -405,26 +313,51 @@ __device__ __noinline__ void quant_from_smem(const float* sF, const float* sW, i
         consumer_sync();
         inv = rsqrtf(__fadd_rn(__fdiv_rn(S->sred[0], (float)N), eps));
     }
-    for (int b = warp; b < (N >> 5); b += DEC_CWARPS) {
-        const int j = b * 32 + lane;
-        float v = sF[j];
-        if (sW != nullptr) v = __fmul_rn(__fmul_rn(v, inv), sW[j]);
-        __half dh;
-        int q = quant_lane(v, &dh);
-        sXq[j] = (int8_t)q;
-        if (lane == 0) sXd[b] = dh;
+    const int nblk = N >> 5;
+    for (int b0 = warp; b0 < nblk; b0 += 4 * DEC_CWARPS) {
+        float v[4], a[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int b = b0 + k * DEC_CWARPS;
+            const int j = (b < nblk ? b : b0) * 32 + lane;
+            float x = sF[j];
+            if (sW != nullptr) x = __fmul_rn(__fmul_rn(x, inv), sW[j]);
+            v[k] = x;
+            a[k] = fabsf(x);
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float o = __shfl_xor_sync(0xffffffffu, a[k], s);
+                if (o > a[k]) a[k] = o;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int b = b0 + k * DEC_CWARPS;
+            if (b < nblk) {
+                const float d = (a[k] > 0.0f) ? __fdiv_rn(a[k], 127.0f) : 1.0f;
+                const __half dh = __float2half_rn(d);
+                const float dq = __half2float(dh);
+                int q = (int)rintf(__fdiv_rn(v[k], dq));
+                q = q < -127 ? -127 : (q > 127 ? 127 : q);
+                sXq[b * 32 + lane] = (int8_t)q;
+                if (lane == 0) sXd[b] = dh;
+            }
+        }
     }
     consumer_sync();
 }
 
 // ---------------------------------------------------------------- consumer: attention phase
 // One CTA per query head.  Every global load of the phase is issued before the first use:
-// the head's q / k / v slices, one K row per thread into registers, and all V rows into
-// shared memory by 16-byte asynchronous copies.
+// the head's q / k / v slices (tagged, produced by P1 of this layer), one K row per thread
+// into registers, and all V rows into shared memory by 16-byte asynchronous copies.
 // sAtt: [maxt] probabilities, hd (q) + hd (new k) + hd (new v) floats, then vcap V rows.
 template <int HD4>      // hd / 4
-__device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int pos, float* sAtt, int vcap,
-                                Shared* S) {
+__device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int pos,
+                                             unsigned tag, float* sAtt, int vcap, Shared* S) {
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
     const int hd = HD4 * 4, nh = P.nh, nkv = P.nkv, maxt = P.max_seq;
@@ -435,6 +368,7 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
     float* sKn = sQ + hd;
     float* sVn = sKn + hd;
     float* sV = sVn + hd;
+    const float2* qkv = (const float2*)P.ws_qkv;
 
     const bool room = (pos >= 0 && pos < maxt);
     if (!room) {
@@ -451,7 +385,7 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
             cp_async16(sV + (size_t)t * hd + c * 4, ly->vcache + ((size_t)t * nkv + hk) * hd + c * 4);
         }
     }
-    // (2) this thread's K row (t = tid) into registers; (3) the q / k / v slices of the new token
+    // (2) this thread's K row (t = tid) into registers
     constexpr int KB = HD4 > 16 ? 16 : HD4;     // float4s of the row held in registers
     float4 kreg[KB];
     const bool mine = (tid < Lc);
@@ -460,22 +394,39 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
 #pragma unroll
         for (int i = 0; i < KB; i++) kreg[i] = Krow[i];
     }
+    // (3) the q / k / v slices of the new token: three groups of hd/2 threads, two elements each
     const int half = hd >> 1;
-    float a1 = 0.0f, a2 = 0.0f;
     int role = -1, j = 0;
-    if (tid >= 256 && tid < 256 + half) { role = 0; j = tid - 256; a1 = __ldcg(P.qkv + h * hd + j); a2 = __ldcg(P.qkv + h * hd + j + half); }
-    else if (tid >= 320 && tid < 320 + half) { role = 1; j = tid - 320; a1 = __ldcg(P.qkv + nq + hk * hd + j); a2 = __ldcg(P.qkv + nq + hk * hd + j + half); }
-    else if (tid >= 384 && tid < 384 + half) { role = 2; j = tid - 384; a1 = __ldcg(P.qkv + nq + nk + hk * hd + j); a2 = __ldcg(P.qkv + nq + nk + hk * hd + j + half); }
+    const float2* src = qkv;
+    if (tid >= 256 && tid < 256 + half) { role = 0; j = tid - 256; src = qkv + h * hd; }
+    else if (tid >= 320 && tid < 320 + half) { role = 1; j = tid - 320; src = qkv + nq + hk * hd; }
+    else if (tid >= 384 && tid < 384 + half) { role = 2; j = tid - 384; src = qkv + nq + nk + hk * hd; }
+    float2 e1 = make_float2(0.0f, 0.0f), e2 = e1;
+    {
+        bool have = (role < 0);
+        const long long t0 = clock64();
+        unsigned spins = 0;
+        for (;;) {
+            if (!have) {
+                e1 = __ldcg(src + j);
+                e2 = __ldcg(src + j + half);
+                have = (__float_as_uint(e1.y) == tag) && (__float_as_uint(e2.y) == tag);
+            }
+            if (consumer_all(have)) break;
+            if (tid == 0) wait_expired(t0, spins, S, P.status);
+            if (S->abort_flag) break;
+        }
+    }
     if (role == 0) {
         float o1, o2;
-        rope_pair(a1, a2, j, hd, P.theta, pos, o1, o2);
+        rope_pair(e1.x, e2.x, j, hd, P.theta, pos, o1, o2);
         sQ[j] = o1; sQ[j + half] = o2;
     } else if (role == 1) {
         float o1, o2;
-        rope_pair(a1, a2, j, hd, P.theta, pos, o1, o2);
+        rope_pair(e1.x, e2.x, j, hd, P.theta, pos, o1, o2);
         sKn[j] = o1; sKn[j + half] = o2;
     } else if (role == 2) {
-        sVn[j] = a1; sVn[j + half] = a2;
+        sVn[j] = e1.x; sVn[j + half] = e2.x;
     }
     consumer_sync();
     if (room && tid < hd) {
@@ -583,14 +534,16 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
             for (; t < Lc; t++) acc = __fmaf_rn(sh[t], Vd[(size_t)t * stride], acc);
             if (room) acc = __fmaf_rn(sh[pos], sVn[tid], acc);
         }
-        P.att[h * hd + tid] = __fdiv_rn(acc, Z);
+        st_tagged((float2*)P.ws_att + h * hd + tid, __fdiv_rn(acc, Z), tag);
     }
     consumer_sync();
 }
 
 // ---------------------------------------------------------------- the kernel
+enum { EPI_QKV = 0, EPI_O = 1, EPI_GATE = 2, EPI_UP = 3, EPI_DOWN = 4, EPI_LOGITS = 5 };
+
 __global__ void __launch_bounds__(DEC_THREADS, 1)
-k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, int fmax, int vcap, int uarea) {
+k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, int fmax, int vcap) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     size_t off = (size_t)nstages * DEC_STAGE_STRIDE;
@@ -604,12 +557,13 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
     off += ((size_t)fmax * 4 + 127) & ~(size_t)127;
     float* sW = (float*)(smem + off);
     off += ((size_t)fmax * 4 + 127) & ~(size_t)127;
-    float* sAtt = (float*)(smem + off);      // attention area; doubles as the staging area of v in P5
-    (void)uarea;
+    float* sRes = (float*)(smem + off);       // residual rows of this CTA for the o_proj / down epilogues
+    off += (size_t)2 * DEC_ROWBUF * 4;
+    float* sAtt = (float*)(smem + off);       // attention area; doubles as the staging area of v in P5
 
     const int tid = threadIdx.x;
-    const int warp = tid >> 5;
-    const int E = P.E, F = P.F, nq = P.nh * P.hd, nqkv = nq + 2 * P.nkv * P.hd;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int E = P.E, F = P.F, nq = P.nh * P.hd, nqkv = nq + 2 * P.nkv * P.hd, L = P.n_layers;
     if (tid == 0) {
         for (int s = 0; s < nstages; s++) {
             mbar_init(&S->full[s], 1);
@@ -628,133 +582,226 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
     __syncthreads();
 
     if (warp == DEC_CWARPS) {       // producer warp: one lane streams weights for the whole step
-        if ((tid & 31) == 0) producer_loop(P, ring, nstages, S);
+        if (lane == 0) producer_loop(P, ring, nstages, S);
         return;
     }
 
     // ------------------------------------------------------------ consumers
     const unsigned nctas = gridDim.x;
-    unsigned epoch = 0, cnt = 0;
+    unsigned cnt = 0;
     float bestv = -3.4e38f;
     int besti = 2147483647;
-    float dummy_v = 0.0f;
-    int dummy_i = 0;
     Tracer tr;
     tr.init(P);
     tr.stamp(101);
+    // tags of this step: token counter * (L+1) + layer + 1
+    const unsigned tag0 = __ldcg(P.epoch) * (unsigned)(L + 1) + 1u;
 
-    // descriptor of layer 0, and the cache lengths of all layers (they only change by this
-    // kernel's own increment)
     constexpr int LY_WORDS = (int)(sizeof(lt_decode_layer) / 8);
     if (tid < LY_WORDS) ((unsigned long long*)&S->ly[0])[tid] = ((const unsigned long long*)P.layers)[tid];
     if ((int)blockIdx.x < P.nh)
-        for (int l = tid; l < P.n_layers; l += DEC_CTHREADS) S->lens[l] = __ldcg(P.layers[l].len);
+        for (int l = tid; l < L; l += DEC_CTHREADS) S->lens[l] = __ldcg(P.layers[l].len);
 
     // x for layer 0: gathered from the Q8_0 table by the device token, or preloaded by the host
-    bool staged;
-    if (P.tok != nullptr) {
-        int t = *P.tok;
-        if (t < 0 || t >= P.V) {
-            if (tid == 0 && blockIdx.x == 0) atomicOr(P.status, (int)LT_STATUS_BAD_TOKEN);
-            t = t < 0 ? 0 : P.V - 1;
-        }
-        const int nbE = E >> 5;
+    {
         const float* nw0 = P.layers[0].attn_norm;
-        for (int j = tid; j < E; j += DEC_CTHREADS) {
-            const __half dh = ((const __half*)P.emb_d)[(size_t)t * nbE + (j >> 5)];
-            const int8_t q = P.emb_q[(size_t)t * E + j];
-            const float nw = __ldg(nw0 + j);
-            const float v = __fmul_rn(__half2float(dh), (float)q);
-            sF[j] = v;
-            sW[j] = nw;
-            if (blockIdx.x == 0) P.x[j] = v;
+        if (P.tok != nullptr) {
+            int t = *P.tok;
+            if (t < 0 || t >= P.V) {
+                if (tid == 0 && blockIdx.x == 0) atomicOr(P.status, (int)LT_STATUS_BAD_TOKEN);
+                t = t < 0 ? 0 : P.V - 1;
+            }
+            const int nbE = E >> 5;
+            for (int j = tid; j < E; j += DEC_CTHREADS) {
+                const __half dh = ((const __half*)P.emb_d)[(size_t)t * nbE + (j >> 5)];
+                const int8_t q = P.emb_q[(size_t)t * E + j];
+                const float nw = __ldg(nw0 + j);
+                sF[j] = __fmul_rn(__half2float(dh), (float)q);
+                sW[j] = nw;
+            }
+        } else {
+            for (int j = tid; j < E; j += DEC_CTHREADS) {
+                const float xv = __ldcg(P.x + j);
+                const float nw = __ldg(nw0 + j);
+                sF[j] = xv;
+                sW[j] = nw;
+            }
         }
-        consumer_sync();
-        staged = stage_vectors(nullptr, nullptr, 0, nullptr, nullptr, 0, S->ly[0].qkv_bias, KIND_QKV, S);
-    } else {
-        consumer_sync();
-        staged = stage_vectors(P.x, sF, E, S->ly[0].attn_norm, sW, E, S->ly[0].qkv_bias, KIND_QKV, S);
+    }
+    consumer_sync();
+
+    const int nph = PH_PER_LAYER * L + 1;
+    for (int idx = 0; idx < nph; idx++) {
+        const int il = idx / PH_PER_LAYER;
+        const bool lm = (il >= L);
+        const int ph = lm ? PH_LM : idx - il * PH_PER_LAYER;
+        const lt_decode_layer* ly = &S->ly[il & 1];
+        const unsigned tag = tag0 + (unsigned)il;           // data produced in this layer
+        int epi = EPI_LOGITS;
+        // ---------------- prologue: fetch the activation, quantise it into sXq / sXd
+        if (ph == PH_QKV || ph == PH_LM) {
+            // prefetch the next layer's descriptor (visible after this phase's barriers)
+            if (!lm && il + 1 < L && tid < LY_WORDS)
+                ((unsigned long long*)&S->ly[(il + 1) & 1])[tid] = ((const unsigned long long*)(P.layers + il + 1))[tid];
+            const float* nw = lm ? P.out_norm : ly->attn_norm;
+            const float* bias = lm ? nullptr : ly->qkv_bias;
+            const int br0 = S->row0[KIND_QKV], bnr = S->row1[KIND_QKV] - br0;
+            if (il > 0) {
+                float nwv[4], bv = 0.0f;
+                if (bias != nullptr && tid < bnr) bv = __ldg(bias + br0 + tid);
+#pragma unroll
+                for (int k = 0; k < 4; k++) { const int j = k * DEC_CTHREADS + tid; nwv[k] = (j < E) ? __ldg(nw + j) : 0.0f; }
+                wait_vector<4>((const float2*)P.ws_x, sF, E, tag - 1u, S, P.status);
+#pragma unroll
+                for (int k = 0; k < 4; k++) { const int j = k * DEC_CTHREADS + tid; if (j < E) sW[j] = nwv[k]; }
+                if (bias != nullptr && tid < bnr) S->add[tid] = bv;
+            } else {
+                if (bias != nullptr && tid < bnr) S->add[tid] = __ldg(bias + br0 + tid);
+            }
+            consumer_sync();
+            if (!lm) {      // residual rows of x for the o_proj epilogue of this layer
+                const int r0 = S->row0[KIND_O], nr = S->row1[KIND_O] - r0;
+                if (tid < nr) sRes[tid] = sF[r0 + tid];
+            }
+            tr.stamp(11);
+            quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
+            epi = lm ? EPI_LOGITS : EPI_QKV;
+            tr.stamp(12);
+        } else if (ph == PH_O) {
+            // P2 first: rope + append + attention on the head CTAs
+            if ((int)blockIdx.x < P.nh) {
+                const int pos = S->lens[il];
+                if (P.hd == 64) attention_phase<16>(P, ly, pos, tag, sAtt, vcap, S);
+                else if (P.hd == 128) attention_phase<32>(P, ly, pos, tag, sAtt, vcap, S);
+                else attention_phase<8>(P, ly, pos, tag, sAtt, vcap, S);
+            }
+            tr.stamp(13);
+            // the cache length advances (every head works from the lengths read at kernel entry)
+            if (blockIdx.x == 0 && tid == 0) {
+                int p = __ldcg(ly->len);
+                if (p >= 0 && p < P.max_seq) *ly->len = p + 1;
+            }
+            wait_vector<4>((const float2*)P.ws_att, sF, nq, tag, S, P.status);
+            consumer_sync();
+            tr.stamp(14);
+            quant_from_smem(sF, nullptr, nq, 0.0f, sXq, sXd, S);
+            epi = EPI_O;
+            tr.stamp(15);
+        } else if (ph == PH_GATE) {
+            float nwv[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const int j = k * DEC_CTHREADS + tid; nwv[k] = (j < E) ? __ldg(ly->ffn_norm + j) : 0.0f; }
+            wait_vector<4>((const float2*)P.ws_x1, sF, E, tag, S, P.status);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const int j = k * DEC_CTHREADS + tid; if (j < E) sW[j] = nwv[k]; }
+            consumer_sync();
+            {               // residual rows of x1 for the down epilogue of this layer
+                const int r0 = S->row0[KIND_DOWN], nr = S->row1[KIND_DOWN] - r0;
+                if (tid < nr) sRes[DEC_ROWBUF + tid] = sF[r0 + tid];
+            }
+            tr.stamp(16);
+            quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
+            epi = EPI_GATE;
+            tr.stamp(17);
+        } else if (ph == PH_UP) {
+            consumer_sync();        // every gate value of this CTA is in shared memory
+            epi = EPI_UP;
+        } else {    // PH_DOWN
+            wait_vector<12>((const float2*)P.ws_v, sAtt, F, tag, S, P.status);
+            consumer_sync();
+            tr.stamp(18);
+            quant_from_smem(sAtt, nullptr, F, 0.0f, sXq, sXd, S);
+            epi = EPI_DOWN;
+            tr.stamp(19);
+        }
+
+        // ---------------- weight phase: fold this CTA's rows, one copy of the code for all phases
+        const GemvDesc d = phase_desc(P, ly, ph);
+        const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
+        const int K = d.K, nb = K >> 5;
+        const int RC = rows_per_chunk(K);
+        for (int r = r0; r < r1; r += RC, cnt++) {
+            const int n = (r1 - r < RC) ? (r1 - r) : RC;
+            const unsigned stage = cnt % nstages;
+            const bool ok = mbar_wait(&S->full[stage], (cnt / nstages) & 1, S, P.status);
+            tr.stamp(21);
+            const unsigned char* base = ring + (size_t)stage * DEC_STAGE_STRIDE;
+            const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb)) & 15;
+            const __half* wdbase = (const __half*)(base + (size_t)n * K + doff);
+            const int nv = (n - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // this warp's rows of the chunk (<= DEC_ILP)
+            if (ok && nv > 0) {
+                // A warp folds up to DEC_ILP rows together (rows warp, warp+15, ... of the chunk):
+                // the block loop is outermost, so each row keeps its own ascending-block fma chain
+                // and its own 5-level shuffle tree while the chains of different rows overlap.
+                float acc[DEC_ILP];
+#pragma unroll
+                for (int k = 0; k < DEC_ILP; k++) acc[k] = 0.0f;
+                for (int b = lane; b < nb; b += 32) {
+                    const int4* xp = (const int4*)(sXq + b * 32);
+                    const int4 x0 = xp[0], x1 = xp[1];
+                    const float xd = __half2float(sXd[b]);
+#pragma unroll
+                    for (int k = 0; k < DEC_ILP; k++) {
+                        if (k < nv) {       // warp-uniform
+                            const int i = warp + k * DEC_CWARPS;
+                            const int4* wp = (const int4*)(base + (size_t)i * K + b * 32);
+                            const int4 w0 = wp[0], w1 = wp[1];
+                            const float wd = __half2float(wdbase[(size_t)i * nb + b]);
+                            acc[k] = q8_accum(wd, xd, block_dot(w0, w1, x0, x1), acc[k]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+                    for (int k = 0; k < DEC_ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
+                }
+                float v = acc[0];       // lane k finishes row k
+#pragma unroll
+                for (int k = 1; k < DEC_ILP; k++) {
+                    const float t = __shfl_sync(0xffffffffu, acc[k], 0);
+                    if (lane == k) v = t;
+                }
+                if (lane < nv) {
+                    const int row = r + warp + lane * DEC_CWARPS;
+                    const int li = row - r0;
+                    switch (epi) {
+                        case EPI_QKV:
+                            if (ly->qkv_bias != nullptr) v = __fadd_rn(v, S->add[li]);
+                            st_tagged((float2*)P.ws_qkv + row, v, tag);
+                            break;
+                        case EPI_O:
+                            v = __fadd_rn(v, sRes[li]);
+                            st_tagged((float2*)P.ws_x1 + row, v, tag);
+                            break;
+                        case EPI_GATE: S->gate[li] = v; break;
+                        case EPI_UP: st_tagged((float2*)P.ws_v + row, silu_mul(S->gate[li], v), tag); break;
+                        case EPI_DOWN:
+                            v = __fadd_rn(v, sRes[DEC_ROWBUF + li]);
+                            st_tagged((float2*)P.ws_x + row, v, tag);
+                            break;
+                        default:
+                            P.logits[row] = v;
+                            if (v > bestv || (v == bestv && row < besti)) { bestv = v; besti = row; }
+                            break;
+                    }
+                }
+            }
+            __syncwarp();
+            tr.stamp(22);
+            if (lane == 0) mbar_arrive(&S->empty[stage]);
+        }
+        tr.stamp(30 + ph);
     }
 
-    for (int il = 0; il < P.n_layers; il++) {
-        const lt_decode_layer* ly = &S->ly[il & 1];
-        // prefetch the next layer's descriptor (visible after the barriers of this layer)
-        if (il + 1 < P.n_layers && tid < LY_WORDS)
-            ((unsigned long long*)&S->ly[(il + 1) & 1])[tid] = ((const unsigned long long*)(P.layers + il + 1))[tid];
-        Epilogue ep;
-        // P1: rmsnorm + quant -> q|k|v (+bias)
-        if (il > 0) staged = stage_vectors(P.x, sF, E, ly->attn_norm, sW, E, ly->qkv_bias, KIND_QKV, S);
-        tr.stamp(11);
-        quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-        tr.stamp(102);
-        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = ly->qkv_bias; ep.out = P.qkv;
-        consume_gemv(P, layer_phase(P, ly, PH_QKV), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
-        tr.stamp(103);
-        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
-        tr.stamp(104);
-        // P2: rope + append + attention
-        if ((int)blockIdx.x < P.nh) {
-            const int pos = S->lens[il];
-            if (P.hd == 64) attention_phase<16>(P, ly, pos, sAtt, vcap, S);
-            else if (P.hd == 128) attention_phase<32>(P, ly, pos, sAtt, vcap, S);
-            else attention_phase<8>(P, ly, pos, sAtt, vcap, S);
-        }
-        tr.stamp(105);
-        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
-        tr.stamp(106);
-        // P3: o_proj + residual; the cache length advances now that every head has read it
-        if (blockIdx.x == 0 && tid == 0) {
-            int p = __ldcg(ly->len);
-            if (p >= 0 && p < P.max_seq) *ly->len = p + 1;
-        }
-        staged = stage_vectors(P.att, sF, nq, nullptr, nullptr, 0, P.x, KIND_O, S);
-        quant_from_smem(sF, nullptr, nq, 0.0f, sXq, sXd, S);
-        tr.stamp(107);
-        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = P.x; ep.out = P.x1;
-        consume_gemv(P, layer_phase(P, ly, PH_O), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
-        tr.stamp(108);
-        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
-        tr.stamp(109);
-        // P4: rmsnorm + quant -> gate rows, up rows, v = silu(gate) * up
-        stage_vectors(P.x1, sF, E, ly->ffn_norm, sW, E, nullptr, KIND_GU, S);
-        quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-        tr.stamp(110);
-        ep.kind = EPI_GATE; ep.add_staged = false; ep.add_g = nullptr; ep.out = nullptr;
-        consume_gemv(P, layer_phase(P, ly, PH_GATE), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
-        consumer_sync();
-        ep.kind = EPI_UP; ep.out = P.gu;
-        consume_gemv(P, layer_phase(P, ly, PH_UP), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
-        tr.stamp(111);
-        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
-        tr.stamp(112);
-        // P5: quant(v) -> down + residual
-        staged = stage_long_vector(P.gu, sAtt, F, P.x1, KIND_DOWN, S);
-        quant_from_smem(sAtt, nullptr, F, 0.0f, sXq, sXd, S);
-        tr.stamp(113);
-        ep.kind = EPI_ADD; ep.add_staged = staged; ep.add_g = P.x1; ep.out = P.x;
-        consume_gemv(P, layer_phase(P, ly, PH_DOWN), ep, ring, nstages, cnt, S, sXq, sXd, dummy_v, dummy_i, tr);
-        tr.stamp(114);
-        grid_sync(P.sync, epoch, nctas, S, P.status, tr);
-        tr.stamp(115);
-    }
-    // LM head + argmax
-    stage_vectors(P.x, sF, E, P.out_norm, sW, E, nullptr, KIND_LM, S);
-    quant_from_smem(sF, sW, E, P.eps, sXq, sXd, S);
-    tr.stamp(116);
-    {
-        Epilogue ep;
-        ep.kind = EPI_LOGITS; ep.add_staged = false; ep.add_g = nullptr; ep.out = P.logits;
-        consume_gemv(P, lm_phase(P), ep, ring, nstages, cnt, S, sXq, sXd, bestv, besti, tr);
-    }
-    tr.stamp(117);
-    // lanes 0..DEC_ILP-1 of every warp hold candidates
+    // ---------------- argmax: lanes 0..DEC_ILP-1 of every warp hold candidates
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bestv, s);
         int oi = __shfl_xor_sync(0xffffffffu, besti, s);
         if (ov > bestv || (ov == bestv && oi < besti)) { bestv = ov; besti = oi; }
     }
-    if ((tid & 31) == 0) { S->best_v[warp] = bestv; S->best_i[warp] = besti; }
+    if (lane == 0) { S->best_v[warp] = bestv; S->best_i[warp] = besti; }
     consumer_sync();
     if (tid == 0) {
         float bv = S->best_v[0];
@@ -767,9 +814,8 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
         P.part_val[blockIdx.x] = bv;
         P.part_idx[blockIdx.x] = bi;
     }
-    grid_sync(P.sync, epoch, nctas, S, P.status, tr);
+    grid_sync_once(P.sync, nctas, S, P.status);
     if (blockIdx.x == 0 && warp == 0) {
-        const int lane = tid & 31;
         float bv = -3.4e38f;
         int bi = 2147483647;
         for (int c = lane; c < (int)nctas; c += 32) {
@@ -794,19 +840,20 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
         }
     }
     tr.stamp(118);
-    // the last CTA to get here resets the barrier counters for the next launch
+    // the last CTA to get here resets the barrier counters and advances the token counter
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(P.sync + 1, 1u) == nctas - 1) {
             P.sync[0] = 0;
             P.sync[1] = 0;
+            *P.epoch = *P.epoch + 1u;
             __threadfence();
         }
     }
 }
 
 struct DecodeGeometry {
-    int nstages, kmax, fmax, vcap, uarea;
+    int nstages, kmax, fmax, vcap;
     size_t smem;
     int ctas;
 };
@@ -822,7 +869,8 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
     g->fmax = d->E > nq ? d->E : nq;
     const size_t r128 = 127;
     size_t fixed = ((sizeof(Shared) + r128) & ~r128) + (((size_t)g->kmax + r128) & ~r128) +
-                   (((size_t)(g->kmax >> 5) * 2 + r128) & ~r128) + 2 * (((size_t)g->fmax * 4 + r128) & ~r128);
+                   (((size_t)(g->kmax >> 5) * 2 + r128) & ~r128) + 2 * (((size_t)g->fmax * 4 + r128) & ~r128) +
+                   (size_t)2 * DEC_ROWBUF * 4;
     const size_t att_fixed = ((size_t)d->max_seq + 3 * d->hd) * 4;
     const size_t vrow = (size_t)d->hd * 4;
     const size_t v_stage = (size_t)d->F * 4;      // P5 stages v in the attention area
@@ -840,12 +888,10 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
     size_t want = att_fixed + (size_t)d->max_seq * vrow;
     if (want < v_stage) want = v_stage;
     if (area > want) {
-        // spare room: deepen the ring
-        while (nst < 8 && area >= want + (size_t)DEC_STAGE_STRIDE) { nst++; area -= DEC_STAGE_STRIDE; }
+        while (nst < 8 && area >= want + (size_t)DEC_STAGE_STRIDE) { nst++; area -= DEC_STAGE_STRIDE; }   // spare room: deepen the ring
         area = want;
     }
     g->nstages = nst;
-    g->uarea = (int)area;
     g->vcap = area > att_fixed ? (int)((area - att_fixed) / vrow) : 0;
     if (g->vcap > d->max_seq) g->vcap = d->max_seq;
     g->smem = (size_t)nst * DEC_STAGE_STRIDE + fixed + area + 128;
@@ -859,13 +905,16 @@ using namespace lt;
 
 extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
     LT_REQUIRE(d != nullptr, "lt_decode_step: null descriptor");
-    LT_REQUIRE(d->layers && d->out_norm && d->lm_q && d->lm_d && d->x && d->x1 && d->qkv && d->att && d->gu &&
-                   d->logits && d->out_tok && d->sync && d->part_val && d->part_idx,
+    LT_REQUIRE(d->layers && d->out_norm && d->lm_q && d->lm_d && d->logits && d->out_tok && d->sync && d->epoch &&
+                   d->part_val && d->part_idx && d->ws_x && d->ws_x1 && d->ws_qkv && d->ws_att && d->ws_v,
                "lt_decode_step: null pointer in descriptor");
-    LT_REQUIRE(d->tok == nullptr || (d->emb_q && d->emb_d), "lt_decode_step: device token loop needs the embedding table");
+    LT_REQUIRE(d->tok != nullptr ? (d->emb_q && d->emb_d) : (d->x != nullptr),
+               "lt_decode_step: needs either a device token with the embedding table or a preloaded input row");
     LT_REQUIRE(d->n_layers > 0 && d->n_layers <= DEC_MAX_LAYERS && d->E > 0 && d->F > 0 && d->V > 0 && d->max_seq > 0,
                "lt_decode_step: bad dimensions");
     LT_REQUIRE(d->E % 32 == 0 && d->F % 32 == 0 && (d->nh * d->hd) % 32 == 0, "lt_decode_step: E, F and nh*hd must be multiples of 32");
+    LT_REQUIRE(d->E <= 4 * DEC_CTHREADS && d->nh * d->hd <= 4 * DEC_CTHREADS && d->F <= 12 * DEC_CTHREADS,
+               "lt_decode_step: this build handles E and nh*hd up to %d and F up to %d", 4 * DEC_CTHREADS, 12 * DEC_CTHREADS);
     LT_REQUIRE(d->hd == 32 || d->hd == 64 || d->hd == 128, "lt_decode_step: hd=%d must be 32, 64 or 128", d->hd);
     LT_REQUIRE(d->nkv > 0 && d->nh % d->nkv == 0, "lt_decode_step: nh must be a multiple of nkv");
     LT_REQUIRE(d->max_seq % 4 == 0, "lt_decode_step: max_seq=%d must be a multiple of 4", d->max_seq);
@@ -881,13 +930,15 @@ extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
     int rc = decode_geometry(d, &g);
     if (rc != LT_OK) return rc;
     LT_REQUIRE(d->nh <= g.ctas, "lt_decode_step: more query heads (%d) than SMs (%d)", d->nh, g.ctas);
+    const int widest = d->F > nq + 2 * nk ? d->F : nq + 2 * nk;
+    LT_REQUIRE(widest / g.ctas + 1 <= DEC_ROWBUF, "lt_decode_step: more rows per CTA than the epilogue buffers hold");
     LT_CUDA(cudaFuncSetAttribute(k_decode_step, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
     lt_decode_desc P = *d;
     if (P.status == nullptr) P.status = device_status_ptr();
     LT_REQUIRE(P.status != nullptr, "lt_decode_step: status word unavailable");
-    int nstages = g.nstages, kmax = g.kmax, fmax = g.fmax, vcap = g.vcap, uarea = g.uarea;
-    void* args[] = {&P, &nstages, &kmax, &fmax, &vcap, &uarea};
-    // cooperative launch: all CTAs are resident together, which the grid barrier relies on
+    int nstages = g.nstages, kmax = g.kmax, fmax = g.fmax, vcap = g.vcap;
+    void* args[] = {&P, &nstages, &kmax, &fmax, &vcap};
+    // cooperative launch: all CTAs are resident together, which the data-flow waits rely on
     LT_CUDA(cudaLaunchCooperativeKernel((const void*)k_decode_step, dim3(g.ctas), dim3(DEC_THREADS), args, g.smem,
                                         (cudaStream_t)stream));
     count_launches(1);

@@ -710,9 +710,9 @@ class _DecDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("n_layers", "E", "nh", "nkv", "hd", "F", "V", "max_seq")] + \
                [(n, ctypes.c_float) for n in ("eps", "theta", "scale")] + [("hist_cap", ctypes.c_int)] + \
                [(n, ctypes.c_void_p) for n in (
-                   "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "x1", "qkv", "att", "gu",
-                   "logits", "tok", "out_tok", "history", "step", "sync", "part_val", "part_idx", "status",
-                   "trace")]
+                   "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "ws_x", "ws_x1", "ws_qkv", "ws_att",
+                   "ws_v", "logits", "tok", "out_tok", "history", "step", "sync", "epoch", "part_val", "part_idx",
+                   "status", "trace")]
 
 
 class FusedDecodeStep:
@@ -752,9 +752,10 @@ class FusedDecodeStep:
         nq, nk = nh * hd, nkv * hd
         nct = _lib.lib().lt_decode_num_ctas()
         f32 = dict(dtype=torch.float32, device="cuda")
-        self.x1 = torch.zeros(E, **f32); self.qkv = torch.zeros(nq + 2 * nk, **f32)
-        self.att = torch.zeros(nq, **f32); self.gu = torch.zeros(2 * F, **f32)
+        # tagged workspaces: {value, tag} pairs, zero tags = "never written"
+        self.ws = [torch.zeros(2 * n, **f32) for n in (E, E, nq + 2 * nk, nq, F)]
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+        self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.part_val = torch.zeros(nct, **f32); self.part_idx = torch.zeros(nct, dtype=torch.int32, device="cuda")
         resid_in, _ = _ensure_resid(E)
         lbuf = _ensure_logits_buf(E, w)
@@ -764,10 +765,11 @@ class FusedDecodeStep:
                              float(np.float32(hd ** -0.5)), int(hist_cap),
                              self._layers_dev.data_ptr(), _addr(_dev_const(_np(w["output_norm.weight"]))),
                              _addr(lq), _addr(ld), None if eq is None else _addr(eq), None if ed is None else _addr(ed),
-                             _addr(resid_in.ptr), self.x1.data_ptr(), self.qkv.data_ptr(), self.att.data_ptr(),
-                             self.gu.data_ptr(), _addr(lbuf.ptr), None if tok_ptr is None else int(tok_ptr),
-                             _addr(out_tok), None if history is None else int(history),
-                             None if step is None else int(step), self.sync.data_ptr(), self.part_val.data_ptr(),
+                             _addr(resid_in.ptr), self.ws[0].data_ptr(), self.ws[1].data_ptr(),
+                             self.ws[2].data_ptr(), self.ws[3].data_ptr(), self.ws[4].data_ptr(), _addr(lbuf.ptr),
+                             None if tok_ptr is None else int(tok_ptr), _addr(out_tok),
+                             None if history is None else int(history), None if step is None else int(step),
+                             self.sync.data_ptr(), self.epoch.data_ptr(), self.part_val.data_ptr(),
                              self.part_idx.data_ptr(), None, None)
 
     def enable_trace(self):
