@@ -119,6 +119,7 @@ struct Shared {
     int lens[DEC_MAX_LAYERS];   // cache lengths at kernel entry (attention CTAs)
     lt_decode_layer ly[2];      // descriptor of the current and of the next layer
     int row0[KIND_COUNT], row1[KIND_COUNT];   // this CTA's row range per matrix kind
+    int rc[KIND_COUNT];                        // rows per ring stage per matrix kind
     float best_v[DEC_CWARPS];
     int best_i[DEC_CWARPS];
     volatile int abort_flag;
@@ -223,22 +224,21 @@ __device__ __forceinline__ int rows_per_chunk(int K) {
 }
 
 // ---------------------------------------------------------------- producer
-__device__ __noinline__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
-    unsigned cnt = 0;
-    const int nphases = PH_PER_LAYER * P.n_layers + 1;
-    for (int idx = 0; idx < nphases; idx++) {
-        const int il = idx / PH_PER_LAYER;
-        const bool lm = (il >= P.n_layers);
+__device__ __forceinline__ void producer_loop(const lt_decode_desc& P, unsigned char* ring, int nstages, Shared* S) {
+    int stage = 0;
+    unsigned fill = 0;          // how many times the ring has wrapped
+    for (int il = 0; il <= P.n_layers; il++) {
+      const bool lm = (il == P.n_layers);
+      for (int ph = lm ? PH_LM : 0; ph < (lm ? PH_LM + 1 : PH_PER_LAYER); ph++) {
         // descriptors are read from global memory: the producer runs ahead of the consumers
-        const GemvDesc d = phase_desc(P, lm ? P.layers : P.layers + il, lm ? PH_LM : idx - il * PH_PER_LAYER);
+        const GemvDesc d = phase_desc(P, lm ? P.layers : P.layers + il, ph);
         const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
         const int nb = d.K >> 5;
-        const int RC = rows_per_chunk(d.K);
-        for (int r = r0; r < r1; r += RC, cnt++) {
+        const int RC = S->rc[d.kind];
+        for (int r = r0; r < r1; r += RC) {
             const int n = (r1 - r < RC) ? (r1 - r) : RC;
-            const unsigned stage = cnt % nstages;
-            if (cnt >= (unsigned)nstages) {
-                if (!mbar_wait(&S->empty[stage], ((cnt / nstages) - 1) & 1, S, P.status)) return;
+            if (fill > 0) {
+                if (!mbar_wait(&S->empty[stage], (fill - 1) & 1, S, P.status)) return;
             }
             unsigned char* dst = ring + (size_t)stage * DEC_STAGE_STRIDE;
             const unsigned qbytes = (unsigned)n * d.K;
@@ -250,7 +250,9 @@ __device__ __noinline__ void producer_loop(const lt_decode_desc& P, unsigned cha
             mbar_expect_tx(&S->full[stage], qbytes + dbytes);
             bulk_g2s(dst, d.Wq + (size_t)r * d.K, qbytes, &S->full[stage]);
             bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &S->full[stage]);
+            if (++stage == nstages) { stage = 0; fill++; }
         }
+      }
     }
 }
 
@@ -325,14 +327,10 @@ __device__ __forceinline__ void quant_from_smem(const float* sF, const float* sW
             v[k] = x;
             a[k] = fabsf(x);
         }
+        // amax over the 32 lanes: the bit patterns of non-negative floats order like unsigned
+        // integers, so one integer max-reduction gives the same maximum as a compare tree
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) {
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const float o = __shfl_xor_sync(0xffffffffu, a[k], s);
-                if (o > a[k]) a[k] = o;
-            }
-        }
+        for (int k = 0; k < 4; k++) a[k] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(a[k])));
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const int b = b0 + k * DEC_CWARPS;
@@ -352,22 +350,25 @@ __device__ __forceinline__ void quant_from_smem(const float* sF, const float* sW
 
 // ---------------------------------------------------------------- consumer: attention phase
 // One CTA per query head.  Every global load of the phase is issued before the first use:
-// the head's q / k / v slices (tagged, produced by P1 of this layer), one K row per thread
-// into registers, and all V rows into shared memory by 16-byte asynchronous copies.
-// sAtt: [maxt] probabilities, hd (q) + hd (new k) + hd (new v) floats, then vcap V rows.
-template <int HD4>      // hd / 4
-__device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int pos,
-                                             unsigned tag, float* sAtt, int vcap, Shared* S) {
+// all cached K and V rows of the head's KV group go to shared memory by 16-byte asynchronous
+// copies (no registers), then the head's q / k / v slices (tagged, produced by P1 of this
+// layer) are awaited.  K rows are padded by 4 floats so that one-row-per-thread reads do not
+// collide on banks.
+// sAtt: [maxt] probabilities, hd (q) + hd (new k) + hd (new v) floats, vcap V rows, vcap K rows.
+__device__ __forceinline__ void attention_phase(const lt_decode_desc& P, const lt_decode_layer* ly, int pos,
+                                                unsigned tag, float* sAtt, int vcap, Shared* S) {
     const int h = blockIdx.x;
     const int tid = threadIdx.x;
-    const int hd = HD4 * 4, nh = P.nh, nkv = P.nkv, maxt = P.max_seq;
+    const int hd = P.hd, hd4 = hd >> 2, nh = P.nh, nkv = P.nkv, maxt = P.max_seq;
     const int nq = nh * hd, nk = nkv * hd;
     const int rep = nh / nkv, hk = h / rep;
+    const int kst = hd + 4;                  // padded K row stride in floats
     float* sh = sAtt;
     float* sQ = sAtt + maxt;
     float* sKn = sQ + hd;
     float* sVn = sKn + hd;
     float* sV = sVn + hd;
+    float* sK = sV + (size_t)vcap * hd;
     const float2* qkv = (const float2*)P.ws_qkv;
 
     const bool room = (pos >= 0 && pos < maxt);
@@ -378,23 +379,16 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
     const int L = room ? pos + 1 : pos;      // attention length after the append
     const int Lc = room ? pos : L;           // rows that already live in the cache
     const bool staged = (L <= vcap);
-    // (1) V rows of the cache -> shared memory, asynchronously
+    // (1) cached K and V rows -> shared memory, asynchronously
     if (staged) {
-        for (int e = tid; e < Lc * HD4; e += DEC_CTHREADS) {
-            const int t = e / HD4, c = e - t * HD4;
-            cp_async16(sV + (size_t)t * hd + c * 4, ly->vcache + ((size_t)t * nkv + hk) * hd + c * 4);
+        for (int e = tid; e < Lc * hd4; e += DEC_CTHREADS) {
+            const int t = e / hd4, c = e - t * hd4;
+            const size_t g = ((size_t)t * nkv + hk) * hd + c * 4;
+            cp_async16(sK + (size_t)t * kst + c * 4, ly->kcache + g);
+            cp_async16(sV + (size_t)t * hd + c * 4, ly->vcache + g);
         }
     }
-    // (2) this thread's K row (t = tid) into registers
-    constexpr int KB = HD4 > 16 ? 16 : HD4;     // float4s of the row held in registers
-    float4 kreg[KB];
-    const bool mine = (tid < Lc);
-    const float4* Krow = (const float4*)(ly->kcache + ((size_t)(mine ? tid : 0) * nkv + hk) * hd);
-    if (mine) {
-#pragma unroll
-        for (int i = 0; i < KB; i++) kreg[i] = Krow[i];
-    }
-    // (3) the q / k / v slices of the new token: three groups of hd/2 threads, two elements each
+    // (2) the q / k / v slices of the new token: three groups of hd/2 threads, two elements each
     const int half = hd >> 1;
     int role = -1, j = 0;
     const float2* src = qkv;
@@ -425,54 +419,28 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
         float o1, o2;
         rope_pair(e1.x, e2.x, j, hd, P.theta, pos, o1, o2);
         sKn[j] = o1; sKn[j + half] = o2;
+        if (room && staged) { sK[(size_t)pos * kst + j] = o1; sK[(size_t)pos * kst + j + half] = o2; }
     } else if (role == 2) {
         sVn[j] = e1.x; sVn[j + half] = e2.x;
+        if (room && staged) { sV[(size_t)pos * hd + j] = e1.x; sV[(size_t)pos * hd + j + half] = e2.x; }
     }
+    cp_async_wait_all();
     consumer_sync();
-    if (room && tid < hd) {
-        if ((h % rep) == 0) {
-            ly->kcache[((size_t)pos * nkv + hk) * hd + tid] = sKn[tid];
-            ly->vcache[((size_t)pos * nkv + hk) * hd + tid] = sVn[tid];
-        }
-        if (staged) sV[(size_t)pos * hd + tid] = sVn[tid];
+    if (room && (h % rep) == 0 && tid < hd) {
+        ly->kcache[((size_t)pos * nkv + hk) * hd + tid] = sKn[tid];
+        ly->vcache[((size_t)pos * nkv + hk) * hd + tid] = sVn[tid];
     }
-    // scores: thread t owns position t (positions beyond the thread count loop below)
-    {
-        float v = -1e30f;
-        if (tid < L) {
-            const float4* q4 = (const float4*)sQ;
-            const float4* kn4 = (const float4*)sKn;
-            float s = 0.0f;
-#pragma unroll
-            for (int i = 0; i < KB; i++) {
-                const float4 kk = mine ? kreg[i] : kn4[i];
-                const float4 qq = q4[i];
-                s = __fmaf_rn(qq.x, kk.x, s);
-                s = __fmaf_rn(qq.y, kk.y, s);
-                s = __fmaf_rn(qq.z, kk.z, s);
-                s = __fmaf_rn(qq.w, kk.w, s);
-            }
-#pragma unroll
-            for (int i = KB; i < HD4; i++) {      // rows longer than the register window: second fetch
-                const float4 kk = mine ? Krow[i] : kn4[i];
-                const float4 qq = q4[i];
-                s = __fmaf_rn(qq.x, kk.x, s);
-                s = __fmaf_rn(qq.y, kk.y, s);
-                s = __fmaf_rn(qq.z, kk.z, s);
-                s = __fmaf_rn(qq.w, kk.w, s);
-            }
-            v = __fmul_rn(s, P.scale);
-        }
-        if (tid < maxt) sh[tid] = v;
-    }
-    for (int t = tid + DEC_CTHREADS; t < maxt; t += DEC_CTHREADS) {
+    // scores: thread t owns positions t, t + 480, ...
+    for (int t = tid; t < maxt; t += DEC_CTHREADS) {
         float v = -1e30f;
         if (t < L) {
-            const float4* K4 = (room && t == pos) ? (const float4*)sKn : (const float4*)(ly->kcache + ((size_t)t * nkv + hk) * hd);
+            const float4* K4 = staged ? (const float4*)(sK + (size_t)t * kst)
+                                      : ((room && t == pos) ? (const float4*)sKn
+                                                            : (const float4*)(ly->kcache + ((size_t)t * nkv + hk) * hd));
             const float4* q4 = (const float4*)sQ;
             float s = 0.0f;
-#pragma unroll
-            for (int i = 0; i < HD4; i++) {
+#pragma unroll 4
+            for (int i = 0; i < hd4; i++) {
                 const float4 kk = K4[i];
                 const float4 qq = q4[i];
                 s = __fmaf_rn(qq.x, kk.x, s);
@@ -507,7 +475,6 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
         for (int t = tid; t < maxt; t += 64) ls = __fadd_rn(ls, sh[t]);
         S->red64[tid] = ls;
     }
-    cp_async_wait_all();
     consumer_sync();
     if (tid < 32) {
         float v = __fadd_rn(S->red64[tid], S->red64[tid + 32]);
@@ -519,6 +486,7 @@ __device__ __noinline__ void attention_phase(const lt_decode_desc& P, const lt_d
     if (tid < hd) {
         float acc = 0.0f;
         if (staged) {
+#pragma unroll 4
             for (int t = 0; t < L; t++) acc = __fmaf_rn(sh[t], sV[(size_t)t * hd + tid], acc);
         } else {
             const float* Vd = ly->vcache + (size_t)hk * hd + tid;
@@ -574,10 +542,12 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (tid < KIND_COUNT) {
-        const int Ms[KIND_COUNT] = {nqkv, E, F, E, P.V};
+        const int M = tid == KIND_QKV ? nqkv : (tid == KIND_GU ? F : (tid == KIND_LM ? P.V : E));
+        const int Kk = tid == KIND_O ? nq : (tid == KIND_DOWN ? F : E);
         int a, b;
-        cta_rows(Ms[tid], a, b);
+        cta_rows(M, a, b);
         S->row0[tid] = a; S->row1[tid] = b;
+        S->rc[tid] = rows_per_chunk(Kk);
     }
     __syncthreads();
 
@@ -588,7 +558,8 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
 
     // ------------------------------------------------------------ consumers
     const unsigned nctas = gridDim.x;
-    unsigned cnt = 0;
+    int stage = 0;
+    unsigned fill = 0;
     float bestv = -3.4e38f;
     int besti = 2147483647;
     Tracer tr;
@@ -631,10 +602,11 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
     consumer_sync();
 
     const int nph = PH_PER_LAYER * L + 1;
-    for (int idx = 0; idx < nph; idx++) {
-        const int il = idx / PH_PER_LAYER;
+    int il = 0, ph = 0;
+    for (int idx = 0; idx < nph; idx++, ph++) {
+        if (ph == PH_PER_LAYER && il < L) { ph = 0; il++; }
         const bool lm = (il >= L);
-        const int ph = lm ? PH_LM : idx - il * PH_PER_LAYER;
+        if (lm) ph = PH_LM;
         const lt_decode_layer* ly = &S->ly[il & 1];
         const unsigned tag = tag0 + (unsigned)il;           // data produced in this layer
         int epi = EPI_LOGITS;
@@ -670,10 +642,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
         } else if (ph == PH_O) {
             // P2 first: rope + append + attention on the head CTAs
             if ((int)blockIdx.x < P.nh) {
-                const int pos = S->lens[il];
-                if (P.hd == 64) attention_phase<16>(P, ly, pos, tag, sAtt, vcap, S);
-                else if (P.hd == 128) attention_phase<32>(P, ly, pos, tag, sAtt, vcap, S);
-                else attention_phase<8>(P, ly, pos, tag, sAtt, vcap, S);
+                attention_phase(P, ly, S->lens[il], tag, sAtt, vcap, S);
             }
             tr.stamp(13);
             // the cache length advances (every head works from the lengths read at kernel entry)
@@ -719,11 +688,10 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
         const GemvDesc d = phase_desc(P, ly, ph);
         const int r0 = S->row0[d.kind], r1 = S->row1[d.kind];
         const int K = d.K, nb = K >> 5;
-        const int RC = rows_per_chunk(K);
-        for (int r = r0; r < r1; r += RC, cnt++) {
+        const int RC = S->rc[d.kind];
+        for (int r = r0; r < r1; r += RC) {
             const int n = (r1 - r < RC) ? (r1 - r) : RC;
-            const unsigned stage = cnt % nstages;
-            const bool ok = mbar_wait(&S->full[stage], (cnt / nstages) & 1, S, P.status);
+            const bool ok = mbar_wait(&S->full[stage], fill & 1, S, P.status);
             tr.stamp(21);
             const unsigned char* base = ring + (size_t)stage * DEC_STAGE_STRIDE;
             const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(d.Wd + (size_t)r * nb)) & 15;
@@ -790,6 +758,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int kmax, i
             __syncwarp();
             tr.stamp(22);
             if (lane == 0) mbar_arrive(&S->empty[stage]);
+            if (++stage == nstages) { stage = 0; fill++; }
         }
         tr.stamp(30 + ph);
     }
@@ -872,7 +841,7 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
                    (((size_t)(g->kmax >> 5) * 2 + r128) & ~r128) + 2 * (((size_t)g->fmax * 4 + r128) & ~r128) +
                    (size_t)2 * DEC_ROWBUF * 4;
     const size_t att_fixed = ((size_t)d->max_seq + 3 * d->hd) * 4;
-    const size_t vrow = (size_t)d->hd * 4;
+    const size_t vrow = (size_t)d->hd * 4 + (size_t)(d->hd + 4) * 4;     // one staged V row + one padded K row
     const size_t v_stage = (size_t)d->F * 4;      // P5 stages v in the attention area
     const size_t avail = (size_t)smem_max - 1024;
     const size_t min_area = att_fixed > v_stage ? att_fixed : v_stage;
@@ -880,9 +849,10 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
         set_error("lt_decode_step: model dimensions need more shared memory than one SM has");
         return LT_ERR_UNSUPPORTED;
     }
-    // ring first (up to 4 stages), then as many staged V rows as fit (up to max_seq)
+    // ring first (3 stages, fewer only if the model leaves no room), then as many staged K/V
+    // rows as fit (up to max_seq), then a deeper ring if room is left
     size_t left = avail - fixed;
-    int nst = 4;
+    int nst = 3;
     while (nst > 2 && (size_t)nst * DEC_STAGE_STRIDE + min_area > left) nst--;
     size_t area = left - (size_t)nst * DEC_STAGE_STRIDE;
     size_t want = att_fixed + (size_t)d->max_seq * vrow;
