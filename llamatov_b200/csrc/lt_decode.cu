@@ -258,7 +258,8 @@ __device__ __forceinline__ void producer_loop(const lt_decode_desc& P, unsigned 
 
 // ---------------------------------------------------------------- consumer helpers
 // Load n tagged elements into shared memory (values only), retrying the ones whose tag is not
-// yet `want`.  All loads of a round are in flight together; one consumer barrier per round.
+// yet `want`.  All loads of a round are in flight together; every warp polls at its own pace
+// (no block barrier per round); the caller synchronises the consumers afterwards.
 template <int B>
 __device__ __forceinline__ void wait_vector(const float2* __restrict__ g, float* s, int n, unsigned want, Shared* S,
                                             int* status) {
@@ -278,9 +279,8 @@ __device__ __forceinline__ void wait_vector(const float2* __restrict__ g, float*
             if (!have[k]) have[k] = (__float_as_uint(v[k].y) == want);
             ok = ok && have[k];
         }
-        if (consumer_all(ok)) break;
-        if (threadIdx.x == 0) wait_expired(t0, spins, S, status);
-        if (S->abort_flag) break;
+        if (__all_sync(0xffffffffu, ok)) break;
+        if (wait_expired(t0, spins, S, status)) break;
     }
 #pragma unroll
     for (int k = 0; k < B; k++) {
@@ -303,17 +303,17 @@ __device__ __forceinline__ void quant_from_smem(const float* sF, const float* sW
             S->sred[t] = local;
         }
         consumer_sync();
-        if (t < 128) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 128]);
-        consumer_sync();
-        if (t < 64) S->sred[t] = __fadd_rn(S->sred[t], S->sred[t + 64]);
-        consumer_sync();
         if (t < 32) {
-            float v = __fadd_rn(S->sred[t], S->sred[t + 32]);
-            v = warp_tree_sum(v);
-            if (t == 0) S->sred[0] = v;
+            // levels 128, 64, 32 of the pairwise tree for lane t, in the declared pairing:
+            // p[t] += p[t+128]; p[t] += p[t+64]; p[t] += p[t+32]
+            const float* p = S->sred;
+            const float a = __fadd_rn(__fadd_rn(p[t], p[t + 128]), __fadd_rn(p[t + 64], p[t + 192]));
+            const float b = __fadd_rn(__fadd_rn(p[t + 32], p[t + 160]), __fadd_rn(p[t + 96], p[t + 224]));
+            float v = warp_tree_sum(__fadd_rn(a, b));      // levels 16 .. 1
+            if (t == 0) S->red64[0] = v;
         }
         consumer_sync();
-        inv = rsqrtf(__fadd_rn(__fdiv_rn(S->sred[0], (float)N), eps));
+        inv = rsqrtf(__fadd_rn(__fdiv_rn(S->red64[0], (float)N), eps));
     }
     const int nblk = N >> 5;
     for (int b0 = warp; b0 < nblk; b0 += 4 * DEC_CWARPS) {
@@ -406,9 +406,8 @@ __device__ __forceinline__ void attention_phase(const lt_decode_desc& P, const l
                 e2 = __ldcg(src + j + half);
                 have = (__float_as_uint(e1.y) == tag) && (__float_as_uint(e2.y) == tag);
             }
-            if (consumer_all(have)) break;
-            if (tid == 0) wait_expired(t0, spins, S, P.status);
-            if (S->abort_flag) break;
+            if (__all_sync(0xffffffffu, have)) break;
+            if (wait_expired(t0, spins, S, P.status)) break;
         }
     }
     if (role == 0) {
