@@ -46,6 +46,9 @@ constexpr int DEC_ILP = 4;                      // rows one warp folds together
 constexpr int DEC_MAX_LAYERS = 128;
 constexpr int DEC_ROWBUF = DEC_CTHREADS;        // per-CTA rows whose epilogue operand is staged
 constexpr long long DEC_WAIT_CLOCKS = 2000000000LL;   // ~1 s at 2 GHz
+#ifndef DEC_POLL_BACKOFF_NS
+#define DEC_POLL_BACKOFF_NS 200
+#endif
 
 // ---------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -258,8 +261,10 @@ __device__ __forceinline__ void producer_loop(const lt_decode_desc& P, unsigned 
 
 // ---------------------------------------------------------------- consumer helpers
 // Load n tagged elements into shared memory (values only), retrying the ones whose tag is not
-// yet `want`.  All loads of a round are in flight together; every warp polls at its own pace
-// (no block barrier per round); the caller synchronises the consumers afterwards.
+// yet `want`.  All loads of a round are in flight together; a round ends in one consumer
+// barrier that also tells whether every element has arrived, and a failed round backs off for
+// a moment: polling that is too eager steals L2 bandwidth from the CTAs still producing
+// (measured: per-warp free-running polls made the step slower).
 template <int B>
 __device__ __forceinline__ void wait_vector(const float2* __restrict__ g, float* s, int n, unsigned want, Shared* S,
                                             int* status) {
@@ -279,8 +284,10 @@ __device__ __forceinline__ void wait_vector(const float2* __restrict__ g, float*
             if (!have[k]) have[k] = (__float_as_uint(v[k].y) == want);
             ok = ok && have[k];
         }
-        if (__all_sync(0xffffffffu, ok)) break;
-        if (wait_expired(t0, spins, S, status)) break;
+        if (consumer_all(ok)) break;
+        if (threadIdx.x == 0) wait_expired(t0, spins, S, status);
+        if (S->abort_flag) break;
+        __nanosleep(DEC_POLL_BACKOFF_NS);
     }
 #pragma unroll
     for (int k = 0; k < B; k++) {
@@ -406,8 +413,10 @@ __device__ __forceinline__ void attention_phase(const lt_decode_desc& P, const l
                 e2 = __ldcg(src + j + half);
                 have = (__float_as_uint(e1.y) == tag) && (__float_as_uint(e2.y) == tag);
             }
-            if (__all_sync(0xffffffffu, have)) break;
-            if (wait_expired(t0, spins, S, P.status)) break;
+            if (consumer_all(have)) break;
+            if (tid == 0) wait_expired(t0, spins, S, P.status);
+            if (S->abort_flag) break;
+            __nanosleep(DEC_POLL_BACKOFF_NS);
         }
     }
     if (role == 0) {
