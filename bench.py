@@ -177,6 +177,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--step-mode", default=None, choices=["pdl", "persistent", "per-op"],
+                    help="how the captured decode step is built (default: the engine's default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -198,6 +200,8 @@ def main():
     V, E = mc["vocab"], mc["n_embd"]
     prompt = np.random.default_rng(0).integers(0, V, size=PROMPT_LEN).tolist()
     dr.reset_engine_state(); dr.apply_production_profile()
+    if args.step_mode is not None:
+        dr._FUSED_STEP = False if args.step_mode == "per-op" else args.step_mode
     w, cfg = synth.reference_weights(model)
 
     # ---- prompt (eager, token by token, as the reference does) + capture
@@ -318,6 +322,7 @@ def main():
            "config": {"workload": f"{ARCH} Q8_0 decode, batch 1, {PROMPT_LEN}-token prompt, {K} greedy steps",
                       "parallelism": "replicas only" if world > 1 else "1 GPU",
                       "l2": "inputs larger than L2 (525 MB of weights streamed per token vs 126 MB L2)",
+                      "step_mode": dr._FUSED_STEP if dr._FUSED_STEP else "per-op",
                       "tokens_device_loop_equal_host_loop": tokens_match, "device_status": sorted(status)},
            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": E * 4, "d2h_bytes_per_step": 4,
                    "ms_per_step": e2e_ms / K},

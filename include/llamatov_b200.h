@@ -182,10 +182,18 @@ typedef struct lt_decode_desc {
     int* status;               /* device status word; NULL = the library's own */
     long long* trace;          /* optional [2][8192][2] (id, SM clock) stamps of CTA 0 and of the last CTA
                                   (diagnostics); NULL in production */
+    const lt_decode_layer* h_layers; /* HOST copy of the layer array (used by lt_decode_step_pdl) */
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);
 int lt_decode_num_ctas(void);
+
+/* The same step, same descriptor and bit-identical results, as a chain of fused kernels (five
+ * per layer + LM head + argmax) linked by programmatic dependent launch: every kernel prefetches
+ * its weights while its predecessor is still running.  The workspaces are used as plain
+ * buffers here (no tags).  part_val / part_idx need lt_decode_pdl_num_parts() entries. */
+int lt_decode_step_pdl(const lt_decode_desc* h_desc, void* stream);
+int lt_decode_pdl_num_parts(void);
 
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a

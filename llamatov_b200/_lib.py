@@ -38,6 +38,8 @@ SIGNATURES = {
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],
     "lt_decode_num_ctas": [],
+    "lt_decode_step_pdl": [_vp, _vp],
+    "lt_decode_pdl_num_parts": [],
 }
 _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}

@@ -694,10 +694,12 @@ def _compute_folded_logits(w, cfg, E):
 
 
 # --------------------------------------------------------------------------- fused decode step
-# When True, GraphRunner records the whole token step as ONE persistent kernel
-# (lt_decode_step) instead of ~320 per-op kernel nodes.  Same arithmetic, bit-identical
-# results; the eager forward_pass_resident keeps the per-op launches and is the parity baseline.
-_FUSED_STEP = True
+# GraphRunner records the token step either as ~320 per-op kernel nodes (False, the reference's
+# structure), as a chain of fused kernels linked by programmatic dependent launch ("pdl",
+# lt_decode_step_pdl: 122 nodes) or as ONE persistent kernel ("persistent", lt_decode_step).
+# Same arithmetic, bit-identical results in every mode; the eager forward_pass_resident keeps
+# the per-op launches and is the parity baseline.
+_FUSED_STEP = "pdl"
 
 
 class _DecLayer(ctypes.Structure):
@@ -712,7 +714,7 @@ class _DecDesc(ctypes.Structure):
                [(n, ctypes.c_void_p) for n in (
                    "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "ws_x", "ws_x1", "ws_qkv", "ws_att",
                    "ws_v", "logits", "tok", "out_tok", "history", "step", "sync", "epoch", "part_val", "part_idx",
-                   "status", "trace")]
+                   "status", "trace", "h_layers")]
 
 
 class FusedDecodeStep:
@@ -745,12 +747,13 @@ class FusedDecodeStep:
                                    _addr(dq), _addr(dd), _addr(c.k_ptr), _addr(c.v_ptr), _addr(c.len_ptr))
         raw = np.frombuffer(bytes(layers), dtype=np.uint8).copy()
         self._layers_dev = torch.from_numpy(raw).cuda()
+        self._layers_host = layers
         lq, ld, V, _ = _weights(_lm_head(w))
         eq, ed = None, None
         if tok_ptr is not None:
             eq, ed, _, _ = _weights(_np(w["token_embd.weight"]))
         nq, nk = nh * hd, nkv * hd
-        nct = _lib.lib().lt_decode_num_ctas()
+        nct = max(_lib.lib().lt_decode_num_ctas(), _lib.lib().lt_decode_pdl_num_parts())
         f32 = dict(dtype=torch.float32, device="cuda")
         # tagged workspaces: {value, tag} pairs, zero tags = "never written"
         self.ws = [torch.zeros(2 * n, **f32) for n in (E, E, nq + 2 * nk, nq, F)]
@@ -770,7 +773,8 @@ class FusedDecodeStep:
                              None if tok_ptr is None else int(tok_ptr), _addr(out_tok),
                              None if history is None else int(history), None if step is None else int(step),
                              self.sync.data_ptr(), self.epoch.data_ptr(), self.part_val.data_ptr(),
-                             self.part_idx.data_ptr(), None, None)
+                             self.part_idx.data_ptr(), None, None, ctypes.addressof(self._layers_host))
+        self.mode = "persistent" if _FUSED_STEP is True else _FUSED_STEP
 
     def enable_trace(self):
         """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""
@@ -780,8 +784,10 @@ class FusedDecodeStep:
         return n
 
     def launch(self):
-        rc = _lib.lib().lt_decode_step(ctypes.byref(self.desc), _stream())
-        _lib.check(rc, "lt_decode_step")
+        if self.mode == "pdl":
+            _lib.check(_lib.lib().lt_decode_step_pdl(ctypes.byref(self.desc), _stream()), "lt_decode_step_pdl")
+        else:
+            _lib.check(_lib.lib().lt_decode_step(ctypes.byref(self.desc), _stream()), "lt_decode_step")
 
 
 class GraphRunner:

@@ -83,7 +83,7 @@ def test_fp32_weight_boundary_equals_q8_boundary():
         assert np.array_equal(bits(x), bits(y))
 
 
-@pytest.fixture(params=[True, False], ids=["fused-step", "per-op-graph"])
+@pytest.fixture(params=["pdl", "persistent", False], ids=["fused-pdl", "fused-persistent", "per-op-graph"])
 def fused(request):
     old = dr._FUSED_STEP
     dr._FUSED_STEP = request.param
@@ -124,7 +124,10 @@ def test_graph_replay_equals_eager_bit_exact(fused, arch):
     # replay_token: device argmax == host argmax of the same logits
     t_dev = gr.replay_token(nxt)
     assert t_dev == int(np.argmax(dr._LOGITS_BUF.to_host()))
-    assert gr.launches_per_token == (1 if fused else gr.launches_per_token)
+    if fused == "persistent":
+        assert gr.launches_per_token == 1
+    elif fused == "pdl":
+        assert gr.launches_per_token == 5 * cfg["n_layers"] + 2
     assert dr._lib.device_status() == set()
 
 
@@ -157,11 +160,12 @@ def test_device_token_loop_equals_host_driven_loop(fused, arch):
     assert dr._lib.device_status() == set()
 
 
-def test_fused_step_kv_overflow_is_flagged_not_faulted():
+@pytest.mark.parametrize("mode", ["pdl", "persistent"])
+def test_fused_step_kv_overflow_is_flagged_not_faulted(mode):
     m, w, cfg = _fresh("tiny", seed=7)
     dr._KV_MAX_SEQ = 8
     old = dr._FUSED_STEP
-    dr._FUSED_STEP = True
+    dr._FUSED_STEP = mode
     try:
         kv = [None] * cfg["n_layers"]
         gr = dr.GraphRunner(w, cfg, kv)
