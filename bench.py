@@ -220,18 +220,15 @@ def main():
             c._len.fill_(PROMPT_LEN)
         torch.cuda.synchronize()
 
+    from llamatov_b200 import replicas
+
     def barrier():
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        replicas.barrier()
         torch.cuda.synchronize()
 
     def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return replicas.max_over_ranks(ms, device="cuda")
 
     if K + W > max_new:
         raise SystemExit(f"steps+warmup = {K + W} exceeds the KV capacity left after the prompt ({max_new})")
