@@ -190,10 +190,10 @@ int lt_decode_num_ctas(void);
 
 /* The same step, same descriptor and bit-identical results, as a chain of fused kernels (five
  * per layer + LM head + argmax) linked by programmatic dependent launch: every kernel prefetches
- * its weights while its predecessors are still running and then waits for its input activation
- * words (tagged like in lt_decode_step) rather than for the predecessor kernel.  Use separate
- * workspaces, sync and epoch words for the two entry points.  part_val / part_idx need
- * lt_decode_pdl_num_parts() entries of 8 bytes each. */
+ * its weights (and cached K/V rows, rope angles) while its predecessor is still running, then
+ * waits for the predecessor (griddepcontrol.wait).  The workspaces are used as plain buffers
+ * here (no tags); epoch and sync are not used.  part_val / part_idx need
+ * lt_decode_pdl_num_parts() entries. */
 int lt_decode_step_pdl(const lt_decode_desc* h_desc, void* stream);
 int lt_decode_pdl_num_parts(void);
 

@@ -1,21 +1,12 @@
-// One decode step as a chain of FUSED kernels linked by programmatic dependent launch and by
-// tagged data.
+// One decode step as a chain of FUSED kernels linked by programmatic dependent launch.
 //
 // Five kernels per layer (q|k|v, attention, o_proj, gate|up, down), an LM-head kernel and a
 // final argmax kernel.  Each kernel (a) lets its successor start launching at once
 // (griddepcontrol.launch_dependents), (b) fetches everything that does not depend on its
-// predecessor -- its weight rows, norm weights, cached K/V rows, rope angles -- with
-// asynchronous copies into shared memory, and then (c) waits for its input ACTIVATION, not for
-// its predecessor kernel: every activation element that crosses kernels is one 8-byte word
-// {payload, 32-bit tag}; the tag names the token and layer that produced it, the consumer
-// loads the vector and retries the words whose tag is not yet the expected one.  Payload and
-// tag travel in one naturally aligned store, so they are never seen apart, and no fence,
-// counter or kernel-completion flush sits on the critical path.  A kernel only ever waits for
-// data of kernels launched BEFORE it in the same stream, all of whose CTAs are resident or
-// done by the time it starts (that is the launch_dependents rule), so every wait terminates;
-// waits are bounded by a clock limit all the same (LT_STATUS_WAIT_TIMEOUT).  Buffer reuse is
-// safe because every rewrite of a buffer is separated from its last read by a full
-// all-to-all phase.
+// predecessor -- its weight rows, norm weights, cached K/V rows -- into shared memory with
+// asynchronous copies, and only then (c) waits for the predecessor's results
+// (griddepcontrol.wait).  Launch latency and the weight stream therefore overlap the
+// predecessor's execution; what stays serial is a short activation prologue and the fold.
 //
 // Activations are quantised where they are produced whenever a producer owns whole 32-blocks
 // (attention heads, gate|up blocks), so that the consumer's prologue is a plain copy.
@@ -35,100 +26,7 @@ __device__ __forceinline__ void fcp_async4(void* dst, const void* src) {
 }
 __device__ __forceinline__ void fcp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-constexpr long long FUSED_WAIT_CLOCKS = 2000000000LL;   // ~1 s
-constexpr unsigned FUSED_BACKOFF_NS = 100;
-
-__device__ __forceinline__ void st_tag_f32(float2* p, float v, unsigned tag) { __stcg(p, make_float2(v, __uint_as_float(tag))); }
-__device__ __forceinline__ void st_tag_u32(uint2* p, unsigned v, unsigned tag) { __stcg(p, make_uint2(v, tag)); }
-
-// one polling round is over: true when the block has everything or has given up
-__device__ __forceinline__ bool poll_round_done(bool ok, long long t0, int* status) {
-    if (__syncthreads_and(ok)) return true;
-    __shared__ int s_giveup;
-    if (threadIdx.x == 0) {
-        s_giveup = 0;
-        if ((*(volatile int*)status & (int)LT_STATUS_WAIT_TIMEOUT) || clock64() - t0 > FUSED_WAIT_CLOCKS) {
-            atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
-            s_giveup = 1;
-        }
-    }
-    __syncthreads();
-    if (s_giveup) return true;
-    __nanosleep(FUSED_BACKOFF_NS);
-    return false;
-}
-
-// Tagged fp32 vector -> shared memory floats.  All loads of a round are in flight together.
-template <int B>
-__device__ __forceinline__ void poll_f32(const float2* __restrict__ g, float* s, int n, unsigned want, int* status) {
-    float2 v[B];
-    bool have[B];
-    const int nt = blockDim.x;
-#pragma unroll
-    for (int k = 0; k < B; k++) have[k] = (k * nt + (int)threadIdx.x >= n);
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll
-        for (int k = 0; k < B; k++)
-            if (!have[k]) v[k] = __ldcg(g + k * nt + threadIdx.x);
-        bool ok = true;
-#pragma unroll
-        for (int k = 0; k < B; k++) {
-            if (!have[k]) have[k] = (__float_as_uint(v[k].y) == want);
-            ok = ok && have[k];
-        }
-        if (poll_round_done(ok, t0, status)) break;
-    }
-#pragma unroll
-    for (int k = 0; k < B; k++) {
-        const int j = k * nt + threadIdx.x;
-        if (j < n) s[j] = v[k].x;
-    }
-}
-
-// Tagged Q8_0 vector: per 32-block nine words, eight {4 quants, tag} and one {fp16 scale, tag}.
-template <int B>
-__device__ __forceinline__ void poll_q8(const uint2* __restrict__ g, int8_t* sXq, __half* sXd, int nblk, unsigned want,
-                                        int* status) {
-    uint2 v[B];
-    bool have[B];
-    const int nt = blockDim.x, n = nblk * 9;
-#pragma unroll
-    for (int k = 0; k < B; k++) have[k] = (k * nt + (int)threadIdx.x >= n);
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll
-        for (int k = 0; k < B; k++)
-            if (!have[k]) v[k] = __ldcg(g + k * nt + threadIdx.x);
-        bool ok = true;
-#pragma unroll
-        for (int k = 0; k < B; k++) {
-            if (!have[k]) have[k] = (v[k].y == want);
-            ok = ok && have[k];
-        }
-        if (poll_round_done(ok, t0, status)) break;
-    }
-#pragma unroll
-    for (int k = 0; k < B; k++) {
-        const int j = k * nt + threadIdx.x;
-        if (j < n) {
-            const int b = j / 9, w = j - b * 9;
-            if (w < 8) ((unsigned*)sXq)[b * 8 + w] = v[k].x;
-            else sXd[b] = __ushort_as_half((unsigned short)(v[k].x & 0xffffu));
-        }
-    }
-}
-
-// a warp publishes one quantised 32-block (lane = element) in the tagged layout
-__device__ __forceinline__ void publish_q8_block(uint2* g, int blk, int q, __half dh, unsigned tag, int lane) {
-    // gather four consecutive quants into one word: lanes 4w..4w+3 -> lane 4w
-    unsigned b = (unsigned)(q & 0xff);
-    b |= __shfl_down_sync(0xffffffffu, b, 1) << 8;
-    b |= __shfl_down_sync(0xffffffffu, b, 2) << 16;
-    if ((lane & 3) == 0) st_tag_u32(g + (size_t)blk * 9 + (lane >> 2), b, tag);
-    if (lane == 0) st_tag_u32(g + (size_t)blk * 9 + 8, (unsigned)__half_as_ushort(dh), tag);
-}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // asynchronous copy of one weight row (K quants, K/32 scales; K % 64 == 0) into shared memory
 __device__ __forceinline__ void prefetch_row(unsigned char* dst, const int8_t* Wq, const __half* Wd, long row, int K,
@@ -206,32 +104,21 @@ __device__ __forceinline__ void block_quant(const float* sF, const float* sW, fl
 
 struct FusedArgs {
     const int8_t* Wq; const __half* Wd; int M, K;
-    // activation: tagged fp32 vector (+ norm weight) to be quantised here, a tagged Q8_0 vector, or
-    // a plain fp32 row written by the host / an embedding row gathered by token (first kernel)
-    const float2* x_tagged; const float* x_plain; const float* normw; float eps;
-    const uint2* xq_tagged;
-    const int* tok; const int8_t* emb_q; const __half* emb_d; int V; float2* x_copy;
-    unsigned in_tag_off;        // tag of the input relative to this step's base tag
+    // activation: f32 vector (+ norm weight) to be quantised here, or an already quantised one
+    const float* x; const float* normw; float eps;
+    const int8_t* xq; const __half* xd;
+    // embedding gather for the first kernel of a step
+    const int* tok; const int8_t* emb_q; const __half* emb_d; int V; float* x_copy;
     // epilogue
-    const float* bias;          // plain constant, or
-    const float2* resid_tagged; // tagged residual stream (already complete when the input has arrived), or
-    const float* resid_plain;   // plain residual (host-written input row)
-    float2* out;                // tagged fp32 [M]
-    unsigned out_tag_off;
+    const float* add; float* out;
     int* len_incr; int max_seq;
-    const unsigned* epoch; int n_layers;
     int* status;
 };
-
-__device__ __forceinline__ unsigned base_tag(const unsigned* epoch, int n_layers) {
-    return __ldcg(epoch) * (unsigned)(n_layers + 1) + 1u;
-}
 
 // shared layout of k_fused_gemv: sXq[K] | sXd[K/32] (pad 16) | sred[272] | sF[K] | sW[K] | rows[8][K + K/16 (+pad)]
 __device__ __forceinline__ int row_stride(int K) { return ((K + (K >> 4)) + 15) & ~15; }
 
-// PRO: 0 = activation arrives quantised (tagged Q8_0), 1 = tagged fp32 vector -> rmsnorm -> quant,
-//      2 = plain fp32 row -> rmsnorm -> quant, 3 = embedding row by token -> rmsnorm -> quant
+// PRO: 0 = activation arrives quantised, 1 = f32 vector -> rmsnorm -> quant, 2 = embedding row -> rmsnorm -> quant
 template <int PRO>
 __global__ void __launch_bounds__(256) k_fused_gemv(const FusedArgs a) {
     extern __shared__ __align__(16) unsigned char fsm[];
@@ -249,20 +136,18 @@ __global__ void __launch_bounds__(256) k_fused_gemv(const FusedArgs a) {
     const long row = (long)blockIdx.x * 8 + warp;
 
     pdl_launch_dependents();
-    // ---- independent of the predecessors: this warp's weight row, the norm weight, the bias
+    // ---- independent of the predecessor: this warp's weight row, the norm weight
     if (row < a.M) prefetch_row(rows + (size_t)warp * row_stride(K), a.Wq, a.Wd, row, K, lane);
     if (PRO)
         for (int c = threadIdx.x; c < (K >> 2); c += 256) fcp_async16(sW + c * 4, a.normw + c * 4);
     float addv = 0.0f;
-    if (a.bias != nullptr && lane == 0 && row < a.M) addv = __ldg(a.bias + row);
-    const unsigned tag0 = base_tag(a.epoch, a.n_layers);
+    pdl_wait();
     // ---- activation
     if (PRO == 0) {
-        poll_q8<6>(a.xq_tagged, sXq, sXd, nb, tag0 + a.in_tag_off, a.status);
+        for (int c = threadIdx.x; c < (K >> 4); c += 256) ((int4*)sXq)[c] = __ldcg((const int4*)a.xq + c);
+        for (int c = threadIdx.x; c < (nb >> 1); c += 256) ((unsigned*)sXd)[c] = __ldcg((const unsigned*)a.xd + c);
     } else if (PRO == 1) {
-        poll_f32<8>(a.x_tagged, sF, K, tag0 + a.in_tag_off, a.status);
-    } else if (PRO == 2) {
-        for (int j = threadIdx.x; j < K; j += 256) sF[j] = __ldcg(a.x_plain + j);
+        for (int j = threadIdx.x; j < K; j += 256) sF[j] = __ldcg(a.x + j);
     } else {
         int t = __ldcg(a.tok);
         if (t < 0 || t >= a.V) {
@@ -272,15 +157,10 @@ __global__ void __launch_bounds__(256) k_fused_gemv(const FusedArgs a) {
         for (int j = threadIdx.x; j < K; j += 256) {
             const float v = __fmul_rn(__half2float(a.emb_d[(size_t)t * nb + (j >> 5)]), (float)a.emb_q[(size_t)t * K + j]);
             sF[j] = v;
-            if (blockIdx.x == 0) st_tag_f32(a.x_copy + j, v, 0u);
+            if (blockIdx.x == 0) a.x_copy[j] = v;
         }
-        if (blockIdx.x == 0) __threadfence();   // the row is the residual of this layer's o_proj
     }
-    // the residual stream is complete once this kernel's input has arrived
-    if (lane == 0 && row < a.M) {
-        if (a.resid_tagged != nullptr) addv = __ldcg(a.resid_tagged + row).x;
-        else if (a.resid_plain != nullptr) addv = __ldcg(a.resid_plain + row);
-    }
+    if (a.add != nullptr && lane == 0 && row < a.M) addv = __ldcg(a.add + row);
     if (a.len_incr != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
         const int p = __ldcg(a.len_incr);
         if (p >= 0 && p < a.max_seq) *a.len_incr = p + 1;
@@ -296,8 +176,8 @@ __global__ void __launch_bounds__(256) k_fused_gemv(const FusedArgs a) {
     if (row < a.M) {
         float v = warp_tree_sum(fold_row(rows + (size_t)warp * row_stride(K), K, sXq, sXd, lane));
         if (lane == 0) {
-            if (a.bias != nullptr || a.resid_tagged != nullptr || a.resid_plain != nullptr) v = __fadd_rn(v, addv);
-            st_tag_f32(a.out + row, v, tag0 + a.out_tag_off);
+            if (a.add != nullptr) v = __fadd_rn(v, addv);
+            a.out[row] = v;
         }
     }
 }
@@ -306,11 +186,8 @@ __global__ void __launch_bounds__(256) k_fused_gemv(const FusedArgs a) {
 // v = silu(gate)*up for its block and quantises it, so the down projection receives Q8_0.
 struct GateUpArgs {
     const int8_t* Wq; const __half* Wd; int F, K;      // [2F, K], rows gate | up
-    const float2* x_tagged; const float* normw; float eps;
-    uint2* vq_tagged;                                   // tagged Q8_0 [F]
-    unsigned tag_off;
-    const unsigned* epoch; int n_layers;
-    int* status;
+    const float* x; const float* normw; float eps;
+    int8_t* vq; __half* vd;                            // [F], [F/32]
 };
 
 __global__ void __launch_bounds__(512) k_fused_gateup(const GateUpArgs a) {
@@ -339,8 +216,8 @@ __global__ void __launch_bounds__(512) k_fused_gateup(const GateUpArgs a) {
         prefetch_row(rows + (size_t)(32 + i) * rs, a.Wq, a.Wd, (long)a.F + blk * 32 + i, K, lane);
     }
     for (int c = threadIdx.x; c < (K >> 2); c += 512) fcp_async16(sW + c * 4, a.normw + c * 4);
-    const unsigned tag = base_tag(a.epoch, a.n_layers) + a.tag_off;
-    poll_f32<4>(a.x_tagged, sF, K, tag, a.status);
+    pdl_wait();
+    for (int j = threadIdx.x; j < K; j += 512) sF[j] = __ldcg(a.x + j);
     fcp_async_wait_all();
     __syncthreads();
     const float ss = block_rms_sumsq(sF, K, sred);
@@ -367,18 +244,17 @@ __global__ void __launch_bounds__(512) k_fused_gateup(const GateUpArgs a) {
     if (warp == 0) {
         __half dh;
         const int q = quant_lane(sv[lane], &dh);
-        publish_q8_block(a.vq_tagged, (int)blk, q, dh, tag, lane);
+        a.vq[blk * 32 + lane] = (int8_t)q;
+        if (lane == 0) a.vd[blk] = dh;
     }
 }
 
 // attention: one CTA per query head, 256 threads; rope + KV append + masked attention, output
 // quantised (a head is hd/32 whole blocks).
 struct AttnArgs {
-    const float2* qkv_tagged; float* kcache; float* vcache; const int* len;
-    uint2* att_tagged;
+    const float* qkv; float* kcache; float* vcache; const int* len;
+    int8_t* aq; __half* ad;
     int hd, nh, nkv, maxt, vcap; float theta, scale;
-    unsigned tag_off;
-    const unsigned* epoch; int n_layers;
     int* status;
 };
 
@@ -397,8 +273,7 @@ __global__ void __launch_bounds__(256) k_fused_attn(const AttnArgs a) {
     const int nq = nh * hd, nk = nkv * hd, rep = nh / nkv, hk = h / rep;
 
     pdl_launch_dependents();
-    // the cache length was last changed by the previous step, and it is advanced in this step
-    // only by a kernel that needs this kernel's output
+    // the cache length was last changed by the previous step: readable before the wait
     int pos = __ldcg(a.len);
     const bool room = (pos >= 0 && pos < maxt);
     if (!room) {
@@ -415,40 +290,27 @@ __global__ void __launch_bounds__(256) k_fused_attn(const AttnArgs a) {
             fcp_async16(sV + (size_t)t * hd + c * 4, a.vcache + g);
         }
     }
-    const unsigned tag = base_tag(a.epoch, a.n_layers) + a.tag_off;
-    // the q / k / v slices of the new token: threads [0, hd/2) rope q, [64, 64 + hd/2) rope k,
-    // [128, 128 + hd) copy v; each polls its own elements
+    // rope angles depend on the position only: evaluated before the predecessor is awaited
     const int half = hd >> 1;
-    int role = -1, j = 0;
-    const float2* src = a.qkv_tagged;
-    if (tid < half) { role = 0; j = tid; src = a.qkv_tagged + h * hd; }
-    else if (tid >= 64 && tid < 64 + half) { role = 1; j = tid - 64; src = a.qkv_tagged + nq + hk * hd; }
-    else if (tid >= 128 && tid < 128 + hd) { role = 2; j = tid - 128; src = a.qkv_tagged + nq + nk + hk * hd; }
-    float2 e1 = make_float2(0.0f, 0.0f), e2 = e1;
-    {
-        bool have = (role < 0);
-        const long long t0 = clock64();
-        for (;;) {
-            if (!have) {
-                e1 = __ldcg(src + j);
-                e2 = (role == 2) ? e1 : __ldcg(src + j + half);
-                have = (__float_as_uint(e1.y) == tag) && (__float_as_uint(e2.y) == tag);
-            }
-            if (poll_round_done(have, t0, a.status)) break;
-        }
-    }
-    if (role == 0) {
+    float rc = 1.0f, rs = 0.0f;
+    if (tid < half) rope_trig(tid, hd, a.theta, pos, rc, rs);
+    else if (tid >= 64 && tid < 64 + half) rope_trig(tid - 64, hd, a.theta, pos, rc, rs);
+    pdl_wait();
+    if (tid < half) {
         float o1, o2;
-        rope_pair(e1.x, e2.x, j, hd, a.theta, pos, o1, o2);
-        sQ[j] = o1; sQ[j + half] = o2;
-    } else if (role == 1) {
+        rope_rotate(__ldcg(a.qkv + h * hd + tid), __ldcg(a.qkv + h * hd + tid + half), rc, rs, o1, o2);
+        sQ[tid] = o1; sQ[tid + half] = o2;
+    } else if (tid >= 64 && tid < 64 + half) {
+        const int j = tid - 64;
         float o1, o2;
-        rope_pair(e1.x, e2.x, j, hd, a.theta, pos, o1, o2);
+        rope_rotate(__ldcg(a.qkv + nq + hk * hd + j), __ldcg(a.qkv + nq + hk * hd + j + half), rc, rs, o1, o2);
         sKn[j] = o1; sKn[j + half] = o2;
         if (room && staged) { sK[(size_t)pos * kst + j] = o1; sK[(size_t)pos * kst + j + half] = o2; }
-    } else if (role == 2) {
-        sVn[j] = e1.x;
-        if (room && staged) sV[(size_t)pos * hd + j] = e1.x;
+    } else if (tid >= 128 && tid < 128 + hd) {
+        const int j = tid - 128;
+        const float v = __ldcg(a.qkv + nq + nk + hk * hd + j);
+        sVn[j] = v;
+        if (room && staged) sV[(size_t)pos * hd + j] = v;
     }
     fcp_async_wait_all();
     __syncthreads();
@@ -534,18 +396,17 @@ __global__ void __launch_bounds__(256) k_fused_attn(const AttnArgs a) {
     if (warp < (hd >> 5)) {
         __half dh;
         const int q = quant_lane(so[warp * 32 + lane], &dh);
-        publish_q8_block(a.att_tagged, (h * hd >> 5) + warp, q, dh, tag, lane);
+        a.aq[h * hd + warp * 32 + lane] = (int8_t)q;
+        if (lane == 0) a.ad[(h * hd >> 5) + warp] = dh;
     }
 }
 
 // LM head: prologue as k_fused_gemv<1>, then a grid-stride walk over the vocabulary rows with
-// the weights streamed from global memory; each CTA leaves its best (value, index), tagged.
+// the weights streamed from global memory; each CTA leaves its best (value, index).
 struct LmArgs {
     const int8_t* Wq; const __half* Wd; int V, K;
-    const float2* x_tagged; const float* normw; float eps;
-    float* logits; float2* part_val; uint2* part_idx;
-    const unsigned* epoch; int n_layers;
-    int* status;
+    const float* x; const float* normw; float eps;
+    float* logits; float* part_val; int* part_idx;
 };
 
 __global__ void __launch_bounds__(256) k_fused_lmhead(const LmArgs a) {
@@ -565,7 +426,7 @@ __global__ void __launch_bounds__(256) k_fused_lmhead(const LmArgs a) {
 
     pdl_launch_dependents();
     for (int c = threadIdx.x; c < (K >> 2); c += 256) fcp_async16(sW + c * 4, a.normw + c * 4);
-    // first group of rows: weights into registers before the activation is awaited
+    // first group of rows: weights into registers before the predecessor is awaited
     int4 w0[R], w1[R];
     float wd[R];
     const bool one_block = (nb <= 32);
@@ -579,8 +440,8 @@ __global__ void __launch_bounds__(256) k_fused_lmhead(const LmArgs a) {
             wd[r] = __half2float(__ushort_as_half(ld_stream_u16(a.Wd + (r0 + r) * nb + lane)));
         }
     }
-    const unsigned tag0 = base_tag(a.epoch, a.n_layers);
-    poll_f32<8>(a.x_tagged, sF, K, tag0 + (unsigned)(a.n_layers - 1), a.status);
+    pdl_wait();
+    for (int j = threadIdx.x; j < K; j += 256) sF[j] = __ldcg(a.x + j);
     fcp_async_wait_all();
     __syncthreads();
     const float ss = block_rms_sumsq(sF, K, sred);
@@ -641,46 +502,27 @@ __global__ void __launch_bounds__(256) k_fused_lmhead(const LmArgs a) {
         int i = bi[0];
         for (int w = 1; w < 8; w++)
             if (bv[w] > v || (bv[w] == v && bi[w] < i)) { v = bv[w]; i = bi[w]; }
-        const unsigned tag = tag0 + (unsigned)a.n_layers;
-        st_tag_f32(a.part_val + blockIdx.x, v, tag);
-        st_tag_u32(a.part_idx + blockIdx.x, (unsigned)i, tag);
+        a.part_val[blockIdx.x] = v;
+        a.part_idx[blockIdx.x] = i;
     }
 }
 
 struct FinalArgs {
-    const float2* part_val; const uint2* part_idx; int nparts;
+    const float* part_val; const int* part_idx; int nparts;
     int* out_tok; int* tok; int* history; int* step; int hist_cap;
-    unsigned* epoch; int n_layers;
-    int* status;
 };
 
-// grid 1 x 256: waits for every CTA of the LM head, picks the token, advances the token counter
 __global__ void __launch_bounds__(256) k_fused_argmax(const FinalArgs a) {
     __shared__ float sv[8];
     __shared__ int si[8];
     pdl_launch_dependents();
-    const unsigned tag = base_tag(a.epoch, a.n_layers) + (unsigned)a.n_layers;
+    pdl_wait();
     float bv = -3.4e38f;
     int bi = 2147483647;
-    const long long t0 = clock64();
-    for (int c0 = 0; c0 < a.nparts; c0 += 256) {
-        const int c = c0 + threadIdx.x;
-        float2 pv = make_float2(0.0f, 0.0f);
-        uint2 pi = make_uint2(0u, 0u);
-        bool have = (c >= a.nparts);
-        for (;;) {
-            if (!have) {
-                pv = __ldcg(a.part_val + c);
-                pi = __ldcg(a.part_idx + c);
-                have = (__float_as_uint(pv.y) == tag) && (pi.y == tag);
-            }
-            if (poll_round_done(have, t0, a.status)) break;
-        }
-        if (c < a.nparts) {
-            const float v = pv.x;
-            const int i = (int)pi.x;
-            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-        }
+    for (int c = threadIdx.x; c < a.nparts; c += 256) {
+        const float v = __ldcg(a.part_val + c);
+        const int i = __ldcg(a.part_idx + c);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) {
@@ -700,8 +542,6 @@ __global__ void __launch_bounds__(256) k_fused_argmax(const FinalArgs a) {
             if (s >= 0 && s < a.hist_cap) a.history[s] = bi;
             *a.step = s + 1;
         }
-        // every kernel of this step has read the counter long ago (this kernel's input needed them all)
-        *a.epoch = *a.epoch + 1u;
     }
 }
 
@@ -742,14 +582,12 @@ using namespace lt;
 extern "C" int lt_decode_step_pdl(const lt_decode_desc* d, void* stream) {
     LT_REQUIRE(d != nullptr, "lt_decode_step_pdl: null descriptor");
     LT_REQUIRE(d->layers && d->h_layers && d->out_norm && d->lm_q && d->lm_d && d->logits && d->out_tok && d->part_val &&
-                   d->part_idx && d->ws_x && d->ws_x1 && d->ws_qkv && d->ws_att && d->ws_v && d->epoch,
+                   d->part_idx && d->ws_x && d->ws_x1 && d->ws_qkv && d->ws_att && d->ws_v,
                "lt_decode_step_pdl: null pointer in descriptor (h_layers is the host copy of the layer array)");
     LT_REQUIRE(d->tok != nullptr ? (d->emb_q && d->emb_d) : (d->x != nullptr),
                "lt_decode_step_pdl: needs either a device token with the embedding table or a preloaded input row");
-    const int E = d->E, F = d->F, hd = d->hd, nq = d->nh * hd, nk = d->nkv * hd, nqkv = nq + 2 * nk, L = d->n_layers;
+    const int E = d->E, F = d->F, hd = d->hd, nq = d->nh * hd, nk = d->nkv * hd, nqkv = nq + 2 * nk;
     LT_REQUIRE(E % 64 == 0 && F % 64 == 0 && nq % 64 == 0, "lt_decode_step_pdl: E, F and nh*hd must be multiples of 64");
-    LT_REQUIRE(E <= 8 * 256 && nq <= 6 * 256 * 32 / 9 && F <= 6 * 256 * 32 / 9,
-               "lt_decode_step_pdl: this build handles E up to 2048 and nh*hd, F up to 5440");
     LT_REQUIRE(hd == 32 || hd == 64 || hd == 128, "lt_decode_step_pdl: hd=%d must be 32, 64 or 128", hd);
     LT_REQUIRE(d->nkv > 0 && d->nh % d->nkv == 0 && d->max_seq % 4 == 0, "lt_decode_step_pdl: bad head / cache geometry");
     cudaStream_t s = (cudaStream_t)stream;
@@ -762,11 +600,13 @@ extern "C" int lt_decode_step_pdl(const lt_decode_desc* d, void* stream) {
     LT_REQUIRE(gemv_smem(F, false) <= (size_t)smem_max && gemv_smem(E, true) <= (size_t)smem_max,
                "lt_decode_step_pdl: model dimensions need more shared memory than one SM has");
 
-    float2* x = (float2*)d->ws_x;             // residual stream (tagged)
-    float2* x1 = (float2*)d->ws_x1;
-    float2* qkv = (float2*)d->ws_qkv;
-    uint2* att = (uint2*)d->ws_att;           // tagged Q8_0: 9 words per 32-block (72 B <= 8 B * 32)
-    uint2* vq = (uint2*)d->ws_v;
+    float* x = (float*)d->ws_x;             // residual stream
+    float* x1 = (float*)d->ws_x1;
+    float* qkv = (float*)d->ws_qkv;
+    int8_t* aq = (int8_t*)d->ws_att;
+    __half* ad = (__half*)((unsigned char*)d->ws_att + nq);
+    int8_t* vq = (int8_t*)d->ws_v;
+    __half* vd = (__half*)((unsigned char*)d->ws_v + F);
 
     // attention shared memory: probabilities, q / new k / new v / out, reductions, staged K and V rows
     const size_t att_fixed = ((size_t)d->max_seq + 4 * hd + 68) * 4;
@@ -778,81 +618,70 @@ extern "C" int lt_decode_step_pdl(const lt_decode_desc* d, void* stream) {
                            (size_t)64 * ((E + (E >> 4) + 15) & ~15);
     LT_REQUIRE(gu_smem <= (size_t)smem_max, "lt_decode_step_pdl: gate|up block does not fit shared memory (E=%d)", E);
 
-    // tags relative to the step's base: data produced in layer l carries l; the embedding row
-    // of a device-token step is written with the absolute tag 0 and never polled
-    for (int il = 0; il < L; il++) {
+    for (int il = 0; il < d->n_layers; il++) {
         const lt_decode_layer* ly = d->h_layers + il;
         int rc;
         {   // q|k|v
             FusedArgs a = {};
             a.Wq = ly->qkv_q; a.Wd = (const __half*)ly->qkv_d; a.M = nqkv; a.K = E;
-            a.normw = ly->attn_norm; a.eps = d->eps; a.bias = ly->qkv_bias; a.out = qkv; a.out_tag_off = (unsigned)il;
-            a.epoch = d->epoch; a.n_layers = L; a.status = status;
-            if (il > 0) {
-                a.x_tagged = x; a.in_tag_off = (unsigned)(il - 1);
-                rc = launch_pdl(k_fused_gemv<1>, a, (nqkv + 7) / 8, 256, gemv_smem(E, true), s, "lt_decode_step_pdl(qkv)");
-            } else if (d->tok != nullptr) {
+            a.normw = ly->attn_norm; a.eps = d->eps; a.add = ly->qkv_bias; a.out = qkv; a.status = status;
+            if (il == 0 && d->tok != nullptr) {
                 a.tok = d->tok; a.emb_q = d->emb_q; a.emb_d = (const __half*)d->emb_d; a.V = d->V; a.x_copy = x;
-                rc = launch_pdl(k_fused_gemv<3>, a, (nqkv + 7) / 8, 256, gemv_smem(E, true), s, "lt_decode_step_pdl(qkv)");
-            } else {
-                a.x_plain = d->x;
                 rc = launch_pdl(k_fused_gemv<2>, a, (nqkv + 7) / 8, 256, gemv_smem(E, true), s, "lt_decode_step_pdl(qkv)");
+            } else {
+                a.x = (il == 0) ? d->x : x;
+                rc = launch_pdl(k_fused_gemv<1>, a, (nqkv + 7) / 8, 256, gemv_smem(E, true), s, "lt_decode_step_pdl(qkv)");
             }
             if (rc != LT_OK) return rc;
         }
         {   // attention
             AttnArgs a = {};
-            a.qkv_tagged = qkv; a.kcache = ly->kcache; a.vcache = ly->vcache; a.len = ly->len; a.att_tagged = att;
+            a.qkv = qkv; a.kcache = ly->kcache; a.vcache = ly->vcache; a.len = ly->len; a.aq = aq; a.ad = ad;
             a.hd = hd; a.nh = d->nh; a.nkv = d->nkv; a.maxt = d->max_seq; a.vcap = vcap; a.theta = d->theta;
-            a.scale = d->scale; a.tag_off = (unsigned)il; a.epoch = d->epoch; a.n_layers = L; a.status = status;
+            a.scale = d->scale; a.status = status;
             rc = launch_pdl(k_fused_attn, a, d->nh, 256, att_smem, s, "lt_decode_step_pdl(attn)");
             if (rc != LT_OK) return rc;
         }
         {   // o_proj + residual (x, or the input row for layer 0 in host mode)
             FusedArgs a = {};
-            a.Wq = ly->o_q; a.Wd = (const __half*)ly->o_d; a.M = E; a.K = nq; a.xq_tagged = att; a.in_tag_off = (unsigned)il;
-            if (il == 0 && d->tok == nullptr) a.resid_plain = d->x; else a.resid_tagged = x;
-            a.out = x1; a.out_tag_off = (unsigned)il; a.len_incr = ly->len; a.max_seq = d->max_seq;
-            a.epoch = d->epoch; a.n_layers = L; a.status = status;
+            a.Wq = ly->o_q; a.Wd = (const __half*)ly->o_d; a.M = E; a.K = nq; a.xq = aq; a.xd = ad;
+            a.add = (il == 0 && d->tok == nullptr) ? d->x : x; a.out = x1; a.len_incr = ly->len; a.max_seq = d->max_seq;
+            a.status = status;
             rc = launch_pdl(k_fused_gemv<0>, a, (E + 7) / 8, 256, gemv_smem(nq, false), s, "lt_decode_step_pdl(o)");
             if (rc != LT_OK) return rc;
         }
         {   // gate|up -> quantised silu(gate)*up
             GateUpArgs a = {};
-            a.Wq = ly->gu_q; a.Wd = (const __half*)ly->gu_d; a.F = F; a.K = E; a.x_tagged = x1; a.normw = ly->ffn_norm;
-            a.eps = d->eps; a.vq_tagged = vq; a.tag_off = (unsigned)il; a.epoch = d->epoch; a.n_layers = L; a.status = status;
+            a.Wq = ly->gu_q; a.Wd = (const __half*)ly->gu_d; a.F = F; a.K = E; a.x = x1; a.normw = ly->ffn_norm;
+            a.eps = d->eps; a.vq = vq; a.vd = vd;
             rc = launch_pdl(k_fused_gateup, a, F / 32, 512, gu_smem, s, "lt_decode_step_pdl(gateup)");
             if (rc != LT_OK) return rc;
         }
         {   // down + residual
             FusedArgs a = {};
-            a.Wq = ly->down_q; a.Wd = (const __half*)ly->down_d; a.M = E; a.K = F; a.xq_tagged = vq; a.in_tag_off = (unsigned)il;
-            a.resid_tagged = x1; a.out = x; a.out_tag_off = (unsigned)il;
-            a.epoch = d->epoch; a.n_layers = L; a.status = status;
+            a.Wq = ly->down_q; a.Wd = (const __half*)ly->down_d; a.M = E; a.K = F; a.xq = vq; a.xd = vd; a.add = x1;
+            a.out = x; a.status = status;
             rc = launch_pdl(k_fused_gemv<0>, a, (E + 7) / 8, 256, gemv_smem(F, false), s, "lt_decode_step_pdl(down)");
             if (rc != LT_OK) return rc;
         }
     }
     {
         LmArgs a = {};
-        a.Wq = d->lm_q; a.Wd = (const __half*)d->lm_d; a.V = d->V; a.K = E; a.x_tagged = x; a.normw = d->out_norm;
-        a.eps = d->eps; a.logits = d->logits; a.part_val = (float2*)d->part_val; a.part_idx = (uint2*)d->part_idx;
-        a.epoch = d->epoch; a.n_layers = L; a.status = status;
+        a.Wq = d->lm_q; a.Wd = (const __half*)d->lm_d; a.V = d->V; a.K = E; a.x = x; a.normw = d->out_norm; a.eps = d->eps;
+        a.logits = d->logits; a.part_val = d->part_val; a.part_idx = d->part_idx;
         const int grid = sms * 4;
         const size_t smem = (((size_t)E + (E >> 5) * 2 + 15) & ~(size_t)15) + 272 * 4 + (size_t)2 * E * 4;
         int rc = launch_pdl(k_fused_lmhead, a, grid, 256, smem, s, "lt_decode_step_pdl(lm)");
         if (rc != LT_OK) return rc;
         FinalArgs f = {};
-        f.part_val = (const float2*)d->part_val; f.part_idx = (const uint2*)d->part_idx; f.nparts = grid;
-        f.out_tok = d->out_tok; f.tok = d->tok; f.history = d->history; f.step = d->step; f.hist_cap = d->hist_cap;
-        f.epoch = d->epoch; f.n_layers = L; f.status = status;
+        f.part_val = d->part_val; f.part_idx = d->part_idx; f.nparts = grid; f.out_tok = d->out_tok; f.tok = d->tok;
+        f.history = d->history; f.step = d->step; f.hist_cap = d->hist_cap;
         rc = launch_pdl(k_fused_argmax, f, 1, 256, 0, s, "lt_decode_step_pdl(argmax)");
         if (rc != LT_OK) return rc;
     }
     return LT_OK;
 }
 
-/* entries that part_val / part_idx need for lt_decode_step_pdl: 8 bytes each */
 extern "C" int lt_decode_pdl_num_parts(void) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;

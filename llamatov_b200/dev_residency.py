@@ -753,8 +753,8 @@ class FusedDecodeStep:
         if tok_ptr is not None:
             eq, ed, _, _ = _weights(_np(w["token_embd.weight"]))
         nq, nk = nh * hd, nkv * hd
-        # partial-argmax slots: one per CTA of the persistent kernel, or 8-byte tagged words per LM-head CTA
-        nct = max(_lib.lib().lt_decode_num_ctas(), 2 * _lib.lib().lt_decode_pdl_num_parts())
+        # partial-argmax slots: one per CTA of the persistent kernel / per CTA of the fused LM-head kernel
+        nct = max(_lib.lib().lt_decode_num_ctas(), _lib.lib().lt_decode_pdl_num_parts())
         f32 = dict(dtype=torch.float32, device="cuda")
         # tagged workspaces: {value, tag} pairs, zero tags = "never written"
         self.ws = [torch.zeros(2 * n, **f32) for n in (E, E, nq + 2 * nk, nq, F)]
