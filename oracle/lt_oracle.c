@@ -270,8 +270,10 @@ void lto_rope(float* X, const int* pos, int nrows, int n_head, int hd, float the
                 float c = cosf(ang), s = sinf(ang);
                 long base = row * n_head * hd + (long)head * hd;
                 float x1 = X[base + j], x2 = X[base + j + half];
+                /* contraction of the reference kernel as nvcc compiles it for sm_100a
+                 * (checked against the reference's own kernel on the GPU) */
                 X[base + j] = fmaf(x1, c, -(x2 * s));
-                X[base + j + half] = fmaf(x1, s, x2 * c);
+                X[base + j + half] = fmaf(x2, c, x1 * s);
             }
 }
 
