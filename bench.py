@@ -45,9 +45,9 @@ PROMPT_LEN = 32
 METRIC = "decode tok/s (0.5B Q8_0, bs1)"
 UNIT = "tok/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMV kernel from an ncu
-# capture (profiles/), keyed by (M, K); None until captured.
-NCU_TRAFFIC = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE token's launches, from an ncu capture of
+# this very command (profiles/decode_step_qwen05b.md), keyed by step mode; None where not captured.
+NCU_TRAFFIC = {"pdl": 530232064}
 
 
 def _peaks():
@@ -267,49 +267,48 @@ def main():
     status = _lib.device_status()
     tokens_match = (dev_tokens == e2e_tokens)
 
-    # ---- roofline of the GEMV kernel: a captured chain of exactly one token's GEMV launches
-    chain = []          # (dWq, dWd, M, K)
-    for il, ly in enumerate(model["layers"]):
-        for name in ("qkv", "o", "gateup", "down"):
-            q8 = ly[name]
-            dWq, dWd, N_, K_ = dr._weights(q8 if name in ("o", "down") else
-                                           (dr._fused_qkv_weight(w, f"blk.{il}")[0] if name == "qkv"
-                                            else dr._fused_gateup_weight(w, f"blk.{il}")[0]))
-            chain.append((dWq, dWd, N_, K_))
+    # ---- roofline.  The step is one chain of kernels whose job is to stream every weight once:
+    # algorithmic bytes per token = 34 B per 32 weights of every matrix + the fp32 KV rows read
+    # once per KV head (at the middle position of the timed run), over the device time per token
+    # measured above with CUDA events on the replay stream.
+    nq = mc["n_head"] * mc["hd"]; nk = mc["n_head_kv"] * mc["hd"]
+    weight_bytes = sum(M_ * (K_ // 32) * 34 * n_ for (M_, K_, n_) in gemv_shapes(mc))
+    mid_len = PROMPT_LEN + W + K // 2
+    kv_bytes = mc["n_layers"] * 2 * mid_len * nk * 4
+    step_bytes = weight_bytes + kv_bytes
+    peak, peak_src = _peaks()
+    achieved = step_bytes / (dev_ms / K * 1e-3) / 1e9
+    # the one launch of the chain that is bandwidth-bound by itself: the LM-head GEMV, timed alone
+    # (its 145 MB exceed L2, so every launch streams from HBM)
     dWq, dWd, N_, K_ = dr._weights(dr._lm_head(w))
-    chain.append((dWq, dWd, N_, K_))
-    maxK = max(c[3] for c in chain); maxM = max(c[2] for c in chain)
-    xq = torch.randint(-127, 128, (maxK,), dtype=torch.int8, device="cuda")
-    xd = torch.full((maxK // 32,), 0x2000, dtype=torch.int16, device="cuda")
-    ybuf = torch.empty(maxM, dtype=torch.float32, device="cuda")
-    g2 = torch.cuda.CUDAGraph()
+    xq = torch.randint(-127, 128, (K_,), dtype=torch.int8, device="cuda")
+    xd = torch.full((K_ // 32,), 0x2000, dtype=torch.int16, device="cuda")
+    ybuf = torch.empty(N_, dtype=torch.float32, device="cuda")
     s2 = torch.cuda.Stream()
     torch.cuda.synchronize()
-    with torch.cuda.graph(g2, stream=s2):
-        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        for (a, b, M_, Kk) in chain:
-            _lib.call("lt_q8_gemv", a, b, xq.data_ptr(), xd.data_ptr(), None, ybuf.data_ptr(), M_, Kk, 1, st)
     with torch.cuda.stream(s2):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         for _ in range(W):
-            g2.replay()
+            _lib.call("lt_q8_gemv", dWq, dWd, xq.data_ptr(), xd.data_ptr(), None, ybuf.data_ptr(), N_, K_, 1, st)
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(K):
-            g2.replay()
+        for _ in range(20):
+            _lib.call("lt_q8_gemv", dWq, dWd, xq.data_ptr(), xd.data_ptr(), None, ybuf.data_ptr(), N_, K_, 1, st)
         e1.record()
     torch.cuda.synchronize()
-    gemv_ms_per_token = e0.elapsed_time(e1) / K
-    n_gemv = len(chain)
-    gemv_bytes_token = sum(gemv_bytes(M_, Kk) for (_, _, M_, Kk) in chain)
-    peak, peak_src = _peaks()
-    achieved = gemv_bytes_token / (gemv_ms_per_token * 1e-3) / 1e9
+    lm_us = 1000.0 * e0.elapsed_time(e1) / 20
+    lm_gbs = gemv_bytes(N_, K_) / (lm_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC.get("per_token"),
-                "kernel": "lt::k_q8_gemv<4,1>", "launches_per_token": n_gemv,
-                "bytes_per_launch_avg": gemv_bytes_token / n_gemv,
-                "us_per_launch_avg": 1000.0 * gemv_ms_per_token / n_gemv,
+                "traffic": NCU_TRAFFIC.get(dr._FUSED_STEP if dr._FUSED_STEP else "per-op"),
+                "kernel": "decode step = %d launches per token (%s)" % (
+                    gr.launches_per_step, "k_fused_gemv, k_fused_gateup, k_fused_attn, k_fused_lmhead, k_fused_argmax"
+                    if dr._FUSED_STEP == "pdl" else ("k_decode_step" if dr._FUSED_STEP else "per-op kernels")),
+                "algorithmic_bytes_per_launch": step_bytes / max(1, gr.launches_per_step),
+                "algorithmic_bytes_per_token": step_bytes,
+                "us_per_token": 1000.0 * dev_ms / K,
                 "peak_source": peak_src,
-                "token_frac": (gemv_bytes_token / (dev_ms / K * 1e-3) / 1e9) / peak}
+                "lm_head_gemv_alone": {"kernel": "lt::k_q8_gemv<4,1>", "shape": [N_, K_], "us": lm_us,
+                                       "achieved": lm_gbs, "frac": lm_gbs / peak}}
 
     value = world * K / (dev_ms * 1e-3)
     e2e_val = world * K / (e2e_ms * 1e-3)
