@@ -79,6 +79,18 @@ int lt_add(const float* a, const float* b, float* y, int n, void* stream);
 int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
                const float* Resid, float* Y, int M, int K, int T, void* stream);
 
+/* The same contract (same lane fold, same tree, bit-identical results) for wider activation
+ * batches, with the integer block dots on the tensor cores: one tcgen05.mma kind::i8 per Q8_0
+ * block gives the int32 sums of 128 weight rows x one tile of columns in tensor memory, the
+ * fp32 scale-and-fold runs in the frozen order on the CUDA cores.  This is the batched form the
+ * reference does not have (its prefill loops the per-token GEMV and requires batched results to
+ * equal the per-token ones, bpd/lib/dev_residency.py:1344-1350).  K must be a multiple of 128.
+ * variant: 0 = choose by T; 1 = 16-column tiles, 128-byte weight chunks (streams the matrix once,
+ * for decode batches); 2 = 32-column tiles, 32-byte chunks (fewer live partials, for prefill).
+ * lt_q8_gemv forwards to this entry for T > 8 when K allows it. */
+int lt_q8_gemm_tc(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                  const float* Resid, float* Y, int M, int K, int T, int variant, void* stream);
+
 /* ---- RMSNorm --------------------------------------------------------------------------
  * replaces k_rmsnorm, mode block_row (bpd/kernelgen/emitters/norm_softmax_from_facts.pl:83-108;
  * launched from bpd/lib/dev_residency.py:757-781): 256 strided lanes fold fma(x,x,.), 8-level

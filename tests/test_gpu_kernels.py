@@ -106,6 +106,29 @@ def test_skinny_gemm_bit_exact(oracle, M, K, T):
     assert np.array_equal(bits(y), bits(want))
 
 
+def gpu_gemm_tc(dWq, dWd, dXq, dXd, M, K, T, variant, resid=None):
+    y = torch.full((T * M,), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.call("lt_q8_gemm_tc", dWq.data_ptr(), dWd.data_ptr(), dXq.data_ptr(), dXd.data_ptr(),
+              None if resid is None else resid.data_ptr(), y.data_ptr(), M, K, T, variant, stream())
+    return y
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("M,K,T", [(128, 128, 16), (128, 896, 16), (896, 896, 64), (300, 4864, 33), (1152, 896, 70),
+                                   (256, 4096, 5), (200, 14336, 17), (4864, 896, 257)])
+def test_tensor_core_gemm_bit_exact(oracle, M, K, T, variant):
+    Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=T + variant)
+    xq, xd = gpu_quant(x, rows=T)
+    r = np.random.default_rng(2).standard_normal(M).astype(np.float32)
+    dWq, dWd = dev(Wq), dev(Wd)
+    want = oracle.q8_gemm(Wq, Wd, host(xq), host(xd, np.uint16), M, K, T)
+    y = host(gpu_gemm_tc(dWq, dWd, xq, xd, M, K, T, variant)).reshape(T, M)
+    assert np.array_equal(bits(y), bits(want))
+    y = host(gpu_gemm_tc(dWq, dWd, xq, xd, M, K, T, variant, resid=dev(r))).reshape(T, M)
+    assert np.array_equal(bits(y), bits(want + r[None, :]))
+    assert _lib.device_status() == set()
+
+
 def test_gemv_linearity_full_size():
     # size-independent property at the LM-head size: W(x1 quantised) + W(x2 quantised) rows are
     # independent of which other rows are computed (row-slice consistency), and the result does
