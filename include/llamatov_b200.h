@@ -85,11 +85,15 @@ int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uin
  * fp32 scale-and-fold runs in the frozen order on the CUDA cores.  This is the batched form the
  * reference does not have (its prefill loops the per-token GEMV and requires batched results to
  * equal the per-token ones, bpd/lib/dev_residency.py:1344-1350).  K must be a multiple of 128.
- * variant: 0 = choose by T; 1 = 16-column tiles, 128-byte weight chunks (streams the matrix once,
- * for decode batches); 2 = 32-column tiles, 32-byte chunks (fewer live partials, for prefill).
+ * variant: 0 = default (1); 1 = 16-column tiles, 128-byte weight chunks, 8 epilogue warps (the matrix
+ * streams once from HBM in 128-byte rows; fastest measured at every width); 2 = 32-column tiles,
+ * 32-byte chunks (fewest live partials per thread); 3 = as 1 with 16 epilogue warps.
+ * Resid: NULL, or a bias of M entries added to every column (resid_ld = 0), or one row per
+ * column, Resid[t * resid_ld + n] (the residual stream of a prefill; Y may then alias Resid).
  * lt_q8_gemv forwards to this entry for T > 8 when K allows it. */
 int lt_q8_gemm_tc(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
-                  const float* Resid, float* Y, int M, int K, int T, int variant, void* stream);
+                  const float* Resid, int resid_ld, float* Y, int M, int K, int T, int variant,
+                  void* stream);
 
 /* ---- RMSNorm --------------------------------------------------------------------------
  * replaces k_rmsnorm, mode block_row (bpd/kernelgen/emitters/norm_softmax_from_facts.pl:83-108;

@@ -21,8 +21,8 @@
 //
 // Pipeline per CTA (persistent over tiles of 128 rows x NT columns):
 //   warp EW   : producer, TMA tiled loads (hardware swizzle) of weight and activation chunks
-//               into a ring of shared-memory stages; a stage = UB blocks
-//   warp EW+1 : one thread issues the MMAs of a stage into a ring of TMEM slots and commits
+//               into a ring of shared-memory stages; a stage = one chunk of CB blocks
+//   warp EW+1 : one thread issues the CB MMAs of a stage into a ring of TMEM slots and commits
 //   warps 0..EW-1 : epilogue, TMEM -> registers -> fp32 fold -> Y
 // Every wait is bounded: after the limit a CTA sets LT_STATUS_WAIT_TIMEOUT, all its later waits
 // return at once, it drains and frees its tensor memory.
@@ -34,8 +34,6 @@ namespace lt {
 namespace tc {
 
 constexpr int TM = 128;          // weight rows per tile (MMA M, TMEM lanes)
-constexpr int UB = 4;            // Q8_0 blocks per pipeline unit (stage / TMEM slot)
-constexpr int NSTAGE = 4;        // shared-memory stages
 constexpr int TMEM_COLS = 256;   // allocated tensor-memory columns (two CTAs may share an SM)
 constexpr long long WAIT_LIMIT = 3000000000LL;  // SM clocks (> 1 s) before a wait gives up
 
@@ -64,11 +62,22 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 
 // Bounded wait.  *abort_flag (shared) is set by the first wait of the CTA that runs out of time;
 // from then on every wait returns immediately so that all roles run to the end of their loops.
+#ifdef LT_TC_PROF
+__device__ long long g_tc_prof[8];   // waits: 0 producer/empty, 1 mma/full, 2 mma/tempty, 3 epilogue/tfull, 4 kernel clocks
+#define LT_PROF_T0() const long long prof_t0 = clock64()
+#define LT_PROF_ADD(slot) atomicAdd((unsigned long long*)&g_tc_prof[slot], (unsigned long long)(clock64() - prof_t0))
+#else
+#define LT_PROF_T0()
+#define LT_PROF_ADD(slot)
+#endif
+
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                           int* status) {
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (*abort_flag) return;
         if (clock64() - t0 > WAIT_LIMIT) {
             *abort_flag = 1;
@@ -94,9 +103,9 @@ __device__ __forceinline__ void mma_i8(unsigned d_tmem, unsigned long long adesc
                                        unsigned idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u)
+        "l"(adesc), "l"(bdesc), "r"(idesc)
         : "memory");
 }
 __device__ __forceinline__ void mma_commit(unsigned long long* bar) {
@@ -117,6 +126,12 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
 template <int CW>
 __device__ __forceinline__ void tmem_ld(unsigned taddr, int (&v)[CW]);
 template <>
+__device__ __forceinline__ void tmem_ld<4>(unsigned taddr, int (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr));
+}
+template <>
 __device__ __forceinline__ void tmem_ld<8>(unsigned taddr, int (&v)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
@@ -130,7 +145,20 @@ __device__ __forceinline__ void tmem_ld<16>(unsigned taddr, int (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Completes the TMEM loads of this thread.  The loaded registers are passed through the
+// statement (eight at a time) so that no use of them can be scheduled above the wait.
+__device__ __forceinline__ void reg_fence4(int* v) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3])::"memory");
+}
+template <int N, int CB, int CW>
+__device__ __forceinline__ void tmem_ld_wait(int (&v)[CB][CW]) {
+    static_assert(N == CB * CW && CW % 4 == 0, "register count");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < CB; i++)
+#pragma unroll
+        for (int c = 0; c < CW; c += 4) reg_fence4(&v[i][c]);
+}
 
 constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v >> 1); }
 
@@ -142,6 +170,7 @@ struct Params {
     int* status;
     int M, K, T;
     int row_tiles, t_tiles;
+    int resid_ld;   // 0: Resid[n] for every column (bias); else Resid[t * resid_ld + n]
 };
 
 template <int NT, int CB, int EW>
@@ -149,35 +178,38 @@ struct Cfg {
     static constexpr int CW = NT * 4 / EW;             // columns per epilogue thread
     static constexpr int G = 32 / CB;                  // lane groups
     static constexpr int LV = ilog2(G);                // stack depth
-    static constexpr int THREADS = (EW + 2) * 32;
-    static constexpr int W_STAGE = UB * TM * 32;       // bytes
-    static constexpr int X_STAGE = UB * NT * 32;
-    static constexpr int SLOT_COLS = UB * NT;
+    static constexpr int MW = 2;                       // MMA-issuing warps
+    static constexpr int THREADS = (EW + 1 + MW) * 32;
+    static constexpr int W_STAGE = CB * TM * 32;       // bytes: one stage = one chunk of CB blocks
+    static constexpr int X_STAGE = CB * NT * 32;
+    static constexpr int STAGE = W_STAGE + ((X_STAGE + 1023) / 1024) * 1024;
+    static constexpr int NSTAGE = CB == 4 ? 4 : (CB == 2 ? 6 : 8);
+    static constexpr int SLOT_COLS = CB * NT;
     static constexpr int NSLOT = TMEM_COLS / SLOT_COLS;
-    static_assert(EW % 4 == 0 && (CW == 8 || CW == 16), "epilogue shape");
-    static_assert(NSLOT >= 2, "at least two TMEM slots");
-    static_assert(X_STAGE % 1024 == 0, "activation stage keeps 1024-byte alignment");
+    static constexpr int LB = CB * CW <= 16 ? CB : (CB >= 2 && CW <= 8 ? 2 : 1);   // blocks per TMEM round trip
+    static_assert(EW % 4 == 0 && (CW == 4 || CW == 8 || CW == 16), "epilogue shape");
+    static_assert(NSLOT >= 2 && NSLOT <= 16 && (NSLOT & (NSLOT - 1)) == 0, "TMEM slots");
+    static_assert(W_STAGE % 1024 == 0, "stages keep 1024-byte alignment");
 };
 
 struct Barriers {
-    unsigned long long full[NSTAGE], empty[NSTAGE];
-    unsigned long long tfull[8], tempty[8];
+    unsigned long long full[8], empty[8];
+    unsigned long long tfull[16], tempty[16];
     unsigned tmem_base;
     int abort_flag;
+    int next_start[32];   // per visiting position: first block of the next group that has blocks, -1 = none
 };
 
 template <int NT, int CB, int EW>
 __global__ void __launch_bounds__(Cfg<NT, CB, EW>::THREADS, 1)
 k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params P) {
     using C = Cfg<NT, CB, EW>;
-    constexpr int CW = C::CW, G = C::G, LV = C::LV, NSLOT = C::NSLOT;
+    constexpr int CW = C::CW, G = C::G, LV = C::LV, NSLOT = C::NSLOT, NSTAGE = C::NSTAGE, LB = C::LB, MW = C::MW;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // 1024-byte aligned carve-up: weight stages, activation stages, barriers, activation scales
+    // 1024-byte aligned carve-up: stages (weights, then activations), barriers, activation scales
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sW = base;
-    unsigned char* sX = sW + NSTAGE * C::W_STAGE;
-    Barriers* B = (Barriers*)(sX + NSTAGE * C::X_STAGE);
-    float* xs = (float*)((unsigned char*)B + 256);
+    Barriers* B = (Barriers*)(base + NSTAGE * C::STAGE);
+    float* xs = (float*)((unsigned char*)B + 1024);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = P.K >> 5;
@@ -194,6 +226,14 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             mbar_init(&B->tempty[s], EW);
         }
         B->abort_flag = 0;
+        for (int gi = 0; gi < G; gi++) {
+            int nxt = -1;
+            for (int gj = gi + 1; gj < G && nxt < 0; gj++) {
+                const int b0 = CB * (int)(__brev((unsigned)gj) >> (32 - LV));
+                if (b0 < nb) nxt = b0;
+            }
+            B->next_start[gi] = nxt;
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -207,89 +247,105 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = B->tmem_base;
+#ifdef LT_TC_PROF
+    const long long prof_k0 = clock64();
+#endif
 
+    // chunks per tile: groups in bit-reversed order, rounds ascending; identical in all three roles
     if (warp == EW) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            unsigned it = 0;   // units issued
+            unsigned it = 0;   // chunks issued
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
                 const int rt = tile / P.t_tiles, tt = tile - rt * P.t_tiles;
                 const int row0 = rt * TM, t0 = tt * NT;
-                if (CB == UB) {
-                    for (int gi = 0; gi < G; gi++) {
-                        const int g = (int)(__brev((unsigned)gi) >> (32 - LV));
-                        for (int b0 = CB * g; b0 < nb; b0 += 32) {
-                            const int s = it % NSTAGE;
-                            mbar_wait(&B->empty[s], ((it / NSTAGE) & 1) ^ 1, abort_flag, P.status);
-                            mbar_expect_tx(&B->full[s], C::W_STAGE + C::X_STAGE);
-                            tma_load_2d(sW + s * C::W_STAGE, &tmW, b0 * 32, row0, &B->full[s]);
-                            tma_load_2d(sX + s * C::X_STAGE, &tmX, b0 * 32, t0, &B->full[s]);
-                            it++;
+                for (int gi = 0; gi < G; gi++) {
+                    const int g = (int)(__brev((unsigned)gi) >> (32 - LV));
+                    for (int b0 = CB * g; b0 < nb; b0 += 32, it++) {
+                        const int s = it % NSTAGE;
+                        unsigned char* st = base + s * C::STAGE;
+                        {
+                            LT_PROF_T0();
+                            mbar_wait<64>(&B->empty[s], ((it / NSTAGE) & 1) ^ 1, abort_flag, P.status);
+                            LT_PROF_ADD(0);
                         }
-                    }
-                } else {
-                    // CB == 1: a unit gathers the next UB blocks of the visiting order
-                    int pos = 0, left = nb;
-                    for (int gi = 0; gi < G; gi++) {
-                        const int g = (int)(__brev((unsigned)gi) >> (32 - LV));
-                        for (int b = g; b < nb; b += 32) {
-                            const int s = it % NSTAGE;
-                            if (pos == 0) {
-                                const int cnt = left < UB ? left : UB;
-                                mbar_wait(&B->empty[s], ((it / NSTAGE) & 1) ^ 1, abort_flag, P.status);
-                                mbar_expect_tx(&B->full[s], cnt * (TM * 32 + NT * 32));
-                            }
-                            tma_load_2d(sW + s * C::W_STAGE + pos * (TM * 32), &tmW, b * 32, row0, &B->full[s]);
-                            tma_load_2d(sX + s * C::X_STAGE + pos * (NT * 32), &tmX, b * 32, t0, &B->full[s]);
-                            left--;
-                            if (++pos == UB || left == 0) {
-                                pos = 0;
-                                it++;
-                            }
-                        }
+                        mbar_expect_tx(&B->full[s], C::W_STAGE + C::X_STAGE);
+                        tma_load_2d(st, &tmW, b0 * 32, row0, &B->full[s]);
+                        tma_load_2d(st + C::W_STAGE, &tmX, b0 * 32, t0, &B->full[s]);
                     }
                 }
             }
         }
-    } else if (warp == EW + 1) {
+    } else if (warp >= EW + 1) {
         // ------------------------------------------------------------------ MMA issue
+        // MW warps share the chunks round-robin (a chunk has its own stage and slot, so the warps
+        // are independent); issuing, not the tensor pipe, limits these small MMAs.
         if (lane == 0) {
             // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = NT, M = 128
             constexpr unsigned idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(NT >> 3) << 17) |
                                        ((unsigned)(TM >> 4) << 24);
-            unsigned it = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const int units = (nb + UB - 1) / UB;
-                for (int u = 0; u < units; u++, it++) {
-                    const int s = it % NSTAGE, slot = it % NSLOT;
-                    const int cnt = (nb - u * UB) < UB ? (nb - u * UB) : UB;
-                    mbar_wait(&B->full[s], (it / NSTAGE) & 1, abort_flag, P.status);
-                    mbar_wait(&B->tempty[slot], ((it / NSLOT) & 1) ^ 1, abort_flag, P.status);
-                    tc_fence_after();
-                    const unsigned wbase = smem_u32(sW + s * C::W_STAGE), xbase = smem_u32(sX + s * C::X_STAGE);
-                    for (int i = 0; i < cnt; i++) {
-                        // CB == UB: block i is the i-th 32-byte slice of the swizzled 128-byte rows;
-                        // CB == 1: block i is its own 32-byte-swizzled tile
-                        const unsigned wa = CB == UB ? wbase + i * 32 : wbase + i * (TM * 32);
-                        const unsigned xa = CB == UB ? xbase + i * 32 : xbase + i * (NT * 32);
-                        mma_i8(tmem + slot * C::SLOT_COLS + i * NT, smem_desc<CB>(wa), smem_desc<CB>(xa), idesc);
-                    }
-                    mma_commit(&B->empty[s]);     // the stage may be refilled once these MMAs have read it
-                    mma_commit(&B->tfull[slot]);  // and the slot holds the block sums
+            const unsigned long long wdesc0 = smem_desc<CB>(smem_u32(base));
+            const unsigned long long xdesc0 = smem_desc<CB>(smem_u32(base) + C::W_STAGE);
+            const unsigned chunks = (unsigned)(nb / CB);
+            int my_tiles = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) my_tiles++;
+            const unsigned total = (unsigned)my_tiles * chunks;
+            for (unsigned it = (unsigned)(warp - (EW + 1)); it < total; it += MW) {
+                const unsigned s = it % NSTAGE, slot = it % NSLOT;
+                {
+                    LT_PROF_T0();
+                    mbar_wait<32>(&B->full[s], (it / NSTAGE) & 1, abort_flag, P.status);
+                    LT_PROF_ADD(1);
                 }
+                {
+                    LT_PROF_T0();
+                    mbar_wait<32>(&B->tempty[slot], ((it / NSLOT) & 1) ^ 1, abort_flag, P.status);
+                    LT_PROF_ADD(2);
+                }
+                tc_fence_after();
+                // descriptors differ from the first stage's only in the start address (16-byte units)
+                const unsigned long long wd0 = wdesc0 + (unsigned long long)(s * (C::STAGE >> 4));
+                const unsigned long long xd0 = xdesc0 + (unsigned long long)(s * (C::STAGE >> 4));
+                const unsigned d0 = tmem + slot * C::SLOT_COLS;
+#pragma unroll
+                for (int i = 0; i < CB; i++)   // block i = the i-th 32-byte slice of the swizzled rows
+                    mma_i8(d0 + i * NT, wd0 + 2 * i, xd0 + 2 * i, idesc);
+                mma_commit(&B->empty[s]);     // the stage may be refilled once these MMAs have read it
+                mma_commit(&B->tfull[slot]);  // and the slot holds the block sums
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
+        // A thread walks its row's blocks in the visiting order.  While it folds a block, the
+        // TMEM load of the next block and the global load of the next weight scales are in flight.
         const int q = warp & 3, cg = warp >> 2;
         const int col0 = cg * CW;
-        const unsigned lane_addr = ((unsigned)(q * 32) << 16);
-        unsigned it = 0;       // units consumed
+        const unsigned lane_addr = ((unsigned)(q * 32) << 16) + (unsigned)col0;
+        int my_tiles = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) my_tiles++;
+        const unsigned total = (unsigned)my_tiles * (unsigned)(nb / CB);   // chunks this thread consumes
+        unsigned it = 0;                                                   // chunks consumed so far
+        auto scale_row = [&](int tile) {   // this thread's row of weight scales in a tile (row 0 if out of range)
+            int r = (tile / P.t_tiles) * TM + q * 32 + lane;
+            if (r >= P.M) r = 0;
+            return P.Wd + (long)r * nb;
+        };
+        auto scales_at = [&](const __half* p) {   // the CB scales of blocks b .. b+CB-1
+            uint2 w = make_uint2(0u, 0u);
+            if (CB == 4) w = __ldg((const uint2*)p);
+            else if (CB == 2) w.x = __ldg((const unsigned*)p);
+            else w.x = __ldg((const unsigned short*)p);
+            return w;
+        };
+        uint2 wnext = make_uint2(0u, 0u);
+        if (total > 0) wnext = scales_at(scale_row(blockIdx.x));
+
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
             const int rt = tile / P.t_tiles, tt = tile - rt * P.t_tiles;
             const int row = rt * TM + q * 32 + lane, t0 = tt * NT;
             const bool row_ok = row < P.M;
-            const __half* wdrow = P.Wd + (long)(row_ok ? row : 0) * nb;
+            const __half* wdrow = scale_row(tile);
+            const __half* wdrow_next = scale_row(tile + gridDim.x < tiles ? tile + (int)gridDim.x : tile);
 
             // activation scales of this column tile: xs[b][c] = f32(Xd[t0 + c, b])
             asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
@@ -302,8 +358,6 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
 
             float stack[CB][LV > 0 ? LV : 1][CW];
             float fin[CB][CW];
-            int pos = 0;      // block position inside the current unit (CB == 1)
-            int left = nb;
 #pragma unroll
             for (int gi = 0; gi < G; gi++) {
                 const int g = (int)(__brev((unsigned)gi) >> (32 - LV));
@@ -314,41 +368,59 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     for (int c = 0; c < CW; c++) leaf[i][c] = 0.0f;
 
                 for (int b0 = CB * g; b0 < nb; b0 += 32) {
-#pragma unroll
-                    for (int i = 0; i < CB; i++) {
-                        const int b = b0 + i;
-                        const int slot = it % NSLOT;
-                        const int p = CB == UB ? i : pos;
-                        if (p == 0) {
-                            mbar_wait(&B->tfull[slot], (it / NSLOT) & 1, abort_flag, P.status);
-                            tc_fence_after();
+                    const uint2 wcur = wnext;
+                    {   // scales of the next chunk: next round of this group, else the next group that
+                        // has blocks, else the first chunk of the next tile
+                        const __half* np = wdrow + b0 + 32;
+                        if (b0 + 32 >= nb) {
+                            const int ns = B->next_start[gi];
+                            np = ns < 0 ? wdrow_next : wdrow + ns;
                         }
-                        int v[CW];
-                        tmem_ld<CW>(tmem + lane_addr + slot * C::SLOT_COLS + p * NT + col0, v);
-                        const float wd = __half2float(wdrow[b]);
-                        const float4* xp = (const float4*)(xs + b * NT + col0);
-                        float xd[CW];
+                        wnext = scales_at(np);
+                    }
+                    // all CB blocks of the chunk in one round trip to tensor memory
+                    const unsigned slot = it % NSLOT;
+                    const unsigned taddr = tmem + lane_addr + slot * C::SLOT_COLS;
+                    {
+                        LT_PROF_T0();
+                        mbar_wait(&B->tfull[slot], (it / NSLOT) & 1, abort_flag, P.status);
+#ifdef LT_TC_PROF
+                        if (tid == 0) LT_PROF_ADD(3);
+#endif
+                    }
+                    tc_fence_after();
 #pragma unroll
-                        for (int c4 = 0; c4 < CW / 4; c4++) {
-                            float4 x = xp[c4];
-                            xd[4 * c4] = x.x; xd[4 * c4 + 1] = x.y; xd[4 * c4 + 2] = x.z; xd[4 * c4 + 3] = x.w;
-                        }
-                        tmem_ld_wait();
+                    for (int h = 0; h < CB; h += LB) {   // LB blocks per round trip to tensor memory
+                        int v[LB][CW];
 #pragma unroll
-                        for (int c = 0; c < CW; c++) leaf[i][c] = q8_accum(wd, xd[c], v[c], leaf[i][c]);
-                        left--;
-                        bool unit_done;
-                        if (CB == UB) {
-                            unit_done = (i == CB - 1);
-                        } else {
-                            unit_done = (++pos == UB) || left == 0;
-                            if (unit_done) pos = 0;
-                        }
-                        if (unit_done) {
+                        for (int i = 0; i < LB; i++) tmem_ld<CW>(taddr + (h + i) * NT, v[i]);
+                        tmem_ld_wait<LB * CW>(v);
+                        if (h + LB == CB) {
+                            // the chunk's sums are in registers: hand the slot back to the MMA warp
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&B->tempty[slot]);
                             it++;
+                        }
+#pragma unroll
+                        for (int j = 0; j < LB; j++) {
+                            const int i = h + j;
+                            const unsigned short wbits =
+                                CB == 4 ? (unsigned short)((i < 2 ? wcur.x : wcur.y) >> ((i & 1) * 16))
+                                        : (unsigned short)(wcur.x >> ((i & 1) * 16));
+                            const float wd = __half2float(__ushort_as_half(wbits));
+                            const float4* xp = (const float4*)(xs + (b0 + i) * NT + col0);
+#pragma unroll
+                            for (int c4 = 0; c4 < CW / 4; c4++) {
+                                const float4 x = xp[c4];
+                                leaf[i][4 * c4] = __fmaf_rn(__fmul_rn(wd, x.x), (float)v[j][4 * c4], leaf[i][4 * c4]);
+                                leaf[i][4 * c4 + 1] =
+                                    __fmaf_rn(__fmul_rn(wd, x.y), (float)v[j][4 * c4 + 1], leaf[i][4 * c4 + 1]);
+                                leaf[i][4 * c4 + 2] =
+                                    __fmaf_rn(__fmul_rn(wd, x.z), (float)v[j][4 * c4 + 2], leaf[i][4 * c4 + 2]);
+                                leaf[i][4 * c4 + 3] =
+                                    __fmaf_rn(__fmul_rn(wd, x.w), (float)v[j][4 * c4 + 3], leaf[i][4 * c4 + 3]);
+                            }
                         }
                     }
                 }
@@ -384,13 +456,12 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     for (int c = 0; c < CW; c++) fin[i][c] = __fadd_rn(fin[i][c], fin[i + s][c]);
 
             if (row_ok) {
-                const float r = P.Resid != nullptr ? P.Resid[row] : 0.0f;
 #pragma unroll
                 for (int c = 0; c < CW; c++) {
                     const int t = t0 + col0 + c;
                     if (t < P.T) {
                         float y = fin[0][c];
-                        if (P.Resid != nullptr) y = __fadd_rn(y, r);
+                        if (P.Resid != nullptr) y = __fadd_rn(y, P.Resid[(long)t * P.resid_ld + row]);
                         P.Y[(long)t * P.M + row] = y;
                     }
                 }
@@ -399,6 +470,9 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     }
 
     // ---------------------------------------------------------------------- teardown
+#ifdef LT_TC_PROF
+    if (tid == 0) atomicAdd((unsigned long long*)&g_tc_prof[4], (unsigned long long)(clock64() - prof_k0));
+#endif
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && warp == EW && lane == 0) {
@@ -459,7 +533,7 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int box_k,
 
 template <int NT, int CB, int EW>
 static int launch(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, const float* Resid,
-                  float* Y, int M, int K, int T, cudaStream_t s) {
+                  int resid_ld, float* Y, int M, int K, int T, cudaStream_t s) {
     using C = Cfg<NT, CB, EW>;
     const int nb = K / 32;
     CUtensorMap tmW, tmX;
@@ -467,7 +541,7 @@ static int launch(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const 
     if (rc != LT_OK) return rc;
     rc = make_map(&tmX, Xq, T, K, CB * 32, NT);
     if (rc != LT_OK) return rc;
-    const size_t smem = 1024 + (size_t)NSTAGE * (C::W_STAGE + C::X_STAGE) + 256 + (size_t)nb * NT * 4;
+    const size_t smem = 1024 + (size_t)C::NSTAGE * C::STAGE + 1024 + (size_t)nb * NT * 4;
     LT_REQUIRE(smem <= 220 * 1024, "lt_q8_gemm_tc: K=%d needs %zu bytes of shared memory per CTA", K, smem);
     static bool attr_done = false;
     if (!attr_done) {
@@ -478,7 +552,7 @@ static int launch(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const 
     P.Wd = (const __half*)Wd; P.Xd = (const __half*)Xd; P.Resid = Resid; P.Y = Y;
     P.status = device_status_ptr();
     LT_REQUIRE(P.status != nullptr, "lt_q8_gemm_tc: status word unavailable");
-    P.M = M; P.K = K; P.T = T;
+    P.M = M; P.K = K; P.T = T; P.resid_ld = resid_ld;
     P.row_tiles = (M + TM - 1) / TM;
     P.t_tiles = (T + NT - 1) / NT;
     int dev = 0, sms = 148;
@@ -496,16 +570,29 @@ static int launch(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const 
 using namespace lt;
 
 extern "C" int lt_q8_gemm_tc(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
-                             const float* Resid, float* Y, int M, int K, int T, int variant, void* stream) {
+                             const float* Resid, int resid_ld, float* Y, int M, int K, int T, int variant,
+                             void* stream) {
     LT_REQUIRE(Wq && Wd && Xq && Xd && Y, "lt_q8_gemm_tc: null pointer");
     LT_REQUIRE(M > 0 && T > 0, "lt_q8_gemm_tc: M=%d T=%d must be positive", M, T);
     LT_REQUIRE(K > 0 && K % 128 == 0, "lt_q8_gemm_tc: K=%d must be a positive multiple of 128", K);
     LT_REQUIRE(aligned16(Wq) && aligned16(Xq), "lt_q8_gemm_tc: Wq and Xq must be 16-byte aligned");
-    LT_REQUIRE(Resid == nullptr || (const void*)Y != (const void*)Resid, "lt_q8_gemm_tc: Y must not alias Resid");
+    LT_REQUIRE(resid_ld == 0 || resid_ld >= M, "lt_q8_gemm_tc: resid_ld=%d must be 0 or at least M=%d", resid_ld, M);
+    LT_REQUIRE(Resid == nullptr || resid_ld != 0 || T == 1 || (const void*)Y != (const void*)Resid,
+               "lt_q8_gemm_tc: Y may alias Resid only when Resid has one row per column");
     cudaStream_t s = (cudaStream_t)stream;
-    if (variant == 0) variant = T <= 64 ? 1 : 2;
-    if (variant == 1) return tc::launch<16, 4, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
-    if (variant == 2) return tc::launch<32, 1, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    if (variant == 0) variant = 1;
+    if (variant == 1) return tc::launch<16, 4, 8>(Wq, Wd, Xq, Xd, Resid, resid_ld, Y, M, K, T, s);
+    if (variant == 2) return tc::launch<32, 1, 8>(Wq, Wd, Xq, Xd, Resid, resid_ld, Y, M, K, T, s);
+    if (variant == 3) return tc::launch<16, 4, 16>(Wq, Wd, Xq, Xd, Resid, resid_ld, Y, M, K, T, s);
     set_error("lt_q8_gemm_tc: unknown variant %d", variant);
     return LT_ERR_INVALID;
 }
+
+#ifdef LT_TC_PROF
+extern "C" int lt_tc_prof_read(long long* out8) {
+    cudaMemcpyFromSymbol(out8, lt::tc::g_tc_prof, sizeof(long long) * 8);
+    long long z[8] = {0};
+    cudaMemcpyToSymbol(lt::tc::g_tc_prof, z, sizeof(z));
+    return 0;
+}
+#endif

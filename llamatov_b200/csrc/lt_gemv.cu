@@ -192,7 +192,10 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
     if (T <= 2) return launch_gemv<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 4) return launch_gemv<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 8) return launch_gemv<2, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
-    // wider batches: chunks of up to 64 columns, each chunk one pass over the matrix
+    // wider batches: block dots on the tensor cores when the row length allows the tiled loads
+    if (K % 128 == 0 && (T == 1 || Resid == nullptr || Y != Resid))
+        return lt_q8_gemm_tc(Wq, Wd, Xq, Xd, Resid, 0, Y, M, K, T, 0, stream);
+    // otherwise chunks of up to 64 columns, each chunk one pass over the matrix with dp4a
     const int nb = K / 32;
     for (int t0 = 0; t0 < T; t0 += 64) {
         int tc = T - t0 < 64 ? T - t0 : 64;

@@ -96,7 +96,7 @@ def test_gemv_lm_head_shape(oracle):
 
 
 @pytest.mark.parametrize("T", [2, 3, 4, 8, 16, 33, 64, 70])
-@pytest.mark.parametrize("M,K", [(896, 896), (300, 4864)])
+@pytest.mark.parametrize("M,K", [(896, 896), (300, 4864), (200, 1056)])
 def test_skinny_gemm_bit_exact(oracle, M, K, T):
     Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=T)
     xq, xd = gpu_quant(x, rows=T)
@@ -106,14 +106,14 @@ def test_skinny_gemm_bit_exact(oracle, M, K, T):
     assert np.array_equal(bits(y), bits(want))
 
 
-def gpu_gemm_tc(dWq, dWd, dXq, dXd, M, K, T, variant, resid=None):
+def gpu_gemm_tc(dWq, dWd, dXq, dXd, M, K, T, variant, resid=None, resid_ld=0):
     y = torch.full((T * M,), float("nan"), dtype=torch.float32, device="cuda")
     _lib.call("lt_q8_gemm_tc", dWq.data_ptr(), dWd.data_ptr(), dXq.data_ptr(), dXd.data_ptr(),
-              None if resid is None else resid.data_ptr(), y.data_ptr(), M, K, T, variant, stream())
+              None if resid is None else resid.data_ptr(), resid_ld, y.data_ptr(), M, K, T, variant, stream())
     return y
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("M,K,T", [(128, 128, 16), (128, 896, 16), (896, 896, 64), (300, 4864, 33), (1152, 896, 70),
                                    (256, 4096, 5), (200, 14336, 17), (4864, 896, 257)])
 def test_tensor_core_gemm_bit_exact(oracle, M, K, T, variant):
@@ -126,6 +126,10 @@ def test_tensor_core_gemm_bit_exact(oracle, M, K, T, variant):
     assert np.array_equal(bits(y), bits(want))
     y = host(gpu_gemm_tc(dWq, dWd, xq, xd, M, K, T, variant, resid=dev(r))).reshape(T, M)
     assert np.array_equal(bits(y), bits(want + r[None, :]))
+    # one residual row per column (the residual stream of a prefill)
+    R = np.random.default_rng(3).standard_normal((T, M)).astype(np.float32)
+    y = host(gpu_gemm_tc(dWq, dWd, xq, xd, M, K, T, variant, resid=dev(R), resid_ld=M)).reshape(T, M)
+    assert np.array_equal(bits(y), bits(want + R))
     assert _lib.device_status() == set()
 
 
