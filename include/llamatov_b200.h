@@ -213,6 +213,34 @@ int lt_decode_num_ctas(void);
 int lt_decode_step_pdl(const lt_decode_desc* h_desc, void* stream);
 int lt_decode_pdl_num_parts(void);
 
+/* ---- row-batched operators for prefilling a prompt in one pass ---------------------------
+ * The reference prefills by running its one-token step once per prompt token
+ * (bpd/lib/dev_residency.py:1344-1350, forward_pass_resident recursing over the tokens) and
+ * requires a batched form to give the same numbers.  Each entry below computes for row r exactly
+ * what the one-token operator computes for that token; together with lt_rmsnorm / lt_quant_q8
+ * (rows) and lt_q8_gemm_tc they make a prompt chunk one pass over the weights.
+ *
+ * lt_embed_q8_rows      rows of lt_embed_q8: out[r, :] = dequantised table row of toks[r].
+ * lt_rope_rows          k_rope (rope_from_facts.pl:40-69) on row r at position *pos0 + r; a row holds
+ *                       n_head heads of hd floats at its start, rows are ld floats apart.
+ * lt_append_kv_rows     k_append_kv_incr (dev_residency.py:303-315) for nrows rows: row r goes to cache
+ *                       position *len + r; then *len += nrows when incr != 0.  Overflow sets
+ *                       LT_STATUS_KV_OVERFLOW and appends nothing.
+ * lt_silu_mul_quant_rows  lt_silu_mul_quant with gate and up rows ld floats apart.
+ * lt_attn_prefill       k_attn_decode_masked (dev_residency.py:1955-2010) for the nrows rows just
+ *                       appended: *len is the length after the append, row r is the query at position
+ *                       *len - nrows + r and sees the positions up to and including its own.
+ *                       maxt >= *len bounds the shared-memory score rows (<= 12000). */
+int lt_embed_q8_rows(const int8_t* Wq, const uint16_t* Wd, const int* toks, float* out, int E, int V,
+                     int nrows, void* stream);
+int lt_rope_rows(float* X, int ld, const int* pos0, int nrows, int n_head, int hd, float theta, void* stream);
+int lt_append_kv_rows(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int src_ld, int* len,
+                      int width, int max_seq, int nrows, int incr, void* stream);
+int lt_silu_mul_quant_rows(const float* g, const float* u, int ld, int8_t* Xq, uint16_t* Xd, int K, int rows,
+                           void* stream);
+int lt_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
+                    int out_ld, int hd, int nh, int nkv, float scale, int nrows, int maxt, void* stream);
+
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a
  * slab it owns).  Y[M] = W . quant(X[K]) (+ Resid), the same arithmetic as lt_quant_q8

@@ -35,6 +35,11 @@ SIGNATURES = {
     "lt_argmax_scratch_bytes": [],
     "lt_embed_q8": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_token_record": [_vp, _vp, _vp, _i, _vp],
+    "lt_embed_q8_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "lt_rope_rows": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "lt_append_kv_rows": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "lt_silu_mul_quant_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
+    "lt_attn_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],

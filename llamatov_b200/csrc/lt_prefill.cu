@@ -1,0 +1,306 @@
+// Row-batched forms of the decode operators, for prefilling a prompt in one pass.
+//
+// The reference prefills by running its one-token step once per prompt token
+// (bpd/lib/dev_residency.py:1344-1350) and requires any batched form to give the same
+// numbers.  Every kernel here therefore computes, for row r of the batch, exactly what the
+// one-token kernel computes for that token: same fold orders, same device functions.  What
+// changes is only how the work is spread: rows share one launch, and the causal attention
+// reads each cached K/V row once per tile of query rows instead of once per query.
+#include "lt_common.cuh"
+#include "lt_device_ops.cuh"
+
+namespace lt {
+
+// ------------------------------------------------------------------ embedding rows
+__global__ void k_embed_q8_rows(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd,
+                                const int* __restrict__ toks, float* __restrict__ out, int E, int V, int nrows,
+                                int* status) {
+    const int r = blockIdx.x;
+    if (r >= nrows) return;
+    int t = toks[r];
+    if (t < 0 || t >= V) {
+        if (threadIdx.x == 0) atomicOr(status, (int)LT_STATUS_BAD_TOKEN);
+        t = t < 0 ? 0 : V - 1;
+    }
+    const int nb = E >> 5;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float q = (float)Wq[(long)t * E + i];
+        const float d = __half2float(Wd[(long)t * nb + (i >> 5)]);
+        out[(long)r * E + i] = __fmul_rn(q, d);
+    }
+}
+
+// ------------------------------------------------------------------ rope rows
+// row r of X (row stride ld floats, n_head heads of hd at the row start) is rotated at position *pos0 + r
+__global__ void k_rope_rows(float* __restrict__ X, int ld, const int* __restrict__ pos0, int nrows, int n_head, int hd,
+                            float theta) {
+    const int half = hd / 2;
+    const long total = (long)nrows * n_head * half;
+    const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const int j = gid % half;
+    const long hr = gid / half;
+    const int head = hr % n_head;
+    const int row = hr / n_head;
+    const long base = (long)row * ld + (long)head * hd;
+    float o1, o2;
+    rope_pair(X[base + j], X[base + j + half], j, hd, theta, *pos0 + row, o1, o2);
+    X[base + j] = o1;
+    X[base + j + half] = o2;
+}
+
+// ------------------------------------------------------------------ KV append rows
+// rows 0..nrows-1 of ksrc / vsrc (row stride src_ld) go to cache positions *len .. *len+nrows-1
+__global__ void k_append_kv_rows(float* __restrict__ kbase, const float* __restrict__ ksrc, float* __restrict__ vbase,
+                                 const float* __restrict__ vsrc, int src_ld, const int* __restrict__ len, int width,
+                                 int max_seq, int nrows, int* status) {
+    const int L = *len;
+    if (L < 0 || L + nrows > max_seq) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, (int)LT_STATUS_KV_OVERFLOW);
+        return;
+    }
+    const long total = (long)nrows * width;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / width), c = (int)(i - (long)r * width);
+        kbase[(long)(L + r) * width + c] = ksrc[(long)r * src_ld + c];
+        vbase[(long)(L + r) * width + c] = vsrc[(long)r * src_ld + c];
+    }
+}
+__global__ void k_add_len(int* len, int n, int max_seq) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int L = *len;
+        if (L >= 0 && L + n <= max_seq) *len = L + n;
+    }
+}
+
+// ------------------------------------------------------------------ silu * up -> quant, strided rows
+__global__ void k_silu_mul_quant_rows(const float* __restrict__ G, const float* __restrict__ U, int ld,
+                                      int8_t* __restrict__ Xq, __half* __restrict__ Xd, int K, int rows) {
+    const int nb = K >> 5;
+    const long blk = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= (long)rows * nb) return;
+    const int r = (int)(blk / nb), b = (int)(blk - (long)r * nb);
+    const long src = (long)r * ld + (long)b * 32 + lane;
+    const float v = silu_mul(G[src], U[src]);
+    __half d;
+    const int q = quant_lane(v, &d);
+    Xq[(long)r * K + (long)b * 32 + lane] = (int8_t)q;
+    if (lane == 0) Xd[(long)r * nb + b] = d;
+}
+
+// ------------------------------------------------------------------ causal attention over a chunk of rows
+// Row r of the chunk is the query at cache position L0 + r, L0 = *len - nrows (the chunk's K/V rows
+// are already appended), and sees L_r = L0 + r + 1 positions.  Per (row, head) the arithmetic is the
+// one-token kernel's (lt_attn.cu): sequential-i fma scores, * scale, max, __expf, Z on 64 strided
+// lanes + tree, left-fold V sum, / Z.
+constexpr int PF_THREADS = 256;
+
+template <int HD, int QT>
+__global__ void __launch_bounds__(PF_THREADS)
+k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
+               const int* __restrict__ len_ptr, float* __restrict__ OUT, int out_ld, int nh, int nkv, float scale,
+               int nrows, int maxt, int* status) {
+    extern __shared__ __align__(16) float pf_smem[];
+    float* qs = pf_smem;                 // [QT][HD]
+    float* red = qs + QT * HD;           // [QT][64]
+    float* zs = red + QT * 64;           // [QT] max, then Z
+    float* sc = zs + QT;                 // [QT][maxt]
+    const int tid = threadIdx.x;
+    const int h = blockIdx.y;
+    const int r0 = blockIdx.x * QT;
+    int Lafter = *len_ptr;
+    if (Lafter < nrows || Lafter > maxt) {
+        if (tid == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
+        return;
+    }
+    const int L0 = Lafter - nrows;
+    const int nq = nrows - r0 < QT ? nrows - r0 : QT;   // query rows of this tile
+    const int Lmax = L0 + r0 + nq;                      // positions the last row sees
+    const int hk = h / (nh / nkv);
+
+    for (int i = tid; i < QT * HD; i += PF_THREADS) {
+        const int qi = i / HD, d = i - qi * HD;
+        qs[i] = qi < nq ? Q[(long)(r0 + qi) * q_ld + (long)h * HD + d] : 0.0f;
+    }
+    __syncthreads();
+
+    // scores: one thread per cached position, the K row read once for all QT queries
+    for (int t = tid; t < Lmax; t += PF_THREADS) {
+        const float4* Kt = (const float4*)(K + ((long)t * nkv + hk) * HD);
+        float s[QT];
+#pragma unroll
+        for (int qi = 0; qi < QT; qi++) s[qi] = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < HD / 4; i++) {
+            const float4 kk = Kt[i];
+#pragma unroll
+            for (int qi = 0; qi < QT; qi++) {
+                const float4 qq = ((const float4*)(qs + qi * HD))[i];
+                s[qi] = __fmaf_rn(qq.x, kk.x, s[qi]);
+                s[qi] = __fmaf_rn(qq.y, kk.y, s[qi]);
+                s[qi] = __fmaf_rn(qq.z, kk.z, s[qi]);
+                s[qi] = __fmaf_rn(qq.w, kk.w, s[qi]);
+            }
+        }
+#pragma unroll
+        for (int qi = 0; qi < QT; qi++) sc[(long)qi * maxt + t] = t < L0 + r0 + qi + 1 ? __fmul_rn(s[qi], scale) : -1e30f;
+    }
+    __syncthreads();
+
+    // softmax per query row on the frozen 64-lane layout: 4 rows at a time, 64 threads each
+    const int grp = tid >> 6, l64 = tid & 63;
+    for (int qb = 0; qb < QT; qb += 4) {
+        const int qi = qb + grp;
+        float* row = sc + (long)qi * maxt;
+        float m = -1e30f;
+        for (int t = l64; t < Lmax; t += 64) m = fmaxf(m, row[t]);
+        red[qi * 64 + l64] = m;
+        __syncthreads();
+        if (l64 < 32) {
+            float v = fmaxf(red[qi * 64 + l64], red[qi * 64 + l64 + 32]);
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+            if (l64 == 0) zs[qi] = v;
+        }
+        __syncthreads();
+        const float mx = zs[qi];
+        for (int t = l64; t < Lmax; t += 64) row[t] = __expf(__fsub_rn(row[t], mx));
+        __syncthreads();
+        float ls = 0.0f;
+        for (int t = l64; t < Lmax; t += 64) ls = __fadd_rn(ls, row[t]);
+        red[qi * 64 + l64] = ls;
+        __syncthreads();
+        if (l64 < 32) {
+            float v = __fadd_rn(red[qi * 64 + l64], red[qi * 64 + l64 + 32]);
+            v = warp_tree_sum(v);
+            if (l64 == 0) zs[qi] = v;
+        }
+        __syncthreads();
+    }
+
+    // V sum: thread = (row group, output element); each V row is read once for the group's rows
+    constexpr int NG = PF_THREADS / HD;      // row groups
+    constexpr int RPG = (QT + NG - 1) / NG;  // rows per group
+    const int g = tid / HD, d = tid - g * HD;
+    float acc[RPG];
+    int Lr[RPG];
+#pragma unroll
+    for (int k = 0; k < RPG; k++) {
+        acc[k] = 0.0f;
+        const int qi = g + k * NG;
+        Lr[k] = qi < nq ? L0 + r0 + qi + 1 : 0;
+    }
+    const float* Vd = V + (long)hk * HD + d;
+    const long vstride = (long)nkv * HD;
+    for (int t = 0; t < Lmax; t++) {
+        const float v = Vd[(long)t * vstride];
+#pragma unroll
+        for (int k = 0; k < RPG; k++) {
+            const int qi = g + k * NG;
+            if (t < Lr[k]) acc[k] = __fmaf_rn(sc[(long)qi * maxt + t], v, acc[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < RPG; k++) {
+        const int qi = g + k * NG;
+        if (qi < nq) OUT[(long)(r0 + qi) * out_ld + (long)h * HD + d] = __fdiv_rn(acc[k], zs[qi]);
+    }
+}
+
+template <int HD, int QT>
+static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
+                               int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_attn_prefill: status word unavailable");
+    const size_t smem = ((size_t)QT * HD + QT * 64 + QT + (size_t)QT * maxt) * sizeof(float);
+    LT_REQUIRE(smem <= 200 * 1024, "lt_attn_prefill: maxt=%d needs %zu bytes of shared memory", maxt, smem);
+    static bool attr_done = false;
+    if (!attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_attn_prefill<HD, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    dim3 grid((nrows + QT - 1) / QT, nh);
+    k_attn_prefill<HD, QT><<<grid, PF_THREADS, smem, s>>>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt,
+                                                         st);
+    return check_launch("lt_attn_prefill");
+}
+
+template <int HD>
+static int pick_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
+                             int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
+    // as many query rows per tile as the score rows allow in shared memory
+    const size_t budget = 190 * 1024 / sizeof(float);
+    if ((size_t)16 * (maxt + HD + 65) <= budget)
+        return launch_attn_prefill<HD, 16>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
+    if ((size_t)8 * (maxt + HD + 65) <= budget)
+        return launch_attn_prefill<HD, 8>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
+    return launch_attn_prefill<HD, 4>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
+}
+
+}  // namespace lt
+
+using namespace lt;
+
+extern "C" int lt_embed_q8_rows(const int8_t* Wq, const uint16_t* Wd, const int* toks, float* out, int E, int V,
+                                int nrows, void* stream) {
+    LT_REQUIRE(Wq && Wd && toks && out, "lt_embed_q8_rows: null pointer");
+    LT_REQUIRE(E > 0 && E % 32 == 0 && V > 0 && nrows > 0, "lt_embed_q8_rows: E=%d (multiple of 32) V=%d nrows=%d", E, V, nrows);
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_embed_q8_rows: status word unavailable");
+    k_embed_q8_rows<<<nrows, 256, 0, (cudaStream_t)stream>>>(Wq, (const __half*)Wd, toks, out, E, V, nrows, st);
+    return check_launch("lt_embed_q8_rows");
+}
+
+extern "C" int lt_rope_rows(float* X, int ld, const int* pos0, int nrows, int n_head, int hd, float theta,
+                            void* stream) {
+    LT_REQUIRE(X && pos0, "lt_rope_rows: null pointer");
+    LT_REQUIRE(nrows > 0 && n_head > 0 && hd > 0 && hd % 2 == 0 && ld >= n_head * hd,
+               "lt_rope_rows: nrows=%d n_head=%d hd=%d ld=%d", nrows, n_head, hd, ld);
+    const long total = (long)nrows * n_head * (hd / 2);
+    k_rope_rows<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(X, ld, pos0, nrows, n_head, hd, theta);
+    return check_launch("lt_rope_rows");
+}
+
+extern "C" int lt_append_kv_rows(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int src_ld, int* len,
+                                 int width, int max_seq, int nrows, int incr, void* stream) {
+    LT_REQUIRE(kbase && ksrc && vbase && vsrc && len, "lt_append_kv_rows: null pointer");
+    LT_REQUIRE(width > 0 && max_seq > 0 && nrows > 0 && src_ld >= width,
+               "lt_append_kv_rows: width=%d max_seq=%d nrows=%d src_ld=%d", width, max_seq, nrows, src_ld);
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_append_kv_rows: status word unavailable");
+    const long total = (long)nrows * width;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 1184) blocks = 1184;
+    k_append_kv_rows<<<blocks, 256, 0, (cudaStream_t)stream>>>(kbase, ksrc, vbase, vsrc, src_ld, len, width, max_seq,
+                                                              nrows, st);
+    int n = 1;
+    if (incr) {
+        k_add_len<<<1, 32, 0, (cudaStream_t)stream>>>(len, nrows, max_seq);
+        n = 2;
+    }
+    return check_launch("lt_append_kv_rows", n);
+}
+
+extern "C" int lt_silu_mul_quant_rows(const float* g, const float* u, int ld, int8_t* Xq, uint16_t* Xd, int K, int rows,
+                                      void* stream) {
+    LT_REQUIRE(g && u && Xq && Xd, "lt_silu_mul_quant_rows: null pointer");
+    LT_REQUIRE(K > 0 && K % 32 == 0 && rows > 0 && ld >= K, "lt_silu_mul_quant_rows: K=%d rows=%d ld=%d", K, rows, ld);
+    const long blocks32 = (long)rows * (K / 32);
+    k_silu_mul_quant_rows<<<(unsigned)((blocks32 + 7) / 8), 256, 0, (cudaStream_t)stream>>>(g, u, ld, Xq, (__half*)Xd, K,
+                                                                                         rows);
+    return check_launch("lt_silu_mul_quant_rows");
+}
+
+extern "C" int lt_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
+                               int out_ld, int hd, int nh, int nkv, float scale, int nrows, int maxt, void* stream) {
+    LT_REQUIRE(Q && K && V && len && OUT, "lt_attn_prefill: null pointer");
+    LT_REQUIRE(hd == 64 || hd == 128, "lt_attn_prefill: hd=%d (64 and 128 are built)", hd);
+    LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "lt_attn_prefill: nh=%d must be a positive multiple of nkv=%d", nh, nkv);
+    LT_REQUIRE(nrows > 0 && maxt >= nrows && maxt <= 12000, "lt_attn_prefill: nrows=%d maxt=%d (maxt in nrows..12000)", nrows, maxt);
+    LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_prefill: q_ld=%d out_ld=%d", q_ld, out_ld);
+    LT_REQUIRE(aligned16(Q) && aligned16(K), "lt_attn_prefill: Q and K must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return pick_attn_prefill<64>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
+    return pick_attn_prefill<128>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
+}

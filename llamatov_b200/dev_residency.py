@@ -630,6 +630,15 @@ def forward_pass_resident(w, cfg, tok, positions, kv_cache):
     nh, nkv = cfg["n_head"], cfg["n_head_kv"]
     hd = cfg["n_embd"] // nh
     nl = cfg["n_layers"]
+    if tok.numel() > 1 and _BATCHED_PREFILL and not _capturing() and _DEVICE_EMBED is None:
+        from . import prefill as _pf
+        if _pf.supported(cfg, w):
+            flat = tok.reshape(-1)
+            last = None
+            for c0 in range(0, flat.numel(), _pf.MAX_ROWS):
+                last = _pf.prefill_resident(w, cfg, flat[c0:c0 + _pf.MAX_ROWS], kv_cache,
+                                            want_logits=c0 + _pf.MAX_ROWS >= flat.numel())
+            return last
     if tok.numel() > 1:
         toks = tok.reshape(-1).tolist(); poss = positions.reshape(-1).tolist()
         last = None
@@ -700,6 +709,11 @@ def _compute_folded_logits(w, cfg, E):
 # Same arithmetic, bit-identical results in every mode; the eager forward_pass_resident keeps
 # the per-op launches and is the parity baseline.
 _FUSED_STEP = "pdl"
+
+# A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
+# architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
+# same bits.
+_BATCHED_PREFILL = True
 
 
 class _DecLayer(ctypes.Structure):
@@ -816,6 +830,12 @@ class GraphRunner:
         _ensure_logits_buf(self.E, self.w)
         _ensure_logits_scratch(self.E)
         _ensure_argmax_buf()
+        if first_tok.numel() > 1:
+            # the prompt but its last token in one batched pass; the last token takes the one-token
+            # path, which settles every fixed scratch pointer the captured step will use
+            ft, fp = first_tok.reshape(-1), first_pos.reshape(-1)
+            forward_pass_resident(self.w, self.cfg, ft[:-1], fp[:-1], self.kv)
+            first_tok, first_pos = ft[-1:], fp[-1:]
         logits = forward_pass_resident(self.w, self.cfg, first_tok, first_pos, self.kv)
         torch.cuda.synchronize()
         self._weight_cache_frozen = (frozenset(_DEV_CONST.keys()), frozenset(fd._DEV_WEIGHT_CACHE.keys()),

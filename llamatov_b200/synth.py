@@ -21,6 +21,8 @@ ARCHS = {
     # small shapes for tests (same structure: GQA, bias, tied head)
     "tiny": dict(n_layers=2, n_embd=128, n_head=4, n_head_kv=2, hd=32, n_ffn=256,
                  norm_eps=1e-6, rope_theta=1e6, vocab=512, qkv_bias=True, tied=True, arch="qwen2"),
+    "tiny-qwen64": dict(n_layers=2, n_embd=256, n_head=4, n_head_kv=2, hd=64, n_ffn=384,
+                        norm_eps=1e-6, rope_theta=1e6, vocab=512, qkv_bias=True, tied=True, arch="qwen2"),
     "tiny-llama": dict(n_layers=2, n_embd=256, n_head=4, n_head_kv=2, hd=64, n_ffn=512,
                        norm_eps=1e-5, rope_theta=5e5, vocab=640, qkv_bias=False, tied=False, arch="llama"),
 }
