@@ -97,6 +97,80 @@ k_q8_gemv(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const in
     }
 }
 
+// One activation column (the decode GEMV), tuned for latency as well as bandwidth: a warp owns R
+// rows and keeps U rounds of every row's blocks in flight (R * U * 34 bytes per lane) before it
+// folds them, so short matrices are one or two round trips to memory instead of K/1024.  The
+// fold itself walks the rounds in ascending block order, the lane chain of the contract.
+template <int R, int U>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const int8_t* __restrict__ Xq,
+           const __half* __restrict__ Xd, const float* __restrict__ Resid, float* __restrict__ Y, int M, int K) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nb = K >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long warps_total = (long)gridDim.x * GEMV_WARPS;
+    const long gwarp = (long)blockIdx.x * GEMV_WARPS + warp;
+    {
+        const int4* src = (const int4*)Xq;
+        int4* dst = (int4*)smem;
+        for (int i = threadIdx.x; i < (K >> 4); i += GEMV_THREADS) dst[i] = src[i];
+        __half* dsth = (__half*)(smem + K);
+        for (int i = threadIdx.x; i < nb; i += GEMV_THREADS) dsth[i] = Xd[i];
+    }
+    __syncthreads();
+    const __half* xds = (const __half*)(smem + K);
+
+    for (long r0 = gwarp * R; r0 < M; r0 += warps_total * R) {
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) acc[r] = 0.0f;
+        for (int b0 = lane; b0 < nb; b0 += 32 * U) {
+            int4 w0[U][R], w1[U][R];
+            unsigned short wd[U][R];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int b = b0 + 32 * u;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const long row = r0 + r;
+                    if (b < nb && row < M) {
+                        const int8_t* p = Wq + row * K + (long)b * 32;
+                        w0[u][r] = ld_stream_v4(p);
+                        w1[u][r] = ld_stream_v4(p + 16);
+                        wd[u][r] = ld_stream_u16(Wd + row * nb + b);
+                    } else {
+                        w0[u][r] = make_int4(0, 0, 0, 0);
+                        w1[u][r] = make_int4(0, 0, 0, 0);
+                        wd[u][r] = 0;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int b = b0 + 32 * u;
+                if (b < nb) {
+                    const int4* xp = (const int4*)(smem + b * 32);
+                    const int4 x0 = xp[0], x1 = xp[1];
+                    const float xd = __half2float(xds[b]);
+#pragma unroll
+                    for (int r = 0; r < R; r++)
+                        acc[r] = q8_accum(__half2float(__ushort_as_half(wd[u][r])), xd,
+                                          block_dot(w0[u][r], w1[u][r], x0, x1), acc[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            float v = warp_tree_sum(acc[r]);
+            const long row = r0 + r;
+            if (lane == 0 && row < M) {
+                if (Resid != nullptr) v = __fadd_rn(v, Resid[row]);
+                Y[row] = v;
+            }
+        }
+    }
+}
+
 // Wide skinny GEMM (8 < T <= TW): one warp per row, the row's blocks stay in registers while
 // all T columns are folded, so the matrix is still read exactly once.  The activation
 // columns come from global memory through L1/L2 (T*K bytes, cache resident).  Same lane /
@@ -174,6 +248,42 @@ static int launch_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, c
     return check_launch("lt_q8_gemv");
 }
 
+template <int R, int U>
+static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                        const float* Resid, float* Y, int M, int K, cudaStream_t s) {
+    const int nb = K / 32;
+    const size_t smem = (size_t)((K + nb * 2 + 15) / 16) * 16;
+    static bool attr_done = false;
+    if (smem > 48 * 1024 && !attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
+    int ctas = gemv_grid(((long)M + R - 1) / R);
+    k_q8_gemv1<R, U><<<(unsigned)ctas, GEMV_THREADS, smem, s>>>(Wq, (const __half*)Wd, Xq, (const __half*)Xd, Resid, Y,
+                                                              M, K);
+    return check_launch("lt_q8_gemv");
+}
+
+// rows per warp by matrix height (enough warps to fill the GPU), rounds in flight by row length
+static int dispatch_gemv1(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+                          const float* Resid, float* Y, int M, int K, cudaStream_t s) {
+    const int rounds = (K / 32 + 31) / 32;
+    if (M >= 32768) {
+        if (rounds >= 2) return launch_gemv1<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+        return launch_gemv1<4, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    }
+    if (M >= 8192) {
+        if (rounds >= 3) return launch_gemv1<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+        if (rounds == 2) return launch_gemv1<2, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+        return launch_gemv1<2, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    }
+    if (rounds >= 5) return launch_gemv1<1, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    if (rounds >= 3) return launch_gemv1<1, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    if (rounds == 2) return launch_gemv1<1, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    return launch_gemv1<1, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+}
+
 }  // namespace lt
 
 using namespace lt;
@@ -188,7 +298,7 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
                "lt_q8_gemv: scale pointers must be 2-byte aligned");
     LT_REQUIRE(T == 1 || Resid == nullptr || Y != Resid, "lt_q8_gemv: Y may alias Resid only when T == 1");
     cudaStream_t s = (cudaStream_t)stream;
-    if (T == 1) return launch_gemv<4, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
+    if (T == 1) return dispatch_gemv1(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
     if (T <= 2) return launch_gemv<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 4) return launch_gemv<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 8) return launch_gemv<2, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);

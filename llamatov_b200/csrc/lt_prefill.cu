@@ -97,7 +97,7 @@ __global__ void k_silu_mul_quant_rows(const float* __restrict__ G, const float* 
 constexpr int PF_THREADS = 256;
 
 template <int HD, int QT>
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, QT <= 8 ? 3 : 1)
 k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
                const int* __restrict__ len_ptr, float* __restrict__ OUT, int out_ld, int nh, int nkv, float scale,
                int nrows, int maxt, int* status) {
@@ -105,7 +105,8 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     float* qs = pf_smem;                 // [QT][HD]
     float* red = qs + QT * HD;           // [QT][64]
     float* zs = red + QT * 64;           // [QT] max, then Z
-    float* sc = zs + QT;                 // [QT][maxt]
+    float* sc = zs + QT;                 // [QT][ld], ld = maxt rounded up to 4 floats
+    const int ld = (maxt + 3) & ~3;
     const int tid = threadIdx.x;
     const int h = blockIdx.y;
     const int r0 = blockIdx.x * QT;
@@ -144,7 +145,7 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
             }
         }
 #pragma unroll
-        for (int qi = 0; qi < QT; qi++) sc[(long)qi * maxt + t] = t < L0 + r0 + qi + 1 ? __fmul_rn(s[qi], scale) : -1e30f;
+        for (int qi = 0; qi < QT; qi++) sc[qi * ld + t] = t < L0 + r0 + qi + 1 ? __fmul_rn(s[qi], scale) : -1e30f;
     }
     __syncthreads();
 
@@ -152,7 +153,7 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     const int grp = tid >> 6, l64 = tid & 63;
     for (int qb = 0; qb < QT; qb += 4) {
         const int qi = qb + grp;
-        float* row = sc + (long)qi * maxt;
+        float* row = sc + qi * ld;
         float m = -1e30f;
         for (int t = l64; t < Lmax; t += 64) m = fmaxf(m, row[t]);
         red[qi * 64 + l64] = m;
@@ -193,12 +194,27 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     }
     const float* Vd = V + (long)hk * HD + d;
     const long vstride = (long)nkv * HD;
-    for (int t = 0; t < Lmax; t++) {
+    // positions every row of the tile sees: four at a time, the probabilities as one 16-byte load
+    const int Lcommon = (L0 + r0 + 1) & ~3;
+    int t = 0;
+    for (; t < Lcommon; t += 4) {
+        const float v0 = Vd[(long)t * vstride], v1 = Vd[(long)(t + 1) * vstride];
+        const float v2 = Vd[(long)(t + 2) * vstride], v3 = Vd[(long)(t + 3) * vstride];
+#pragma unroll
+        for (int k = 0; k < RPG; k++) {
+            const float4 pr = *(const float4*)(sc + (g + k * NG) * ld + t);
+            acc[k] = __fmaf_rn(pr.x, v0, acc[k]);
+            acc[k] = __fmaf_rn(pr.y, v1, acc[k]);
+            acc[k] = __fmaf_rn(pr.z, v2, acc[k]);
+            acc[k] = __fmaf_rn(pr.w, v3, acc[k]);
+        }
+    }
+    for (; t < Lmax; t++) {   // the causal edge: row by row
         const float v = Vd[(long)t * vstride];
 #pragma unroll
         for (int k = 0; k < RPG; k++) {
             const int qi = g + k * NG;
-            if (t < Lr[k]) acc[k] = __fmaf_rn(sc[(long)qi * maxt + t], v, acc[k]);
+            if (t < Lr[k]) acc[k] = __fmaf_rn(sc[qi * ld + t], v, acc[k]);
         }
     }
 #pragma unroll
@@ -213,7 +229,7 @@ static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const f
                                int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_attn_prefill: status word unavailable");
-    const size_t smem = ((size_t)QT * HD + QT * 64 + QT + (size_t)QT * maxt) * sizeof(float);
+    const size_t smem = ((size_t)QT * HD + QT * 64 + QT + (size_t)QT * ((maxt + 3) & ~3)) * sizeof(float);
     LT_REQUIRE(smem <= 200 * 1024, "lt_attn_prefill: maxt=%d needs %zu bytes of shared memory", maxt, smem);
     static bool attr_done = false;
     if (!attr_done) {
@@ -229,11 +245,12 @@ static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const f
 template <int HD>
 static int pick_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
                              int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
-    // as many query rows per tile as the score rows allow in shared memory
-    const size_t budget = 190 * 1024 / sizeof(float);
-    if ((size_t)16 * (maxt + HD + 65) <= budget)
+    // query rows per tile: 8 while three CTAs of score rows fit an SM (the V sum and the softmax are
+    // chains of dependent operations, resident warps hide them), else 4; 16 only for short chunks
+    const size_t per_row = (size_t)((maxt + 3) & ~3) + HD + 65;
+    if (16 * per_row * sizeof(float) <= 72 * 1024)
         return launch_attn_prefill<HD, 16>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
-    if ((size_t)8 * (maxt + HD + 65) <= budget)
+    if (8 * per_row * sizeof(float) <= 72 * 1024 || 4 * per_row * sizeof(float) > 200 * 1024 / 2)
         return launch_attn_prefill<HD, 8>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
     return launch_attn_prefill<HD, 4>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
 }

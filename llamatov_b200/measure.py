@@ -1,0 +1,176 @@
+"""Measurements beside the headline decode bench: prompt prefill and the GEMV / skinny-GEMM sweep.
+
+  python -m llamatov_b200.measure prefill [--tokens 2048] [--batch 1 8] [--arch qwen2.5-0.5b]
+  python -m llamatov_b200.measure gemv-sweep [--batch 1 4 16 64] [--shapes all]
+
+Every line printed is one JSON object.  All timing is CUDA events on the launching stream after
+warm-up; inputs are synthetic (llamatov_b200.synth), seeded.
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+from . import _lib, synth
+from . import dev_residency as dr
+from . import prefill as pf
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SWEEP_SHAPES = [(896, 896), (128, 896), (4864, 896), (896, 4864), (151936, 896), (4096, 4096), (14336, 4096),
+                (4096, 14336), (128256, 4096)]
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return float(j["hbm_gbs"]), float(j.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _event_ms(fn, reps):
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def gemv_bytes(M, K, T):
+    """Algorithmic bytes of one launch: 34 B per 32 weights + T * (4K + 4M)."""
+    return M * (K // 32) * 34 + T * (4 * K + 4 * M)
+
+
+def run_prefill(args):
+    hbm, _tf, src = peaks()
+    model = synth.make_model(args.arch, seed=0)
+    mc = model["cfg"]
+    w, cfg = synth.reference_weights(model)
+    T = args.tokens
+    # int8 multiply-accumulates of the Q8_0 GEMMs per prompt token
+    E, F = mc["n_embd"], mc["n_ffn"]
+    nq, nk = mc["n_head"] * mc["hd"], mc["n_head_kv"] * mc["hd"]
+    macs = mc["n_layers"] * ((nq + 2 * nk) * E + E * nq + 2 * F * E + E * F)
+    for B in args.batch:
+        dr.reset_engine_state(); dr.apply_production_profile()
+        dr._KV_MAX_SEQ = T
+        rng = np.random.default_rng(0)
+        toks = torch.from_numpy(rng.integers(0, mc["vocab"], size=(B, T)).astype(np.int64))
+        times = []
+        for it in range(args.warmup + args.steps):
+            kvs = [[None] * cfg["n_layers"] for _ in range(B)]
+            torch.cuda.synchronize()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            n0 = _lib.launch_count()
+            e0.record()
+            pf.prefill_resident(w, cfg, toks, kvs, want_logits=True)
+            e1.record(); torch.cuda.synchronize()
+            if it >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+            launches = _lib.launch_count() - n0
+            for kv in kvs:
+                for c in kv:
+                    c.free()
+            del kvs
+        ms = float(np.median(times))
+        print(json.dumps({
+            "metric": "prefill tok/s (Q8_0, batched pass)", "value": B * T / (ms * 1e-3), "unit": "tok/s",
+            "ms_per_prompt_batch": ms, "config": {"workload": f"{args.arch} Q8_0 prefill, {T}-token prompt, batch {B}",
+                                                  "rows_per_pass": B * T},
+            "gpu_launches": launches, "steps": args.steps, "warmup": args.warmup,
+            "int8_tmacs_per_s": macs * B * T / (ms * 1e-3) / 1e12,
+            "device_status": sorted(_lib.device_status()), "data": "synthetic", "peak_source": src}), flush=True)
+
+
+def run_gemv_sweep(args):
+    hbm, _tf, src = peaks()
+    shapes = SWEEP_SHAPES
+    L2_BYTES = 126e6
+    for (M, K) in shapes:
+        nb = K // 32
+        wbytes = M * nb * 34
+        # steady state: enough distinct copies of the matrix that consecutive launches cannot hit L2
+        R = int(max(1, min(64, np.ceil(2.5 * L2_BYTES / wbytes))))
+        Wq = torch.randint(-127, 128, (R, M * K), dtype=torch.int8, device="cuda")
+        Wd = (torch.rand((R, M * nb), device="cuda") * 0.02).to(torch.float16).view(torch.int16)
+        for T in args.batch:
+            xq = torch.randint(-127, 128, (T * K,), dtype=torch.int8, device="cuda")
+            xd = (torch.rand((T * nb,), device="cuda") * 0.05).to(torch.float16).view(torch.int16)
+            y = torch.empty(T * M, dtype=torch.float32, device="cuda")
+
+            def run(i):
+                r = i % R
+                _lib.call("lt_q8_gemv", Wq[r].data_ptr(), Wd[r].data_ptr(), xq.data_ptr(), xd.data_ptr(), None,
+                          y.data_ptr(), M, K, T, _stream())
+            for i in range(max(3, R)):
+                run(i)
+            torch.cuda.synchronize()
+            # steady state: a captured chain of launches over the rotating copies, so that the host's
+            # launch rate does not enter (small shapes run for ~2 us)
+            chain = int(max(R, min(256, 2e9 // max(wbytes, 1))))
+            chain = max(R, (chain // R) * R)
+            side = torch.cuda.Stream()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(chain):
+                    run(i)
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    g.replay()
+                side.synchronize()
+                ms = _event_ms(lambda i: g.replay(), 5) / chain
+            # one launch alone with a cold L2: the flush (a write larger than L2) is queued first, the
+            # events and the launch behind it, so the host's launch latency is hidden behind the flush
+            flush = torch.empty(int(2 * L2_BYTES), dtype=torch.uint8, device="cuda")
+            cold = []
+            for i in range(5):
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                flush.fill_(i)
+                e0.record(); run(i); e1.record()
+                torch.cuda.synchronize()
+                cold.append(e0.elapsed_time(e1))
+            del flush
+            b = gemv_bytes(M, K, T)
+            print(json.dumps({"M": M, "K": K, "batch": T, "algorithmic_bytes": b,
+                              "steady_us": ms * 1e3, "steady_GBs": b / (ms * 1e-3) / 1e9,
+                              "steady_frac_of_hbm": b / (ms * 1e-3) / 1e9 / hbm,
+                              "alone_cold_us": float(np.median(cold)) * 1e3,
+                              "alone_cold_frac_of_hbm": b / (float(np.median(cold)) * 1e-3) / 1e9 / hbm,
+                              "copies_in_rotation": R, "peak_GBs": hbm, "peak_source": src}), flush=True)
+        del Wq, Wd
+    print(json.dumps({"device_status": sorted(_lib.device_status())}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="llamatov_b200.measure")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("prefill")
+    p.add_argument("--arch", default="qwen2.5-0.5b")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, nargs="+", default=[1, 8])
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=1)
+    g = sub.add_parser("gemv-sweep")
+    g.add_argument("--batch", type=int, nargs="+", default=[1, 4, 16, 64])
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("llamatov_b200.measure needs a CUDA device (there is no CPU path)")
+    if args.cmd == "prefill":
+        run_prefill(args)
+    else:
+        run_gemv_sweep(args)
+
+
+if __name__ == "__main__":
+    main()
