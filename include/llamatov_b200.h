@@ -241,6 +241,28 @@ int lt_silu_mul_quant_rows(const float* g, const float* u, int ld, int8_t* Xq, u
 int lt_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
                     int out_ld, int hd, int nh, int nkv, float scale, int nrows, int maxt, void* stream);
 
+/* ---- decode operators for a batch of sequences / long contexts ------------------------------
+ * No batched engine exists in the reference; its contract is that every sequence gets the
+ * one-sequence result.  The KV caches of a batch are one buffer per layer,
+ * [B][max_seq][nkv*hd] fp32, with one device length per sequence (lens[B]).
+ *
+ * lt_rope_batch         k_rope with one position per row: row r (ld floats apart) at pos[r].
+ * lt_append_kv_batch    k_append_kv_incr per sequence: row b goes to position lens[b] of cache b,
+ *                       then lens[b] += 1 when incr != 0; a full cache sets LT_STATUS_KV_OVERFLOW.
+ * lt_attn_decode_batch  k_attn_decode_masked (bpd/lib/dev_residency.py:1955-2010) for B query rows,
+ *                       lens[b] = length after the append.  Three launches (scores over position
+ *                       chunks, softmax per head, V sum per output element) so that a long context
+ *                       is scanned by many CTAs; every fold keeps the frozen order, results are
+ *                       bit-identical to lt_attn_decode_masked.  scratch holds
+ *                       lt_attn_decode_batch_scratch_floats(nh, max_seq, B) floats, 16-byte aligned. */
+int lt_rope_batch(float* X, int ld, const int* pos, int nrows, int n_head, int hd, float theta, void* stream);
+int lt_append_kv_batch(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int src_ld, int* lens,
+                       int width, int max_seq, int B, int incr, void* stream);
+long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B);
+int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* V, const int* lens, float* OUT,
+                         int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
+                         void* stream);
+
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a
  * slab it owns).  Y[M] = W . quant(X[K]) (+ Resid), the same arithmetic as lt_quant_q8

@@ -40,6 +40,9 @@ SIGNATURES = {
     "lt_append_kv_rows": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "lt_silu_mul_quant_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
     "lt_attn_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "lt_rope_batch": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "lt_append_kv_batch": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],
@@ -49,6 +52,8 @@ SIGNATURES = {
 }
 _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}
+# name -> (argtypes, restype) for the entries that return something other than a status code
+_QUERIES = {"lt_attn_decode_batch_scratch_floats": ([_i, _i, _i], ctypes.c_long)}
 
 
 def lib():
@@ -67,6 +72,10 @@ def lib():
         for name, rt in _RESTYPES.items():
             fn = getattr(L, name)
             fn.argtypes = []
+            fn.restype = rt
+        for name, (args, rt) in _QUERIES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
             fn.restype = rt
         _lib = L
     return _lib

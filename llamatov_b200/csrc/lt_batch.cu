@@ -1,0 +1,240 @@
+// Decode step operators for a batch of sequences and for long contexts.
+//
+// Same per-(sequence, head) arithmetic as the one-sequence kernels (lt_elementwise.cu,
+// lt_attn.cu) -- the reference has no batched engine, its contract is that every sequence gets
+// the one-sequence result (bpd/lib/dev_residency.py:1344-1350).  What differs is the spread of
+// the work: the attention of one (sequence, head) is three launches, so that a long context is
+// scanned by many CTAs while every fp32 fold keeps its frozen order:
+//   scores   one thread per cached position (sequential-i fma, * scale), all query heads of a
+//            KV head from one read of the K row                -> S[b, h, t]
+//   softmax  one CTA per (b, h): max, __expf, Z on the 64-lane strided layout + tree -> P, Z
+//   V sum    one thread per output element, left fold over t, the query heads of a KV head
+//            sharing the V rows                                -> OUT[b, h, d] = fold / Z
+// The KV caches of the batch are one buffer per layer, [B][max_seq][nkv*hd], with a device
+// length per sequence.
+#include "lt_common.cuh"
+#include "lt_device_ops.cuh"
+
+namespace lt {
+
+constexpr int BT = 256;
+constexpr int MAX_REP = 8;   // query heads per KV head handled together
+
+// ------------------------------------------------------------------ rope, one position per row
+__global__ void k_rope_batch(float* __restrict__ X, int ld, const int* __restrict__ pos, int nrows, int n_head, int hd,
+                             float theta) {
+    const int half = hd / 2;
+    const long total = (long)nrows * n_head * half;
+    const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const int j = gid % half;
+    const long hr = gid / half;
+    const int head = hr % n_head;
+    const int row = hr / n_head;
+    const long base = (long)row * ld + (long)head * hd;
+    float o1, o2;
+    rope_pair(X[base + j], X[base + j + half], j, hd, theta, pos[row], o1, o2);
+    X[base + j] = o1;
+    X[base + j + half] = o2;
+}
+
+// ------------------------------------------------------------------ append one row per sequence
+__global__ void k_append_kv_batch(float* __restrict__ kbase, const float* __restrict__ ksrc, float* __restrict__ vbase,
+                                  const float* __restrict__ vsrc, int src_ld, int* __restrict__ lens, int width,
+                                  int max_seq, int incr, int* status) {
+    const int b = blockIdx.x;
+    const int L = lens[b];
+    const bool ok = L >= 0 && L < max_seq;
+    if (ok) {
+        const long off = ((long)b * max_seq + L) * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            kbase[off + i] = ksrc[(long)b * src_ld + i];
+            vbase[off + i] = vsrc[(long)b * src_ld + i];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!ok) atomicOr(status, (int)LT_STATUS_KV_OVERFLOW);
+        else if (incr) lens[b] = L + 1;
+    }
+}
+
+// ------------------------------------------------------------------ attention, phase 1: scores
+// grid (position chunks, nkv, B); S[(b*nh + h)*s_ld + t]
+__global__ void __launch_bounds__(BT)
+k_attn_scores(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const int* __restrict__ lens,
+              float* __restrict__ S, int s_ld, int hd, int nh, int nkv, float scale, int max_seq, int* status) {
+    extern __shared__ __align__(16) float qs[];   // [rep][hd]
+    const int b = blockIdx.z, hk = blockIdx.y;
+    const int rep = nh / nkv;
+    int L = lens[b];
+    if (L < 0 || L > max_seq) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
+        L = L < 0 ? 0 : max_seq;
+    }
+    const int t = blockIdx.x * BT + threadIdx.x;
+    if (blockIdx.x * BT >= L) return;
+    for (int i = threadIdx.x; i < rep * hd; i += BT) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    __syncthreads();
+    if (t >= L) return;
+    const float4* Kt = (const float4*)(K + (((long)b * max_seq + t) * nkv + hk) * hd);
+    float s[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; r++) s[r] = 0.0f;
+    for (int i = 0; i < (hd >> 2); i++) {
+        const float4 kk = Kt[i];
+#pragma unroll
+        for (int r = 0; r < MAX_REP; r++) {
+            if (r < rep) {
+                const float4 qq = ((const float4*)(qs + r * hd))[i];
+                s[r] = __fmaf_rn(qq.x, kk.x, s[r]);
+                s[r] = __fmaf_rn(qq.y, kk.y, s[r]);
+                s[r] = __fmaf_rn(qq.z, kk.z, s[r]);
+                s[r] = __fmaf_rn(qq.w, kk.w, s[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < MAX_REP; r++)
+        if (r < rep) S[((long)b * nh + hk * rep + r) * s_ld + t] = __fmul_rn(s[r], scale);
+}
+
+// ------------------------------------------------------------------ phase 2: softmax numerators and Z
+// grid (nh, B); the row is staged in shared memory (max_seq floats)
+__global__ void __launch_bounds__(BT)
+k_attn_softmax(float* __restrict__ S, int s_ld, const int* __restrict__ lens, float* __restrict__ Z, int nh,
+               int max_seq) {
+    extern __shared__ float sh[];
+    __shared__ float red[64];
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    int L = lens[b];
+    L = L < 0 ? 0 : (L > max_seq ? max_seq : L);
+    float* row = S + ((long)b * nh + h) * s_ld;
+    for (int t = d; t < L; t += BT) sh[t] = row[t];
+    __syncthreads();
+    // max (exact in any order; the one-sequence kernel also scans the masked -1e30 entries)
+    if (d < 64) {
+        float m = -1e30f;
+        for (int t = d; t < L; t += 64) m = fmaxf(m, sh[t]);
+        red[d] = m;
+    }
+    __syncthreads();
+    if (d < 32) {
+        float v = fmaxf(red[d], red[d + 32]);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+        if (d == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float mx = red[0];
+    __syncthreads();
+    for (int t = d; t < L; t += BT) {
+        const float p = __expf(__fsub_rn(sh[t], mx));
+        sh[t] = p;
+        row[t] = p;
+    }
+    __syncthreads();
+    // Z: lane r sums t = r, r+64, ... ascending; masked entries of the one-sequence kernel add +0
+    if (d < 64) {
+        float ls = 0.0f;
+        for (int t = d; t < L; t += 64) ls = __fadd_rn(ls, sh[t]);
+        red[d] = ls;
+    }
+    __syncthreads();
+    if (d < 32) {
+        float v = __fadd_rn(red[d], red[d + 32]);
+        v = warp_tree_sum(v);
+        if (d == 0) Z[(long)b * nh + h] = v;
+    }
+}
+
+// ------------------------------------------------------------------ phase 3: V sum
+// grid (hd/32, nkv, B), block = 32 output elements x rep query heads
+__global__ void k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V,
+                          const int* __restrict__ lens, const float* __restrict__ Z, float* __restrict__ OUT, int out_ld,
+                          int hd, int nh, int nkv, int max_seq) {
+    const int b = blockIdx.z, hk = blockIdx.y;
+    const int rep = nh / nkv;
+    const int d = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int h = hk * rep + (threadIdx.x >> 5);
+    int L = lens[b];
+    L = L < 0 ? 0 : (L > max_seq ? max_seq : L);
+    const float* p = P + ((long)b * nh + h) * s_ld;
+    const float* Vd = V + ((long)b * max_seq * nkv + hk) * hd + d;
+    const long vs = (long)nkv * hd;
+    float acc = 0.0f;
+    int t = 0;
+    for (; t + 8 <= L; t += 8) {   // loads batched, fold order unchanged
+        const float4 p0 = *(const float4*)(p + t), p1 = *(const float4*)(p + t + 4);
+        const float v0 = Vd[(long)t * vs], v1 = Vd[(long)(t + 1) * vs], v2 = Vd[(long)(t + 2) * vs];
+        const float v3 = Vd[(long)(t + 3) * vs], v4 = Vd[(long)(t + 4) * vs], v5 = Vd[(long)(t + 5) * vs];
+        const float v6 = Vd[(long)(t + 6) * vs], v7 = Vd[(long)(t + 7) * vs];
+        acc = __fmaf_rn(p0.x, v0, acc); acc = __fmaf_rn(p0.y, v1, acc);
+        acc = __fmaf_rn(p0.z, v2, acc); acc = __fmaf_rn(p0.w, v3, acc);
+        acc = __fmaf_rn(p1.x, v4, acc); acc = __fmaf_rn(p1.y, v5, acc);
+        acc = __fmaf_rn(p1.z, v6, acc); acc = __fmaf_rn(p1.w, v7, acc);
+    }
+    for (; t < L; t++) acc = __fmaf_rn(p[t], Vd[(long)t * vs], acc);
+    OUT[(long)b * out_ld + (long)h * hd + d] = __fdiv_rn(acc, Z[(long)b * nh + h]);
+}
+
+}  // namespace lt
+
+using namespace lt;
+
+extern "C" int lt_rope_batch(float* X, int ld, const int* pos, int nrows, int n_head, int hd, float theta,
+                             void* stream) {
+    LT_REQUIRE(X && pos, "lt_rope_batch: null pointer");
+    LT_REQUIRE(nrows > 0 && n_head > 0 && hd > 0 && hd % 2 == 0 && ld >= n_head * hd,
+               "lt_rope_batch: nrows=%d n_head=%d hd=%d ld=%d", nrows, n_head, hd, ld);
+    const long total = (long)nrows * n_head * (hd / 2);
+    k_rope_batch<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(X, ld, pos, nrows, n_head, hd, theta);
+    return check_launch("lt_rope_batch");
+}
+
+extern "C" int lt_append_kv_batch(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int src_ld,
+                                  int* lens, int width, int max_seq, int B, int incr, void* stream) {
+    LT_REQUIRE(kbase && ksrc && vbase && vsrc && lens, "lt_append_kv_batch: null pointer");
+    LT_REQUIRE(width > 0 && max_seq > 0 && B > 0 && src_ld >= width, "lt_append_kv_batch: width=%d max_seq=%d B=%d src_ld=%d",
+               width, max_seq, B, src_ld);
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_append_kv_batch: status word unavailable");
+    const int threads = width >= 1024 ? 1024 : ((width + 31) / 32) * 32;
+    k_append_kv_batch<<<B, threads, 0, (cudaStream_t)stream>>>(kbase, ksrc, vbase, vsrc, src_ld, lens, width, max_seq,
+                                                              incr, st);
+    return check_launch("lt_append_kv_batch");
+}
+
+extern "C" long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B) {
+    const long s_ld = ((long)max_seq + 3) & ~3L;
+    return (long)B * nh * s_ld + (long)B * nh;
+}
+
+extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* V, const int* lens,
+                                    float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale,
+                                    int max_seq, int B, void* stream) {
+    LT_REQUIRE(Q && K && V && lens && OUT && scratch, "lt_attn_decode_batch: null pointer");
+    LT_REQUIRE(hd > 0 && hd % 32 == 0, "lt_attn_decode_batch: hd=%d must be a positive multiple of 32", hd);
+    LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= MAX_REP,
+               "lt_attn_decode_batch: nh=%d must be a multiple of nkv=%d with at most %d query heads per KV head", nh, nkv, MAX_REP);
+    LT_REQUIRE(max_seq > 0 && max_seq <= 49152 && B > 0 && B <= 65535, "lt_attn_decode_batch: max_seq=%d (1..49152) B=%d", max_seq, B);
+    LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_decode_batch: q_ld=%d out_ld=%d", q_ld, out_ld);
+    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(scratch), "lt_attn_decode_batch: Q, K and scratch must be 16-byte aligned");
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_attn_decode_batch: status word unavailable");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int s_ld = (max_seq + 3) & ~3;
+    float* S = scratch;
+    float* Z = scratch + (long)B * nh * s_ld;
+    const int rep = nh / nkv;
+    static bool attr_done = false;
+    if (!attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_attn_softmax, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    k_attn_scores<<<dim3((max_seq + BT - 1) / BT, nkv, B), BT, (size_t)rep * hd * sizeof(float), s>>>(
+        Q, q_ld, K, lens, S, s_ld, hd, nh, nkv, scale, max_seq, st);
+    k_attn_softmax<<<dim3(nh, B), BT, (size_t)max_seq * sizeof(float), s>>>(S, s_ld, lens, Z, nh, max_seq);
+    k_attn_pv<<<dim3(hd / 32, nkv, B), 32 * rep, 0, s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv, max_seq);
+    return check_launch("lt_attn_decode_batch", 3);
+}

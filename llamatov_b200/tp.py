@@ -1,0 +1,332 @@
+"""Tensor-parallel decode of a Q8_0 transformer over the GPUs of one node, one process per GPU.
+
+The reference engine is single-GPU (bpd/lib/dev_residency.py); this module shards the same layer
+sequence (dev_residency.py:1381-1477) for models too large to be worth running on one GPU:
+
+  column split (rows of W):  q|k|v by KV-head group, gate|up, LM head (vocabulary).  A rank's rows
+                             are whole reductions, so its outputs are bit-identical to one GPU's.
+  row split (K of W):        o_proj and down.  Each rank folds its K slice in the frozen order and
+                             the partial sums meet in an all-reduce (sum) of [batch, hidden] fp32;
+                             rank order of the sum is fixed, every rank gets the same bits.  The
+                             association differs from one GPU's single fold: tolerance class.
+  attention / KV cache:      head-parallel, every rank caches only its KV heads; no exchange.
+  next token:                local (max, index) per sequence, all-gather, lowest index wins ties.
+
+`ShardPlan` and the argmax combination are plain host code (tested on CPU with gloo);
+`TPDecoder` drives the C-ABI kernels and `torch.distributed` (NCCL) on the GPUs.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class ShardPlan:
+    """Which rows / K ranges of every matrix a rank owns."""
+
+    def __init__(self, cfg, world):
+        self.world = int(world)
+        self.E = cfg["n_embd"]; self.nh = cfg["n_head"]; self.nkv = cfg["n_head_kv"]
+        self.hd = cfg["hd"]; self.F = cfg["n_ffn"]; self.V = cfg["vocab"]
+        g = self.world
+        if self.nkv % g != 0:
+            raise ValueError(f"{self.nkv} KV heads do not split over {g} ranks")
+        if (self.F // g) % 128 != 0 or self.F % g != 0:
+            raise ValueError(f"FFN width {self.F} does not split over {g} ranks in multiples of 128")
+        self.nkv_l = self.nkv // g
+        self.nh_l = self.nh // g
+        self.nq_l = self.nh_l * self.hd
+        self.nk_l = self.nkv_l * self.hd
+        self.F_l = self.F // g
+        self.V_l = -(-self.V // g)            # rows per rank, the last rank may hold fewer
+
+    def qkv_rows(self, rank):
+        """Row ranges (q, k, v) of the fused [nq + 2 nk, E] matrix owned by `rank`."""
+        nq, nk = self.nh * self.hd, self.nkv * self.hd
+        q = (rank * self.nq_l, (rank + 1) * self.nq_l)
+        k = (nq + rank * self.nk_l, nq + (rank + 1) * self.nk_l)
+        v = (nq + nk + rank * self.nk_l, nq + nk + (rank + 1) * self.nk_l)
+        return q, k, v
+
+    def o_cols(self, rank):
+        return rank * self.nq_l, (rank + 1) * self.nq_l
+
+    def gateup_rows(self, rank):
+        """Row ranges (gate, up) of the fused [2F, E] matrix."""
+        return (rank * self.F_l, (rank + 1) * self.F_l), (self.F + rank * self.F_l, self.F + (rank + 1) * self.F_l)
+
+    def down_cols(self, rank):
+        return rank * self.F_l, (rank + 1) * self.F_l
+
+    def vocab_rows(self, rank):
+        return min(self.V, rank * self.V_l), min(self.V, (rank + 1) * self.V_l)
+
+
+def combine_argmax(vals, idxs):
+    """vals, idxs: [world, B] local maxima and their GLOBAL indices -> [B] winning indices;
+    ties go to the lowest index (dev_residency.py:226-271 keeps the lowest index on ties)."""
+    best = vals.max(dim=0, keepdim=True).values
+    cand = torch.where(vals == best, idxs, torch.full_like(idxs, torch.iinfo(idxs.dtype).max))
+    return cand.min(dim=0).values
+
+
+def take_rows(Wq, Wd, K, ranges):
+    """Rows of a Q8_0 matrix given as tensors Wq [N, K] int8, Wd [N, K/32]."""
+    return (torch.cat([Wq[a:b] for a, b in ranges]).contiguous(), torch.cat([Wd[a:b] for a, b in ranges]).contiguous())
+
+
+def take_cols(Wq, Wd, k0, k1):
+    """K range [k0, k1) (whole 32-blocks) of every row."""
+    assert k0 % 32 == 0 and k1 % 32 == 0
+    return Wq[:, k0:k1].contiguous(), Wd[:, k0 // 32:k1 // 32].contiguous()
+
+
+def random_q8(N, K, gen, device):
+    """Seeded random Q8_0 blocks on the device: q ~ U{-127..127}, d = fp16(U(0,1) * 0.02 / sqrt(K/896))."""
+    Wq = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=device, generator=gen)
+    sc = 0.02 / float(np.sqrt(K / 896.0))
+    Wd = (torch.rand((N, K // 32), device=device, generator=gen) * sc).to(torch.float16)
+    return Wq, Wd
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _W:
+    """One resident Q8_0 matrix shard."""
+    __slots__ = ("q", "d", "N", "K")
+
+    def __init__(self, Wq, Wd):
+        self.q = Wq.contiguous(); self.d = Wd.contiguous().view(torch.int16)
+        self.N, self.K = int(Wq.shape[0]), int(Wq.shape[1])
+
+
+class TPDecoder:
+    """Batched greedy decode of a random-init Q8_0 model, sharded over `world` ranks.
+
+    Every rank builds the full matrices from the same seed and keeps its shard, so the
+    model is the same at every world size (token streams can be compared against world 1).
+    """
+
+    def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None):
+        self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
+        self.max_seq = int(max_seq); self.group = group
+        self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.plan = p = ShardPlan(cfg, world)
+        E, L = p.E, cfg["n_layers"]
+        f32 = dict(dtype=torch.float32, device=self.dev)
+        if model is not None:
+            src = self._from_model(model)
+        else:
+            src = self._random(seed)
+        self.layers = []
+        for _ in range(L):
+            an = next(src)
+            Wq, Wd = next(src)
+            qkv = _W(*take_rows(Wq, Wd, E, self.plan.qkv_rows(rank)))
+            Wq, Wd = next(src)
+            o = _W(*take_cols(Wq, Wd, *p.o_cols(rank)))
+            fn = next(src)
+            Wq, Wd = next(src)
+            gu = _W(*take_rows(Wq, Wd, E, p.gateup_rows(rank)))
+            Wq, Wd = next(src)
+            down = _W(*take_cols(Wq, Wd, *p.down_cols(rank)))
+            del Wq, Wd
+            self.layers.append(dict(attn_norm=an, qkv=qkv, o=o, ffn_norm=fn, gateup=gu, down=down))
+        self.out_norm = next(src)
+        Wq, Wd = next(src)
+        self.embd = _W(Wq, Wd)                                   # replicated (gather of B rows per step)
+        lq, ld = next(src)
+        v0, v1 = p.vocab_rows(rank)
+        self.lm = _W(lq[v0:v1], ld[v0:v1]); self.v0 = v0
+        del lq, ld, src
+        # caches: [B, max_seq, nkv_l * hd] per layer, lengths per sequence
+        wl = p.nk_l
+        self.kc = [torch.zeros(self.B * self.max_seq * wl, **f32) for _ in range(L)]
+        self.vc = [torch.zeros(self.B * self.max_seq * wl, **f32) for _ in range(L)]
+        self.lens = [torch.zeros(self.B, dtype=torch.int32, device=self.dev) for _ in range(L)]
+        # fixed workspaces (the step is graph-capturable)
+        B = self.B
+        kmax = max(E, p.nq_l, p.F_l)
+        self.tok = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        self.x = torch.empty((B, E), **f32); self.x1 = torch.empty((B, E), **f32)
+        self.h = torch.empty((B, E), **f32); self.part = torch.empty((B, E), **f32)
+        self.qkv = torch.empty((B, p.nq_l + 2 * p.nk_l), **f32)
+        self.att = torch.empty((B, p.nq_l), **f32)
+        self.gu = torch.empty((B, 2 * p.F_l), **f32)
+        self.xq = torch.empty(B * kmax, dtype=torch.int8, device=self.dev)
+        self.xd = torch.empty(B * (kmax // 32), dtype=torch.int16, device=self.dev)
+        self.logits = torch.empty((B, max(1, v1 - v0)), **f32)
+        n = _lib.lib().lt_attn_decode_batch_scratch_floats(p.nh_l, self.max_seq, B)
+        self.scratch = torch.empty(n, **f32)
+        self.amax_part = torch.empty(_lib.lib().lt_argmax_scratch_bytes() // 4 * B, **f32)
+        self.loc_idx = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        self.pair = torch.zeros((B, 2), **f32)                   # (value, global index as float bits) per sequence
+        self.gath = torch.zeros((world, B, 2), **f32)
+        self.graph = None
+        self.history = []
+        self.allreduce_calls = 0
+
+    # ------------------------------------------------------------------ weights
+    def _random(self, seed):
+        """The full matrices in layer order, drawn on the device from one seeded generator."""
+        p, cfg = self.plan, self.cfg
+        E = p.E
+        gen = torch.Generator(device=self.dev); gen.manual_seed(seed)
+        f32 = dict(dtype=torch.float32, device=self.dev)
+        for _ in range(cfg["n_layers"]):
+            yield 1.0 + 0.1 * torch.randn(E, generator=gen, **f32)
+            yield random_q8(p.nh * p.hd + 2 * p.nkv * p.hd, E, gen, self.dev)
+            yield random_q8(E, p.nh * p.hd, gen, self.dev)
+            yield 1.0 + 0.1 * torch.randn(E, generator=gen, **f32)
+            yield random_q8(2 * p.F, E, gen, self.dev)
+            yield random_q8(E, p.F, gen, self.dev)
+        yield 1.0 + 0.1 * torch.randn(E, generator=gen, **f32)
+        emb = random_q8(p.V, E, gen, self.dev)
+        yield emb
+        yield emb if cfg.get("tied", False) else random_q8(p.V, E, gen, self.dev)
+
+    def _from_model(self, model):
+        """The same sequence from a host model (llamatov_b200.synth.make_model); no q/k/v bias."""
+        def q8(w):
+            Wq = torch.from_numpy(np.ascontiguousarray(w.Wq).reshape(w.N, w.K)).to(self.dev)
+            Wd = torch.from_numpy(np.ascontiguousarray(w.Wd).view(np.int16).reshape(w.N, w.K // 32)).to(self.dev)
+            return Wq, Wd.view(torch.float16)
+
+        def vec(a):
+            return torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
+        for ly in model["layers"]:
+            if ly["qkv_bias"] is not None:
+                raise ValueError("TPDecoder: q/k/v bias is not supported (Llama-type models)")
+            yield vec(ly["attn_norm"]); yield q8(ly["qkv"]); yield q8(ly["o"])
+            yield vec(ly["ffn_norm"]); yield q8(ly["gateup"]); yield q8(ly["down"])
+        yield vec(model["output_norm"])
+        yield q8(model["token_embd"])
+        yield q8(model["lm_head"])
+
+    # ------------------------------------------------------------------ state
+    def fill_cache(self, ctx, seed=1):
+        """KV caches pre-filled to `ctx` positions with N(0,1) * 0.3; the values of a (layer, sequence) do
+        not depend on the world size or the batch size."""
+        p = self.plan
+        gen = torch.Generator(device=self.dev)
+        wl, wfull = p.nk_l, p.nkv * p.hd
+        c0 = self.rank * wl
+        for il in range(len(self.layers)):
+            kc = self.kc[il].view(self.B, self.max_seq, wl); vc = self.vc[il].view(self.B, self.max_seq, wl)
+            for b in range(self.B):
+                gen.manual_seed(seed * 1000003 + il * 4099 + b)        # one draw per (layer, sequence)
+                full = torch.randn((2, ctx, wfull), generator=gen, dtype=torch.float32, device=self.dev) * 0.3
+                kc[b, :ctx] = full[0, :, c0:c0 + wl]
+                vc[b, :ctx] = full[1, :, c0:c0 + wl]
+            self.lens[il].fill_(ctx)
+
+    def set_tokens(self, toks):
+        self.tok.copy_(torch.as_tensor(toks, dtype=torch.int32).to(self.dev))
+
+    # ------------------------------------------------------------------ one step
+    def _gemm(self, W, y, T, resid=None, resid_ld=0):
+        if T == 1 and resid_ld in (0, W.N):
+            _lib.call("lt_q8_gemv", W.q.data_ptr(), W.d.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(),
+                      None if resid is None else resid.data_ptr(), y.data_ptr(), W.N, W.K, 1, _stream())
+        else:
+            _lib.call("lt_q8_gemm_tc", W.q.data_ptr(), W.d.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(),
+                      None if resid is None else resid.data_ptr(), resid_ld, y.data_ptr(), W.N, W.K, T, 0, _stream())
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+            self.allreduce_calls += 1
+
+    def _row_split(self, W, resid, out):
+        """out = resid + sum over ranks of (W_rank . x_rank): one fold on one rank (the residual rides
+        in the GEMV store, the reference's add-residual form); an all-reduce of partials otherwise."""
+        B, E = self.B, self.plan.E
+        if self.world == 1:
+            self._gemm(W, out, B, resid, E)
+        else:
+            self._gemm(W, self.part, B)
+            self._allreduce(self.part)
+            _lib.call("lt_add", resid.data_ptr(), self.part.data_ptr(), out.data_ptr(), B * E, _stream())
+
+    def step(self):
+        """One greedy decode step for the B sequences: tokens in self.tok -> next tokens in self.tok."""
+        p, cfg, B = self.plan, self.cfg, self.B
+        E, hd = p.E, p.hd
+        eps, theta = float(cfg["norm_eps"]), float(cfg["rope_theta"])
+        scale = float(np.float32(hd ** -0.5))
+        st = _stream
+        qld = p.nq_l + 2 * p.nk_l
+        _lib.call("lt_embed_q8_rows", self.embd.q.data_ptr(), self.embd.d.data_ptr(), self.tok.data_ptr(),
+                  self.x.data_ptr(), E, p.V, B, st())
+        for il, ly in enumerate(self.layers):
+            _lib.call("lt_rmsnorm", self.x.data_ptr(), ly["attn_norm"].data_ptr(), self.h.data_ptr(), B, E, eps, st())
+            _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+            self._gemm(ly["qkv"], self.qkv, B)
+            lens = self.lens[il]
+            _lib.call("lt_rope_batch", self.qkv.data_ptr(), qld, lens.data_ptr(), B, p.nh_l + p.nkv_l, hd, theta, st())
+            _lib.call("lt_append_kv_batch", self.kc[il].data_ptr(), self.qkv.data_ptr() + p.nq_l * 4,
+                      self.vc[il].data_ptr(), self.qkv.data_ptr() + (p.nq_l + p.nk_l) * 4, qld, lens.data_ptr(),
+                      p.nk_l, self.max_seq, B, 1, st())
+            _lib.call("lt_attn_decode_batch", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(), self.vc[il].data_ptr(),
+                      lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(), hd, p.nh_l, p.nkv_l,
+                      scale, self.max_seq, B, st())
+            _lib.call("lt_quant_q8", self.att.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), p.nq_l, B, st())
+            self._row_split(ly["o"], self.x, self.x1)
+            _lib.call("lt_rmsnorm", self.x1.data_ptr(), ly["ffn_norm"].data_ptr(), self.h.data_ptr(), B, E, eps, st())
+            _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+            self._gemm(ly["gateup"], self.gu, B)
+            _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
+                      self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
+            self._row_split(ly["down"], self.x1, self.x)
+        _lib.call("lt_rmsnorm", self.x.data_ptr(), self.out_norm.data_ptr(), self.h.data_ptr(), B, E, eps, st())
+        _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+        self._gemm(self.lm, self.logits, B)
+        nv = self.lm.N
+        stride = _lib.lib().lt_argmax_scratch_bytes() // 4
+        for b in range(B):
+            _lib.call("lt_argmax", self.logits[b].data_ptr(), nv, self.amax_part[b * stride:].data_ptr(),
+                      self.loc_idx[b:].data_ptr(), st())
+        if self.world == 1:
+            self.tok.copy_(self.loc_idx)
+        else:
+            idx = self.loc_idx.long()
+            self.pair[:, 0] = self.logits.gather(1, idx.view(B, 1)).view(B)
+            self.pair[:, 1] = (idx + self.v0).to(torch.int32).view(torch.float32)      # index carried as bits
+            torch.distributed.all_gather_into_tensor(self.gath.view(-1), self.pair.view(-1), group=self.group)
+            vals = self.gath[:, :, 0]
+            idxs = self.gath[:, :, 1].contiguous().view(torch.int32)
+            self.tok.copy_(combine_argmax(vals, idxs))
+
+    # ------------------------------------------------------------------ graph
+    def capture(self):
+        """Record step() (kernels and collectives) into a CUDA graph.  One warm-up step runs first (it is a
+        real decode step: lengths advance, tokens move on); the recorded pass itself executes nothing."""
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()                       # warm-up: NCCL channels, function attributes
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = _lib.launch_count()
+        with torch.cuda.graph(g, stream=side):
+            self.step()
+        self.launches_per_step = _lib.launch_count() - n0
+        self.graph = g
+        return g
+
+    def run(self, steps):
+        """`steps` decode steps (graph replays when captured); returns the tokens [steps, B] on the host."""
+        out = []
+        for _ in range(steps):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.step()
+            out.append(self.tok.clone())
+        torch.cuda.synchronize()
+        return torch.stack(out).cpu().numpy()

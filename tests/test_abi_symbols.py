@@ -23,7 +23,7 @@ def test_header_symbols_exported():
     L = ctypes.CDLL(_lib.LIB_PATH)
     for n in names:
         assert hasattr(L, n), f"{n} declared in the header but not exported"
-    bound = set(_lib.SIGNATURES) | set(_lib._RESTYPES)
+    bound = set(_lib.SIGNATURES) | set(_lib._RESTYPES) | set(_lib._QUERIES)
     assert bound == set(names), (sorted(bound - set(names)), sorted(set(names) - bound))
 
 

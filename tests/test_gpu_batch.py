@@ -1,0 +1,70 @@
+"""GPU: the batched / long-context decode operators against the one-sequence operators they
+must reproduce bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from llamatov_b200 import _lib
+from tests.gpu_util import bits, dev, host, stream
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("hd,nh,nkv,max_seq,lens", [(64, 14, 2, 256, [1, 37, 256]), (128, 32, 8, 4100, [4097, 1000]),
+                                                  (128, 4, 1, 4224, [4097])])
+def test_batched_attention_equals_one_sequence_attention(hd, nh, nkv, max_seq, lens):
+    rng = np.random.default_rng(nh)
+    B = len(lens)
+    width = nkv * hd
+    K = (rng.standard_normal((B, max_seq, width)) * 0.3).astype(np.float32)
+    V = (rng.standard_normal((B, max_seq, width)) * 0.3).astype(np.float32)
+    for b, L in enumerate(lens):                       # nothing beyond a length may be read
+        K[b, L:] = np.nan; V[b, L:] = np.nan
+    Q = rng.standard_normal((B, nh * hd)).astype(np.float32)
+    dK, dV, dQ = dev(K.reshape(-1)), dev(V.reshape(-1)), dev(Q.reshape(-1))
+    dl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = float(np.float32(hd ** -0.5))
+    nscr = _lib.lib().lt_attn_decode_batch_scratch_floats(nh, max_seq, B)
+    scratch = torch.empty(nscr, dtype=torch.float32, device="cuda")
+    out = torch.full((B * nh * hd,), float("nan"), device="cuda")
+    _lib.call("lt_attn_decode_batch", dQ.data_ptr(), nh * hd, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(),
+              out.data_ptr(), nh * hd, scratch.data_ptr(), hd, nh, nkv, scale, max_seq, B, stream())
+    got = host(out).reshape(B, nh * hd)
+    one = torch.empty(nh * hd, device="cuda")
+    for b in range(B):
+        _lib.call("lt_attn_decode_masked", dQ[b * nh * hd:].data_ptr(), dK[b * max_seq * width:].data_ptr(),
+                  dV[b * max_seq * width:].data_ptr(), dl[b:].data_ptr(), one.data_ptr(), hd, nh, nkv, scale, max_seq,
+                  stream())
+        assert np.array_equal(bits(got[b]), bits(host(one))), b
+    assert _lib.device_status() == set()
+
+
+def test_batched_rope_and_append():
+    rng = np.random.default_rng(0)
+    B, nh, nkv, hd, max_seq = 5, 4, 2, 64, 16
+    ld = (nh + 2 * nkv) * hd
+    X = rng.standard_normal((B, ld)).astype(np.float32)
+    pos = np.array([0, 3, 15, 7, 7], np.int32)
+    dX = dev(X.reshape(-1)); dp = torch.from_numpy(pos).cuda()
+    _lib.call("lt_rope_batch", dX.data_ptr(), ld, dp.data_ptr(), B, nh + nkv, hd, 5e5, stream())
+    got = host(dX).reshape(B, ld)
+    for b in range(B):                                  # one row at a time through lt_rope
+        row = dev(X[b, :(nh + nkv) * hd].copy())
+        _lib.call("lt_rope", row.data_ptr(), dp[b:].data_ptr(), 1, nh + nkv, hd, 5e5, stream())
+        assert np.array_equal(bits(got[b, :(nh + nkv) * hd]), bits(host(row)))
+        assert np.array_equal(bits(got[b, (nh + nkv) * hd:]), bits(X[b, (nh + nkv) * hd:]))   # v untouched
+    width = nkv * hd
+    kc = torch.zeros(B * max_seq * width, device="cuda"); vc = torch.zeros(B * max_seq * width, device="cuda")
+    lens = torch.tensor([0, 3, 15, 16, 7], dtype=torch.int32, device="cuda")     # sequence 3 is full
+    _lib.call("lt_append_kv_batch", kc.data_ptr(), dX.data_ptr() + nh * hd * 4, vc.data_ptr(),
+              dX.data_ptr() + (nh + nkv) * hd * 4, ld, lens.data_ptr(), width, max_seq, B, 1, stream())
+    assert _lib.device_status() == {"kv_overflow"}
+    assert lens.tolist() == [1, 4, 16, 16, 8]
+    k = host(kc).reshape(B, max_seq, width); v = host(vc).reshape(B, max_seq, width)
+    for b, L in enumerate([0, 3, 15, None, 7]):
+        if L is None:
+            assert not k[b].any()
+            continue
+        assert np.array_equal(bits(k[b, L]), bits(got[b, nh * hd:(nh + nkv) * hd]))
+        assert np.array_equal(bits(v[b, L]), bits(got[b, (nh + nkv) * hd:]))
+        assert np.count_nonzero(k[b].any(axis=1)) == 1

@@ -1,0 +1,125 @@
+"""GPU: the tensor-parallel batched decoder.  On one GPU (world 1) against the CPU oracle engine and
+against itself (batch of sequences == the sequences one by one; graph replay == eager); on two or
+more GPUs (NCCL, one process per GPU) against world 1: identical greedy tokens, logits within the
+re-association tolerance."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from llamatov_b200 import _lib, synth, tp
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 1e-3
+
+
+def _cfg(m):
+    return m["cfg"]
+
+
+def test_world1_matches_oracle_engine(oracle):
+    m = synth.make_model("tiny-llama", seed=4)
+    dec = tp.TPDecoder(_cfg(m), batch=1, max_seq=64, model=m)
+    eng = oracle.OracleEngine(synth.oracle_model(m), max_seq=64)
+    tok = 11
+    dec.set_tokens([tok])
+    for i in range(10):
+        dec.step()
+        torch.cuda.synchronize()
+        lg, nxt = eng.step(tok)
+        got = dec.logits[0].cpu().numpy()
+        assert np.max(np.abs(got - lg)) < LOGIT_TOL, i
+        top2 = np.partition(lg, -2)[-2:]
+        tok = int(dec.tok[0].item())
+        if top2[1] - top2[0] > 2 * LOGIT_TOL:
+            assert tok == nxt
+    assert all(int(l[0].item()) == 10 for l in dec.lens)
+    assert _lib.device_status() == set()
+
+
+def test_batch_equals_sequences_one_by_one_and_graph_equals_eager():
+    m = synth.make_model("tiny-llama", seed=6)
+    starts = [3, 77, 500]
+    d3 = tp.TPDecoder(_cfg(m), batch=3, max_seq=64, model=m)
+    d3.fill_cache(5, seed=9)
+    d3.set_tokens(starts)
+    eager = d3.run(8)
+    for b, s in enumerate(starts):
+        d = tp.TPDecoder(_cfg(m), batch=1, max_seq=64, model=m)
+        d.fill_cache(5, seed=9)
+        for il in range(len(d.kc)):       # sequence b's cache rows
+            w = d.plan.nk_l
+            d.kc[il].view(1, 64, w)[0].copy_(d3.kc[il].view(3, 64, w)[b]); d.vc[il].view(1, 64, w)[0].copy_(d3.vc[il].view(3, 64, w)[b])
+            d.kc[il].view(1, 64, w)[0, 5:].zero_(); d.vc[il].view(1, 64, w)[0, 5:].zero_()
+        d.set_tokens([s])
+        assert np.array_equal(d.run(8)[:, 0], eager[:, b]), b
+    g3 = tp.TPDecoder(_cfg(m), batch=3, max_seq=64, model=m)
+    g3.fill_cache(5, seed=9)
+    g3.set_tokens(starts)
+    g3.step(); first = g3.tok.clone()
+    g3.capture()                      # its warm-up step runs (2 steps so far); the recorded pass does not
+    torch.cuda.synchronize()
+    rest = g3.run(6)
+    assert np.array_equal(first.cpu().numpy(), eager[0])
+    assert np.array_equal(rest, eager[2:8])
+    assert _lib.device_status() == set()
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _tp_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    m = synth.make_model("tiny-llama", seed=8)
+    d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m)
+    d.fill_cache(6, seed=2)
+    d.set_tokens([5, 600])
+    toks, logits = [], []
+    for _ in range(6):
+        d.step()
+        torch.cuda.synchronize()
+        toks.append(d.tok.cpu().numpy().copy()); logits.append(d.logits.cpu().numpy().copy())
+    d.capture()
+    more = d.run(3)
+    q.put((rank, np.stack(toks), np.concatenate([l for l in logits], axis=0), more, sorted(_lib.device_status())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_world2_matches_world1():
+    import torch.multiprocessing as mp
+    m = synth.make_model("tiny-llama", seed=8)
+    ref = tp.TPDecoder(m["cfg"], batch=2, max_seq=64, model=m)
+    ref.fill_cache(6, seed=2)
+    ref.set_tokens([5, 600])
+    rt, rl = [], []
+    for _ in range(6):
+        ref.step(); torch.cuda.synchronize()
+        rt.append(ref.tok.cpu().numpy().copy()); rl.append(ref.logits.cpu().numpy().copy())
+    ref.step()                        # the warm-up step of the workers' capture()
+    rmore = ref.run(3)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps: p.start()
+    res = sorted((q.get(timeout=300) for _ in ps), key=lambda x: x[0])
+    for p in ps: p.join(timeout=60)
+    V = m["cfg"]["vocab"]
+    full = np.concatenate([res[0][2], res[1][2]], axis=1)[:, :V]      # vocabulary halves side by side
+    want = np.concatenate(rl, axis=0)
+    assert np.max(np.abs(full - want)) < LOGIT_TOL
+    for rank, toks, _lg, more, status in res:
+        assert np.array_equal(toks, np.stack(rt)), rank
+        assert np.array_equal(more, rmore), rank
+        assert status == []
