@@ -73,31 +73,10 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _tp_worker(rank, world, port, q):
-    import torch.distributed as dist
-    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    m = synth.make_model("tiny-llama", seed=8)
-    d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m)
-    d.fill_cache(6, seed=2)
-    d.set_tokens([5, 600])
-    toks, logits = [], []
-    for _ in range(6):
-        d.step()
-        torch.cuda.synchronize()
-        toks.append(d.tok.cpu().numpy().copy()); logits.append(d.logits.cpu().numpy().copy())
-    d.capture()
-    more = d.run(3)
-    q.put((rank, np.stack(toks), np.concatenate([l for l in logits], axis=0), more, sorted(_lib.device_status())))
-    dist.barrier()
-    dist.destroy_process_group()
-
-
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_world2_matches_world1():
-    import torch.multiprocessing as mp
+def test_world2_matches_world1(tmp_path):
+    """Two ranks under torch.distributed.run (tests/tp_worker.py) against this process at world 1."""
+    import subprocess
     m = synth.make_model("tiny-llama", seed=8)
     ref = tp.TPDecoder(m["cfg"], batch=2, max_seq=64, model=m)
     ref.fill_cache(6, seed=2)
@@ -108,18 +87,18 @@ def test_world2_matches_world1():
         rt.append(ref.tok.cpu().numpy().copy()); rl.append(ref.logits.cpu().numpy().copy())
     ref.step()                        # the warm-up step of the workers' capture()
     rmore = ref.run(3)
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    ps = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in ps: p.start()
-    res = sorted((q.get(timeout=300) for _ in ps), key=lambda x: x[0])
-    for p in ps: p.join(timeout=60)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(root, "tests", "tp_worker.py"), str(tmp_path)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    r = subprocess.run(cmd, env=env, cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = [np.load(os.path.join(str(tmp_path), f"rank{k}.npz")) for k in range(2)]
     V = m["cfg"]["vocab"]
-    full = np.concatenate([res[0][2], res[1][2]], axis=1)[:, :V]      # vocabulary halves side by side
+    full = np.concatenate([res[0]["logits"], res[1]["logits"]], axis=1)[:, :V]      # vocabulary halves side by side
     want = np.concatenate(rl, axis=0)
     assert np.max(np.abs(full - want)) < LOGIT_TOL
-    for rank, toks, _lg, more, status in res:
-        assert np.array_equal(toks, np.stack(rt)), rank
-        assert np.array_equal(more, rmore), rank
-        assert status == []
+    for k in range(2):
+        assert np.array_equal(res[k]["toks"], np.stack(rt)), k
+        assert np.array_equal(res[k]["more"], rmore), k
+        assert int(res[k]["status"]) == 0

@@ -1,0 +1,47 @@
+"""Rank program of tests/test_gpu_tp.py::test_world2_matches_world1 (run under torch.distributed.run):
+decodes the tiny model tensor-parallel over NCCL, eagerly and from a captured graph, and leaves
+tokens and logits in <outdir>/rank<k>.npz."""
+import datetime
+import os
+import sys
+import traceback
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    out = sys.argv[1]
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))
+    from llamatov_b200 import _lib, synth, tp
+    m = synth.make_model("tiny-llama", seed=8)
+    d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m)
+    d.fill_cache(6, seed=2)
+    d.set_tokens([5, 600])
+    toks, logits = [], []
+    for _ in range(6):
+        d.step()
+        torch.cuda.synchronize()
+        toks.append(d.tok.cpu().numpy().copy()); logits.append(d.logits.cpu().numpy().copy())
+    d.capture()
+    more = d.run(3)
+    status = _lib.device_status()
+    np.savez(os.path.join(out, f"rank{rank}.npz"), toks=np.stack(toks), logits=np.concatenate(logits, axis=0),
+             more=more, status=np.int32(len(status)))
+    dist.barrier()
+    torch.cuda.synchronize()
+
+
+if __name__ == "__main__":
+    code = 0
+    try:
+        main()
+    except Exception:
+        traceback.print_exc()
+        code = 1
+    sys.stdout.flush(); sys.stderr.flush()
+    os._exit(code)        # no interpreter teardown: a process group being destroyed can wait on its peer
