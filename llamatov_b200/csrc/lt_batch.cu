@@ -81,16 +81,21 @@ k_attn_scores(const float* __restrict__ Q, int q_ld, const float* __restrict__ K
     float s[MAX_REP];
 #pragma unroll
     for (int r = 0; r < MAX_REP; r++) s[r] = 0.0f;
-    for (int i = 0; i < (hd >> 2); i++) {
-        const float4 kk = Kt[i];
+    for (int i0 = 0; i0 < (hd >> 2); i0 += 8) {   // hd is a multiple of 32: eight 16-byte loads in flight
+        float4 kk[8];
 #pragma unroll
-        for (int r = 0; r < MAX_REP; r++) {
-            if (r < rep) {
-                const float4 qq = ((const float4*)(qs + r * hd))[i];
-                s[r] = __fmaf_rn(qq.x, kk.x, s[r]);
-                s[r] = __fmaf_rn(qq.y, kk.y, s[r]);
-                s[r] = __fmaf_rn(qq.z, kk.z, s[r]);
-                s[r] = __fmaf_rn(qq.w, kk.w, s[r]);
+        for (int u = 0; u < 8; u++) kk[u] = Kt[i0 + u];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+#pragma unroll
+            for (int r = 0; r < MAX_REP; r++) {
+                if (r < rep) {
+                    const float4 qq = ((const float4*)(qs + r * hd))[i0 + u];
+                    s[r] = __fmaf_rn(qq.x, kk[u].x, s[r]);
+                    s[r] = __fmaf_rn(qq.y, kk[u].y, s[r]);
+                    s[r] = __fmaf_rn(qq.z, kk[u].z, s[r]);
+                    s[r] = __fmaf_rn(qq.w, kk[u].w, s[r]);
+                }
             }
         }
     }
@@ -149,33 +154,70 @@ k_attn_softmax(float* __restrict__ S, int s_ld, const int* __restrict__ lens, fl
 }
 
 // ------------------------------------------------------------------ phase 3: V sum
-// grid (hd/32, nkv, B), block = 32 output elements x rep query heads
-__global__ void k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V,
-                          const int* __restrict__ lens, const float* __restrict__ Z, float* __restrict__ OUT, int out_ld,
-                          int hd, int nh, int nkv, int max_seq) {
+// grid (hd/32, nkv, B), block = 32 output elements x rep query heads.  The fold over t is one
+// dependent chain per output element; what can be spread is the loading: the CTA stages tiles of
+// PV_TT positions (its 32 columns of V, and the probabilities of its heads) in shared memory with
+// asynchronous copies, one tile ahead of the fold.
+constexpr int PV_TT = 128;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(32 * MAX_REP)
+k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
+          const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq) {
+    __shared__ __align__(16) float vt[2][PV_TT][32];
+    __shared__ __align__(16) float pt[2][MAX_REP][PV_TT];
     const int b = blockIdx.z, hk = blockIdx.y;
     const int rep = nh / nkv;
-    const int d = blockIdx.x * 32 + (threadIdx.x & 31);
-    const int h = hk * rep + (threadIdx.x >> 5);
+    const int dl = threadIdx.x & 31, r = threadIdx.x >> 5;
+    const int d0 = blockIdx.x * 32;
+    const int h = hk * rep + r;
     int L = lens[b];
     L = L < 0 ? 0 : (L > max_seq ? max_seq : L);
-    const float* p = P + ((long)b * nh + h) * s_ld;
-    const float* Vd = V + ((long)b * max_seq * nkv + hk) * hd + d;
+    const float* Vb = V + ((long)b * max_seq * nkv + hk) * hd + d0;
     const long vs = (long)nkv * hd;
+    const float* Pb = P + ((long)b * nh + (long)hk * rep) * s_ld;
+    const int nthreads = 32 * rep;
+    const int tiles = (L + PV_TT - 1) / PV_TT;
+
+    auto stage = [&](int k) {
+        const int buf = k & 1, t0 = k * PV_TT;
+        for (int i = threadIdx.x; i < PV_TT * 8; i += nthreads) {
+            const int row = i >> 3, c = i & 7;
+            if (t0 + row < L) cp_async16(&vt[buf][row][c * 4], Vb + (long)(t0 + row) * vs + c * 4);
+        }
+        for (int i = threadIdx.x; i < rep * (PV_TT / 4); i += nthreads) {
+            const int hr = i / (PV_TT / 4), c = i - hr * (PV_TT / 4);
+            if (t0 + c * 4 < L) cp_async16(&pt[buf][hr][c * 4], Pb + (long)hr * s_ld + t0 + c * 4);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
     float acc = 0.0f;
-    int t = 0;
-    for (; t + 8 <= L; t += 8) {   // loads batched, fold order unchanged
-        const float4 p0 = *(const float4*)(p + t), p1 = *(const float4*)(p + t + 4);
-        const float v0 = Vd[(long)t * vs], v1 = Vd[(long)(t + 1) * vs], v2 = Vd[(long)(t + 2) * vs];
-        const float v3 = Vd[(long)(t + 3) * vs], v4 = Vd[(long)(t + 4) * vs], v5 = Vd[(long)(t + 5) * vs];
-        const float v6 = Vd[(long)(t + 6) * vs], v7 = Vd[(long)(t + 7) * vs];
-        acc = __fmaf_rn(p0.x, v0, acc); acc = __fmaf_rn(p0.y, v1, acc);
-        acc = __fmaf_rn(p0.z, v2, acc); acc = __fmaf_rn(p0.w, v3, acc);
-        acc = __fmaf_rn(p1.x, v4, acc); acc = __fmaf_rn(p1.y, v5, acc);
-        acc = __fmaf_rn(p1.z, v6, acc); acc = __fmaf_rn(p1.w, v7, acc);
+    if (tiles > 0) stage(0);
+    for (int k = 0; k < tiles; k++) {
+        if (k + 1 < tiles) {
+            stage(k + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int buf = k & 1;
+        const int n = L - k * PV_TT < PV_TT ? L - k * PV_TT : PV_TT;
+        const float* pr = pt[buf][r];
+        int t = 0;
+        for (; t + 8 <= n; t += 8) {
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc = __fmaf_rn(pr[t + u], vt[buf][t + u][dl], acc);
+        }
+        for (; t < n; t++) acc = __fmaf_rn(pr[t], vt[buf][t][dl], acc);
+        __syncthreads();
     }
-    for (; t < L; t++) acc = __fmaf_rn(p[t], Vd[(long)t * vs], acc);
-    OUT[(long)b * out_ld + (long)h * hd + d] = __fdiv_rn(acc, Z[(long)b * nh + h]);
+    OUT[(long)b * out_ld + (long)h * hd + d0 + dl] = __fdiv_rn(acc, Z[(long)b * nh + h]);
 }
 
 }  // namespace lt
@@ -219,7 +261,7 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
                "lt_attn_decode_batch: nh=%d must be a multiple of nkv=%d with at most %d query heads per KV head", nh, nkv, MAX_REP);
     LT_REQUIRE(max_seq > 0 && max_seq <= 49152 && B > 0 && B <= 65535, "lt_attn_decode_batch: max_seq=%d (1..49152) B=%d", max_seq, B);
     LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_decode_batch: q_ld=%d out_ld=%d", q_ld, out_ld);
-    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(scratch), "lt_attn_decode_batch: Q, K and scratch must be 16-byte aligned");
+    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(scratch), "lt_attn_decode_batch: Q, K, V and scratch must be 16-byte aligned");
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_attn_decode_batch: status word unavailable");
     cudaStream_t s = (cudaStream_t)stream;

@@ -1,7 +1,9 @@
 """Measurements beside the headline decode bench: prompt prefill and the GEMV / skinny-GEMM sweep.
 
   python -m llamatov_b200.measure prefill [--tokens 2048] [--batch 1 8] [--arch qwen2.5-0.5b]
-  python -m llamatov_b200.measure gemv-sweep [--batch 1 4 16 64] [--shapes all]
+  python -m llamatov_b200.measure gemv-sweep [--batch 1 4 16 64]
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      -m llamatov_b200.measure tp-decode [--batch 1 32] [--ctx 4096] [--steps 128] [--check-world1]
 
 Every line printed is one JSON object.  All timing is CUDA events on the launching stream after
 warm-up; inputs are synthetic (llamatov_b200.synth), seeded.
@@ -152,6 +154,110 @@ def run_gemv_sweep(args):
     print(json.dumps({"device_status": sorted(_lib.device_status())}))
 
 
+def run_tp_decode(args):
+    """Llama-3-8B-architecture (or --arch) random-init Q8_0 decode, tensor-parallel over the ranks this
+    program was launched with (torch.distributed.run; a plain launch is world 1).  KV caches pre-filled
+    to --ctx positions, --steps greedy steps from a captured graph; device time is the max over ranks."""
+    import datetime
+    import torch.distributed as dist
+    from . import tp
+    hbm, _tf, src = peaks()
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=120))
+    a = synth.ARCHS[args.arch]
+    cfg = dict(n_layers=a["n_layers"], n_head=a["n_head"], n_head_kv=a["n_head_kv"], n_embd=a["n_embd"],
+               rope_theta=a["rope_theta"], norm_eps=a["norm_eps"], hd=a["hd"], n_ffn=a["n_ffn"], vocab=a["vocab"],
+               tied=a["tied"])
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    E, F, V, L = cfg["n_embd"], cfg["n_ffn"], cfg["vocab"], cfg["n_layers"]
+    nq, nk = cfg["n_head"] * cfg["hd"], cfg["n_head_kv"] * cfg["hd"]
+    wbytes = (L * ((nq + 2 * nk) * E + E * nq + 2 * F * E + E * F) + V * E) // 32 * 34
+    for B in args.batch:
+        max_seq = args.ctx + args.steps + 8
+        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0)
+        dec.fill_cache(args.ctx, seed=1)
+        start = np.random.default_rng(0).integers(0, V, size=B)
+        dec.set_tokens(start)
+        dec.capture()                               # one warm-up step inside
+        for _ in range(max(0, args.warmup - 1)):
+            dec.graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        toks = []
+        for _ in range(args.steps):
+            dec.graph.replay()
+            toks.append(dec.tok.clone())
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        toks = torch.stack(toks).cpu().numpy()
+        t = torch.tensor([ms], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        # the all-reduces of one step alone, back to back (2 per layer, [B, E] fp32)
+        ar_ms = 0.0
+        if world > 1:
+            buf = torch.zeros((B, E), device="cuda")
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                dist.all_reduce(buf)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(2 * L):
+                    dist.all_reduce(buf)
+            g.replay(); torch.cuda.synchronize()
+            ar_ms = _event_ms(lambda i: g.replay(), 10)
+            t = torch.tensor([ar_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ar_ms = float(t.item())
+        status = sorted(_lib.device_status())
+        match = None
+        if args.check_world1 and world > 1 and rank == 0:
+            del dec
+            torch.cuda.empty_cache()
+            ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0)
+            ref.fill_cache(args.ctx, seed=1)
+            ref.set_tokens(start)
+            ref.step()                              # the warm-up step of capture()
+            for _ in range(max(0, args.warmup - 1)):
+                ref.step()
+            rt = ref.run(args.steps)
+            match = float((rt == toks).mean())
+            del ref
+        if rank == 0:
+            step_ms = ms / args.steps
+            kv_bytes = B * L * 2 * (args.ctx + args.steps // 2) * nk * 4
+            step_bytes = wbytes + kv_bytes
+            print(json.dumps({
+                "metric": "decode tok/s (Q8_0, tensor-parallel)", "value": B * args.steps / (ms * 1e-3), "unit": "tok/s",
+                "n_gpus": world, "ms_per_step": step_ms, "steps": args.steps, "warmup": args.warmup,
+                "config": {"workload": f"{args.arch} Q8_0 decode, batch {B}, context {args.ctx}, TP={world}",
+                           "layers": L, "launches_per_step": dec.launches_per_step if match is None else None},
+                "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
+                             "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
+                             "frac": step_bytes / (step_ms * 1e-3) / 1e9 / (hbm * world), "peak_source": src},
+                "allreduce_ms_per_step_alone": ar_ms, "allreduce_share": ar_ms / step_ms if step_ms else None,
+                "token_match_vs_world1": match, "first_tokens": toks[:4, 0].tolist(),
+                "device_status": status, "data": "synthetic"}), flush=True)
+        try:
+            del dec
+        except NameError:
+            pass
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="llamatov_b200.measure")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -163,11 +269,21 @@ def main(argv=None):
     p.add_argument("--warmup", type=int, default=1)
     g = sub.add_parser("gemv-sweep")
     g.add_argument("--batch", type=int, nargs="+", default=[1, 4, 16, 64])
+    t = sub.add_parser("tp-decode")
+    t.add_argument("--arch", default="llama-3-8b")
+    t.add_argument("--batch", type=int, nargs="+", default=[1, 32])
+    t.add_argument("--ctx", type=int, default=4096)
+    t.add_argument("--steps", type=int, default=128)
+    t.add_argument("--warmup", type=int, default=3)
+    t.add_argument("--layers", type=int, default=0, help="fewer layers than the architecture (smoke runs)")
+    t.add_argument("--check-world1", action="store_true", help="rank 0 re-runs at world 1 and compares the tokens")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("llamatov_b200.measure needs a CUDA device (there is no CPU path)")
     if args.cmd == "prefill":
         run_prefill(args)
+    elif args.cmd == "tp-decode":
+        run_tp_decode(args)
     else:
         run_gemv_sweep(args)
 
