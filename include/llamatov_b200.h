@@ -263,6 +263,30 @@ int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* 
                          int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
                          void* stream);
 
+/* ---- all-reduce over the GPUs of one node, fused with the residual add ---------------------
+ * No counterpart in the reference (it is single-GPU).  For the tensor-parallel decode step:
+ * out = resid + (part_0 + part_1 + ... in rank order), the same bits on every rank.  Each rank owns
+ * a staging buffer and flags that its peers map through CUDA IPC; one kernel per rank stores its
+ * partial into every rank's staging memory (plain peer stores), signals, waits (bounded:
+ * LT_STATUS_WAIT_TIMEOUT) for the others' flags in its own memory and folds the local copies.
+ * One process per GPU.  Setup: every rank calls lt_comm_alloc (fills 128 handle bytes), the ranks
+ * exchange the handle bytes by any host means, every rank calls lt_comm_connect with all of them
+ * (world * 128 bytes, rank order), then a host barrier before the first lt_allreduce_add. */
+#define LT_COMM_MAX_RANKS 8
+typedef struct lt_comm {
+    int rank, world, max_n, max_ctas;
+    float* stage[LT_COMM_MAX_RANKS];      /* stage[r]: rank r's staging buffer as mapped in this process */
+    unsigned int* flags[LT_COMM_MAX_RANKS];
+    float* local_stage;
+    unsigned int* local_flags;
+    unsigned int* ctr;                    /* per-CTA call counters (device) */
+} lt_comm;
+int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handles);
+int lt_comm_connect(lt_comm* comm, int rank, const unsigned char* all_handles);
+int lt_comm_free(lt_comm* comm);
+int lt_allreduce_add(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
+                     void* stream);
+
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a
  * slab it owns).  Y[M] = W . quant(X[K]) (+ Resid), the same arithmetic as lt_quant_q8

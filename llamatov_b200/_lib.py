@@ -43,6 +43,10 @@ SIGNATURES = {
     "lt_rope_batch": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv_batch": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp],
+    "lt_comm_alloc": [_i, _i, _vp, _vp],
+    "lt_comm_connect": [_vp, _i, _vp],
+    "lt_comm_free": [_vp],
+    "lt_allreduce_add": [_vp, _vp, _vp, _vp, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],

@@ -95,6 +95,38 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _CommStruct(ctypes.Structure):
+    """struct lt_comm of include/llamatov_b200.h."""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("max_n", ctypes.c_int), ("max_ctas", ctypes.c_int),
+                ("stage", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8),
+                ("local_stage", ctypes.c_void_p), ("local_flags", ctypes.c_void_p), ("ctr", ctypes.c_void_p)]
+
+
+class P2PComm:
+    """The one-shot all-reduce over peer memory (lt_allreduce_add): staging buffers mapped through CUDA
+    IPC, handles exchanged over the process group that already exists."""
+
+    def __init__(self, rank, world, max_n, group=None):
+        import torch.distributed as dist
+        self.c = _CommStruct()
+        handles = (ctypes.c_ubyte * 128)()
+        _lib.call("lt_comm_alloc", world, max_n, ctypes.byref(self.c), handles)
+        mine = bytes(handles)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=group)
+        allh = (ctypes.c_ubyte * (128 * world)).from_buffer_copy(b"".join(gathered))
+        _lib.call("lt_comm_connect", ctypes.byref(self.c), rank, allh)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)          # every rank's buffers exist and are zero before the first store
+
+    def allreduce_add(self, part, resid, out, n):
+        _lib.call("lt_allreduce_add", ctypes.byref(self.c), part.data_ptr(), None if resid is None else resid.data_ptr(),
+                  out.data_ptr(), n, _stream())
+
+    def free(self):
+        _lib.call("lt_comm_free", ctypes.byref(self.c))
+
+
 class _W:
     """One resident Q8_0 matrix shard."""
     __slots__ = ("q", "d", "N", "K")
@@ -111,7 +143,8 @@ class TPDecoder:
     model is the same at every world size (token streams can be compared against world 1).
     """
 
-    def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None):
+    def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
+                 comm="nccl"):
         self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
         self.max_seq = int(max_seq); self.group = group
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -169,6 +202,13 @@ class TPDecoder:
         self.graph = None
         self.history = []
         self.allreduce_calls = 0
+        # comm: "nccl" = torch.distributed all-reduce + a separate residual add; "p2p" = the one-shot
+        # peer-store all-reduce with the residual add folded in
+        self.comm = None
+        if world > 1 and comm == "p2p":
+            self.comm = P2PComm(rank, world, B * E, group)
+        elif comm not in ("nccl", "p2p"):
+            raise ValueError(f"comm={comm!r}")
 
     # ------------------------------------------------------------------ weights
     def _random(self, seed):
@@ -247,6 +287,10 @@ class TPDecoder:
         B, E = self.B, self.plan.E
         if self.world == 1:
             self._gemm(W, out, B, resid, E)
+        elif self.comm is not None:
+            self._gemm(W, self.part, B)
+            self.comm.allreduce_add(self.part, resid, out, B * E)
+            self.allreduce_calls += 1
         else:
             self._gemm(W, self.part, B)
             self._allreduce(self.part)

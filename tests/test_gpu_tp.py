@@ -102,3 +102,4 @@ def test_world2_matches_world1(tmp_path):
         assert np.array_equal(res[k]["toks"], np.stack(rt)), k
         assert np.array_equal(res[k]["more"], rmore), k
         assert int(res[k]["status"]) == 0
+        assert int(res[k]["p2p_equals_nccl"]) == 1

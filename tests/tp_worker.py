@@ -19,19 +19,24 @@ def main():
                             timeout=datetime.timedelta(seconds=60))
     from llamatov_b200 import _lib, synth, tp
     m = synth.make_model("tiny-llama", seed=8)
-    d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m)
-    d.fill_cache(6, seed=2)
-    d.set_tokens([5, 600])
-    toks, logits = [], []
-    for _ in range(6):
-        d.step()
-        torch.cuda.synchronize()
-        toks.append(d.tok.cpu().numpy().copy()); logits.append(d.logits.cpu().numpy().copy())
-    d.capture()
-    more = d.run(3)
+    res = {}
+    for comm in ("nccl", "p2p"):
+        d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m, comm=comm)
+        d.fill_cache(6, seed=2)
+        d.set_tokens([5, 600])
+        toks, logits = [], []
+        for _ in range(6):
+            d.step()
+            torch.cuda.synchronize()
+            toks.append(d.tok.cpu().numpy().copy()); logits.append(d.logits.cpu().numpy().copy())
+        d.capture()
+        more = d.run(3)
+        res[comm] = (np.stack(toks), np.concatenate(logits, axis=0), more)
     status = _lib.device_status()
-    np.savez(os.path.join(out, f"rank{rank}.npz"), toks=np.stack(toks), logits=np.concatenate(logits, axis=0),
-             more=more, status=np.int32(len(status)))
+    same = all(np.array_equal(a, b) for a, b in zip(res["nccl"], res["p2p"]))      # two ranks: one addition, same bits
+    toks, logits, more = res["p2p"]
+    np.savez(os.path.join(out, f"rank{rank}.npz"), toks=toks, logits=logits, more=more, status=np.int32(len(status)),
+             p2p_equals_nccl=np.int32(same))
     dist.barrier()
     torch.cuda.synchronize()
 
