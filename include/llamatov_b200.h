@@ -101,6 +101,11 @@ int lt_q8_gemm_tc(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const 
  * pairwise tree, inv = rsqrtf(ss/N + eps), y = (x*inv)*w.  M rows of N. */
 int lt_rmsnorm(const float* x, const float* w, float* y, int M, int N, float eps, void* stream);
 
+/* lt_rmsnorm followed by lt_quant_q8 in one launch (the reference's RMS-quant production pairing,
+ * bpd/kernelgen/referee/rms_quant_prod_ab.py); y may be NULL when only the quantised row is wanted. */
+int lt_rmsnorm_quant(const float* x, const float* w, float* y, int8_t* Xq, uint16_t* Xd, int M, int N, float eps,
+                     void* stream);
+
 /* ---- RoPE ------------------------------------------------------------------------------
  * replaces k_rope (bpd/kernelgen/emitters/rope_from_facts.pl:40-69; launched from
  * bpd/lib/dev_residency.py:701-742).  NeoX half-split rotation in place of X[nrows, n_head*hd]

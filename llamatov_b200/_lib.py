@@ -27,6 +27,7 @@ SIGNATURES = {
     "lt_q8_gemv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_q8_gemm_tc": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "lt_rmsnorm": [_vp, _vp, _vp, _i, _i, _f, _vp],
+    "lt_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_rope": [_vp, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_incr_len": [_vp, _vp],

@@ -158,18 +158,23 @@ k_attn_softmax(float* __restrict__ S, int s_ld, const int* __restrict__ lens, fl
 // dependent chain per output element; what can be spread is the loading: the CTA stages tiles of
 // PV_TT positions (its 32 columns of V, and the probabilities of its heads) in shared memory with
 // asynchronous copies, one tile ahead of the fold.
-constexpr int PV_TT = 128;
+constexpr int PV_TT = 128;    // positions per tile
+// tiles in flight per CTA: 4 when few CTAs stream the cache (one sequence: each CTA's V stream is
+// latency-bound otherwise), 2 when the batch supplies CTAs enough and residency matters more
+constexpr size_t pv_smem(int stages) { return (size_t)stages * (PV_TT * 32 + MAX_REP * PV_TT) * sizeof(float); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src)
                  : "memory");
 }
 
+template <int PV_STAGES>
 __global__ void __launch_bounds__(32 * MAX_REP)
 k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
           const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq) {
-    __shared__ __align__(16) float vt[2][PV_TT][32];
-    __shared__ __align__(16) float pt[2][MAX_REP][PV_TT];
+    extern __shared__ __align__(16) float pv_smem[];
+    float (*vt)[PV_TT][32] = (float (*)[PV_TT][32])pv_smem;                                  // [stage][t][d]
+    float (*pt)[MAX_REP][PV_TT] = (float (*)[MAX_REP][PV_TT])(pv_smem + PV_STAGES * PV_TT * 32);   // [stage][head][t]
     const int b = blockIdx.z, hk = blockIdx.y;
     const int rep = nh / nkv;
     const int dl = threadIdx.x & 31, r = threadIdx.x >> 5;
@@ -183,38 +188,46 @@ k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, co
     const int nthreads = 32 * rep;
     const int tiles = (L + PV_TT - 1) / PV_TT;
 
-    auto stage = [&](int k) {
-        const int buf = k & 1, t0 = k * PV_TT;
-        for (int i = threadIdx.x; i < PV_TT * 8; i += nthreads) {
-            const int row = i >> 3, c = i & 7;
-            if (t0 + row < L) cp_async16(&vt[buf][row][c * 4], Vb + (long)(t0 + row) * vs + c * 4);
-        }
-        for (int i = threadIdx.x; i < rep * (PV_TT / 4); i += nthreads) {
-            const int hr = i / (PV_TT / 4), c = i - hr * (PV_TT / 4);
-            if (t0 + c * 4 < L) cp_async16(&pt[buf][hr][c * 4], Pb + (long)hr * s_ld + t0 + c * 4);
+    auto stage = [&](int k) {   // always commits a group, so that group k is tile k
+        if (k < tiles) {
+            const int buf = k % PV_STAGES, t0 = k * PV_TT;
+            for (int i = threadIdx.x; i < PV_TT * 8; i += nthreads) {
+                const int row = i >> 3, c = i & 7;
+                if (t0 + row < L) cp_async16(&vt[buf][row][c * 4], Vb + (long)(t0 + row) * vs + c * 4);
+            }
+            for (int i = threadIdx.x; i < rep * (PV_TT / 4); i += nthreads) {
+                const int hr = i / (PV_TT / 4), c = i - hr * (PV_TT / 4);
+                if (t0 + c * 4 < L) cp_async16(&pt[buf][hr][c * 4], Pb + (long)hr * s_ld + t0 + c * 4);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     float acc = 0.0f;
-    if (tiles > 0) stage(0);
+    for (int k = 0; k < PV_STAGES - 1; k++) stage(k);
     for (int k = 0; k < tiles; k++) {
-        if (k + 1 < tiles) {
-            stage(k + 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        stage(k + PV_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(PV_STAGES - 1) : "memory");
         __syncthreads();
-        const int buf = k & 1;
+        const int buf = k % PV_STAGES;
         const int n = L - k * PV_TT < PV_TT ? L - k * PV_TT : PV_TT;
         const float* pr = pt[buf][r];
+        const float* vc = &vt[buf][0][dl];
         int t = 0;
-        for (; t + 8 <= n; t += 8) {
+        // the fold is one dependent chain; the shared-memory reads of 16 steps are issued together, ahead of it
+        for (; t + 16 <= n; t += 16) {
+            float pp[16], vv[16];
 #pragma unroll
-            for (int u = 0; u < 8; u++) acc = __fmaf_rn(pr[t + u], vt[buf][t + u][dl], acc);
+            for (int u = 0; u < 4; u++) {
+                const float4 p4 = *(const float4*)(pr + t + 4 * u);
+                pp[4 * u] = p4.x; pp[4 * u + 1] = p4.y; pp[4 * u + 2] = p4.z; pp[4 * u + 3] = p4.w;
+            }
+#pragma unroll
+            for (int u = 0; u < 16; u++) vv[u] = vc[(t + u) * 32];
+#pragma unroll
+            for (int u = 0; u < 16; u++) acc = __fmaf_rn(pp[u], vv[u], acc);
         }
-        for (; t < n; t++) acc = __fmaf_rn(pr[t], vt[buf][t][dl], acc);
+        for (; t < n; t++) acc = __fmaf_rn(pr[t], vc[t * 32], acc);
         __syncthreads();
     }
     OUT[(long)b * out_ld + (long)h * hd + d0 + dl] = __fdiv_rn(acc, Z[(long)b * nh + h]);
@@ -272,11 +285,18 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
     static bool attr_done = false;
     if (!attr_done) {
         LT_CUDA(cudaFuncSetAttribute(k_attn_softmax, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(4)));
+        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(2)));
         attr_done = true;
     }
     k_attn_scores<<<dim3((max_seq + BT - 1) / BT, nkv, B), BT, (size_t)rep * hd * sizeof(float), s>>>(
         Q, q_ld, K, lens, S, s_ld, hd, nh, nkv, scale, max_seq, st);
     k_attn_softmax<<<dim3(nh, B), BT, (size_t)max_seq * sizeof(float), s>>>(S, s_ld, lens, Z, nh, max_seq);
-    k_attn_pv<<<dim3(hd / 32, nkv, B), 32 * rep, 0, s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv, max_seq);
+    if ((long)(hd / 32) * nkv * B >= 592)
+        k_attn_pv<2><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(2), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
+                                                                        max_seq);
+    else
+        k_attn_pv<4><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(4), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
+                                                                        max_seq);
     return check_launch("lt_attn_decode_batch", 3);
 }

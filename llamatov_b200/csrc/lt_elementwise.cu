@@ -84,6 +84,29 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float* __restrict__ x, co
     for (int j = threadIdx.x; j < N; j += 256) yr[j] = __fmul_rn(__fmul_rn(xr[j], inv), w[j]);
 }
 
+// RMSNorm and the activation quantiser in one launch (row per CTA): the normalised value goes
+// straight into the warp-wide block quantiser (a warp holds one 32-block per round), the same two
+// computations as k_rmsnorm followed by k_quant_q8.
+__global__ void __launch_bounds__(256) k_rmsnorm_quant(const float* __restrict__ x, const float* __restrict__ w,
+                                                        float* __restrict__ y, int8_t* __restrict__ Xq,
+                                                        __half* __restrict__ Xd, int M, int N, float eps) {
+    __shared__ float sred[256];
+    int row = blockIdx.x;
+    if (row >= M) return;
+    const float* xr = x + (long)row * N;
+    float ss = rms_sumsq_256(xr, N, sred);
+    float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)N), eps));
+    const int nb = N >> 5;
+    for (int j = threadIdx.x; j < N; j += 256) {
+        const float v = __fmul_rn(__fmul_rn(xr[j], inv), w[j]);
+        if (y != nullptr) y[(long)row * N + j] = v;
+        __half dh;
+        const int q = quant_lane(v, &dh);
+        Xq[(long)row * N + j] = (int8_t)q;
+        if ((threadIdx.x & 31) == 0) Xd[(long)row * nb + (j >> 5)] = dh;
+    }
+}
+
 // ------------------------------------------------------------------ RoPE
 __global__ void k_rope(float* __restrict__ X, const int* __restrict__ pos, int nrows, int n_head, int hd,
                        float theta) {
@@ -264,6 +287,14 @@ extern "C" int lt_rmsnorm(const float* x, const float* w, float* y, int M, int N
     LT_REQUIRE(M > 0 && N > 0, "lt_rmsnorm: M=%d N=%d must be positive", M, N);
     k_rmsnorm<<<M, 256, 0, (cudaStream_t)stream>>>(x, w, y, M, N, eps);
     return check_launch("lt_rmsnorm");
+}
+
+extern "C" int lt_rmsnorm_quant(const float* x, const float* w, float* y, int8_t* Xq, uint16_t* Xd, int M, int N,
+                                float eps, void* stream) {
+    LT_REQUIRE(x && w && Xq && Xd, "lt_rmsnorm_quant: null pointer");
+    LT_REQUIRE(M > 0 && N > 0 && N % 32 == 0, "lt_rmsnorm_quant: M=%d, N=%d must be a positive multiple of 32", M, N);
+    k_rmsnorm_quant<<<M, 256, 0, (cudaStream_t)stream>>>(x, w, y, Xq, (__half*)Xd, M, N, eps);
+    return check_launch("lt_rmsnorm_quant");
 }
 
 extern "C" int lt_rope(float* X, const int* pos, int nrows, int n_head, int hd, float theta, void* stream) {

@@ -179,13 +179,15 @@ def run_tp_decode(args):
     wbytes = (L * ((nq + 2 * nk) * E + E * nq + 2 * F * E + E * F) + V * E) // 32 * 34
     for B in args.batch:
         max_seq = args.ctx + args.steps + 8
-        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0)
+        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=args.comm)
         dec.fill_cache(args.ctx, seed=1)
         start = np.random.default_rng(0).integers(0, V, size=B)
         dec.set_tokens(start)
         dec.capture()                               # one warm-up step inside
+        warm = [dec.tok.clone()]
         for _ in range(max(0, args.warmup - 1)):
             dec.graph.replay()
+            warm.append(dec.tok.clone())
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -205,32 +207,54 @@ def run_tp_decode(args):
         # the all-reduces of one step alone, back to back (2 per layer, [B, E] fp32)
         ar_ms = 0.0
         if world > 1:
-            buf = torch.zeros((B, E), device="cuda")
+            buf = torch.zeros((B, E), device="cuda"); buf2 = torch.zeros((B, E), device="cuda")
             side = torch.cuda.Stream()
+
+            def one():
+                if dec.comm is not None:
+                    dec.comm.allreduce_add(buf, None, buf2, B * E)
+                else:
+                    dist.all_reduce(buf)
             with torch.cuda.stream(side):
-                dist.all_reduce(buf)
+                one()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
                 for _ in range(2 * L):
-                    dist.all_reduce(buf)
+                    one()
             g.replay(); torch.cuda.synchronize()
+            dist.barrier()
             ar_ms = _event_ms(lambda i: g.replay(), 10)
             t = torch.tensor([ar_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ar_ms = float(t.item())
         status = sorted(_lib.device_status())
         match = None
         if args.check_world1 and world > 1 and rank == 0:
+            # world 1 on this GPU, teacher-forced with the sharded run's tokens: does it choose the same
+            # next token from the same history, and if not, how far apart are the two candidates' logits
+            launches = dec.launches_per_step
             del dec
             torch.cuda.empty_cache()
             ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0)
             ref.fill_cache(args.ctx, seed=1)
             ref.set_tokens(start)
-            ref.step()                              # the warm-up step of capture()
-            for _ in range(max(0, args.warmup - 1)):
+            warm_h = torch.stack(warm).cpu().numpy()
+            allt = np.concatenate([warm_h, toks], axis=0)      # every token the sharded run produced, warm-up included
+            agree, worst = 0, 0.0
+            for sidx in range(allt.shape[0]):
                 ref.step()
-            rt = ref.run(args.steps)
-            match = float((rt == toks).mean())
+                rt = ref.tok.cpu().numpy()
+                lg = ref.logits
+                for b in range(B):
+                    if rt[b] == allt[sidx, b]:
+                        agree += 1
+                    else:
+                        worst = max(worst, float(lg[b, int(rt[b])] - lg[b, int(allt[sidx, b])]))
+                ref.set_tokens(allt[sidx])
+            match = {"same_next_token_given_same_history": agree / (allt.shape[0] * B),
+                     "largest_logit_gap_where_different": worst}
             del ref
+        else:
+            launches = dec.launches_per_step
         if rank == 0:
             step_ms = ms / args.steps
             kv_bytes = B * L * 2 * (args.ctx + args.steps // 2) * nk * 4
@@ -239,7 +263,7 @@ def run_tp_decode(args):
                 "metric": "decode tok/s (Q8_0, tensor-parallel)", "value": B * args.steps / (ms * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "ms_per_step": step_ms, "steps": args.steps, "warmup": args.warmup,
                 "config": {"workload": f"{args.arch} Q8_0 decode, batch {B}, context {args.ctx}, TP={world}",
-                           "layers": L, "launches_per_step": dec.launches_per_step if match is None else None},
+                           "layers": L, "launches_per_step": launches, "comm": args.comm if world > 1 else None},
                 "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
                              "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
                              "frac": step_bytes / (step_ms * 1e-3) / 1e9 / (hbm * world), "peak_source": src},
@@ -276,6 +300,7 @@ def main(argv=None):
     t.add_argument("--steps", type=int, default=128)
     t.add_argument("--warmup", type=int, default=3)
     t.add_argument("--layers", type=int, default=0, help="fewer layers than the architecture (smoke runs)")
+    t.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
     t.add_argument("--check-world1", action="store_true", help="rank 0 re-runs at world 1 and compares the tokens")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

@@ -83,11 +83,19 @@ def take_cols(Wq, Wd, k0, k1):
     return Wq[:, k0:k1].contiguous(), Wd[:, k0 // 32:k1 // 32].contiguous()
 
 
-def random_q8(N, K, gen, device):
-    """Seeded random Q8_0 blocks on the device: q ~ U{-127..127}, d = fp16(U(0,1) * 0.02 / sqrt(K/896))."""
-    Wq = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=device, generator=gen)
-    sc = 0.02 / float(np.sqrt(K / 896.0))
-    Wd = (torch.rand((N, K // 32), device=device, generator=gen) * sc).to(torch.float16)
+def random_q8(N, K, gen, device, sigma=0.02):
+    """Seeded random-init weights N(0, sigma) quantised to Q8_0 on the device with the engine's weight rule
+    (bpd/lib/fact_dispatch.py:255-282: per 32-block d = fp16(amax/127), 1.0 if 0; q = clip(round(w / f32(d))))."""
+    Wq = torch.empty((N, K), dtype=torch.int8, device=device)
+    Wd = torch.empty((N, K // 32), dtype=torch.float16, device=device)
+    step = max(1, (1 << 26) // K)
+    for r0 in range(0, N, step):
+        r1 = min(N, r0 + step)
+        w = torch.randn((r1 - r0, K // 32, 32), generator=gen, dtype=torch.float32, device=device) * sigma
+        d = (w.abs().amax(dim=-1) / 127.0).to(torch.float16)
+        d = torch.where(d == 0, torch.ones_like(d), d)
+        Wd[r0:r1] = d
+        Wq[r0:r1] = torch.clamp(torch.round(w / d.float().unsqueeze(-1)), -127, 127).to(torch.int8).view(r1 - r0, K)
     return Wq, Wd
 
 
@@ -276,6 +284,18 @@ class TPDecoder:
             _lib.call("lt_q8_gemm_tc", W.q.data_ptr(), W.d.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(),
                       None if resid is None else resid.data_ptr(), resid_ld, y.data_ptr(), W.N, W.K, T, 0, _stream())
 
+    def _norm_quant(self, x, w):
+        """RMSNorm + activation quantiser of the B rows.  One launch when there are rows enough to fill the
+        GPU (a row is one CTA); for a few rows the quantiser spreads better as its own launch."""
+        B, E = self.B, self.plan.E
+        eps = float(self.cfg["norm_eps"])
+        if B >= 16:
+            _lib.call("lt_rmsnorm_quant", x.data_ptr(), w.data_ptr(), None, self.xq.data_ptr(), self.xd.data_ptr(),
+                      B, E, eps, _stream())
+        else:
+            _lib.call("lt_rmsnorm", x.data_ptr(), w.data_ptr(), self.h.data_ptr(), B, E, eps, _stream())
+            _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, _stream())
+
     def _allreduce(self, t):
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
@@ -307,8 +327,7 @@ class TPDecoder:
         _lib.call("lt_embed_q8_rows", self.embd.q.data_ptr(), self.embd.d.data_ptr(), self.tok.data_ptr(),
                   self.x.data_ptr(), E, p.V, B, st())
         for il, ly in enumerate(self.layers):
-            _lib.call("lt_rmsnorm", self.x.data_ptr(), ly["attn_norm"].data_ptr(), self.h.data_ptr(), B, E, eps, st())
-            _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+            self._norm_quant(self.x, ly["attn_norm"])
             self._gemm(ly["qkv"], self.qkv, B)
             lens = self.lens[il]
             _lib.call("lt_rope_batch", self.qkv.data_ptr(), qld, lens.data_ptr(), B, p.nh_l + p.nkv_l, hd, theta, st())
@@ -320,14 +339,12 @@ class TPDecoder:
                       scale, self.max_seq, B, st())
             _lib.call("lt_quant_q8", self.att.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), p.nq_l, B, st())
             self._row_split(ly["o"], self.x, self.x1)
-            _lib.call("lt_rmsnorm", self.x1.data_ptr(), ly["ffn_norm"].data_ptr(), self.h.data_ptr(), B, E, eps, st())
-            _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+            self._norm_quant(self.x1, ly["ffn_norm"])
             self._gemm(ly["gateup"], self.gu, B)
             _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
                       self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
             self._row_split(ly["down"], self.x1, self.x)
-        _lib.call("lt_rmsnorm", self.x.data_ptr(), self.out_norm.data_ptr(), self.h.data_ptr(), B, E, eps, st())
-        _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, st())
+        self._norm_quant(self.x, self.out_norm)
         self._gemm(self.lm, self.logits, B)
         nv = self.lm.N
         stride = _lib.lib().lt_argmax_scratch_bytes() // 4

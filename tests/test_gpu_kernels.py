@@ -181,6 +181,25 @@ def test_rmsnorm(oracle, M, N, eps):
 
 
 # ------------------------------------------------------------------ RoPE
+def test_rmsnorm_quant_equals_the_two_launches():
+    rng = np.random.default_rng(5)
+    M, N = 3, 4096
+    x = rng.standard_normal((M, N)).astype(np.float32) * 3
+    w = (1 + 0.1 * rng.standard_normal(N)).astype(np.float32)
+    dx, dw = dev(x.reshape(-1)), dev(w)
+    y = torch.empty(M * N, device="cuda"); y2 = torch.empty(M * N, device="cuda")
+    xq = torch.empty(M * N, dtype=torch.int8, device="cuda"); xd = torch.empty(M * N // 32, dtype=torch.int16, device="cuda")
+    xq2 = torch.empty_like(xq); xd2 = torch.empty_like(xd)
+    _lib.call("lt_rmsnorm", dx.data_ptr(), dw.data_ptr(), y.data_ptr(), M, N, 1e-5, stream())
+    _lib.call("lt_quant_q8", y.data_ptr(), xq.data_ptr(), xd.data_ptr(), N, M, stream())
+    _lib.call("lt_rmsnorm_quant", dx.data_ptr(), dw.data_ptr(), y2.data_ptr(), xq2.data_ptr(), xd2.data_ptr(), M, N, 1e-5,
+              stream())
+    assert np.array_equal(bits(host(y)), bits(host(y2)))
+    assert np.array_equal(host(xq), host(xq2)) and np.array_equal(host(xd), host(xd2))
+    _lib.call("lt_rmsnorm_quant", dx.data_ptr(), dw.data_ptr(), None, xq2.data_ptr(), xd2.data_ptr(), M, N, 1e-5, stream())
+    assert np.array_equal(host(xq), host(xq2)) and np.array_equal(host(xd), host(xd2))
+
+
 @pytest.mark.parametrize("theta,hd,nh", [(1e6, 64, 16), (5e5, 128, 40)])
 def test_rope(oracle, theta, hd, nh):
     rng = np.random.default_rng(int(hd))
