@@ -2,6 +2,7 @@
 
   python -m llamatov_b200.measure prefill [--tokens 2048] [--batch 1 8] [--arch qwen2.5-0.5b]
   python -m llamatov_b200.measure gemv-sweep [--batch 1 4 16 64]
+  python -m llamatov_b200.measure gemm -m 4864 -k 896 -t 2048 [--variant 1]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       -m llamatov_b200.measure tp-decode [--batch 1 32] [--ctx 4096] [--steps 128] [--check-world1]
 
@@ -154,6 +155,35 @@ def run_gemv_sweep(args):
     print(json.dumps({"device_status": sorted(_lib.device_status())}))
 
 
+def run_gemm(args):
+    """One Q8_0 GEMM shape through lt_q8_gemm_tc (or lt_q8_gemv with --variant -1), resident random data."""
+    hbm, _tf, src = peaks()
+    M, K, T = args.m, args.k, args.t
+    nb = K // 32
+    Wq = torch.randint(-127, 128, (M * K,), dtype=torch.int8, device="cuda")
+    Wd = (torch.rand((M * nb,), device="cuda") * 0.02).to(torch.float16).view(torch.int16)
+    xq = torch.randint(-127, 128, (T * K,), dtype=torch.int8, device="cuda")
+    xd = (torch.rand((T * nb,), device="cuda") * 0.05).to(torch.float16).view(torch.int16)
+    y = torch.empty(T * M, dtype=torch.float32, device="cuda")
+
+    def run(i):
+        if args.variant < 0:
+            _lib.call("lt_q8_gemv", Wq.data_ptr(), Wd.data_ptr(), xq.data_ptr(), xd.data_ptr(), None, y.data_ptr(),
+                      M, K, T, _stream())
+        else:
+            _lib.call("lt_q8_gemm_tc", Wq.data_ptr(), Wd.data_ptr(), xq.data_ptr(), xd.data_ptr(), None, 0,
+                      y.data_ptr(), M, K, T, args.variant, _stream())
+    for i in range(args.warmup):
+        run(i)
+    torch.cuda.synchronize()
+    ms = _event_ms(run, args.steps)
+    b = gemv_bytes(M, K, T)
+    print(json.dumps({"M": M, "K": K, "T": T, "variant": args.variant, "us": ms * 1e3,
+                      "output_blocks_per_s": M * nb * T / (ms * 1e-3), "int8_tmacs_per_s": M * K * T / (ms * 1e-3) / 1e12,
+                      "algorithmic_GBs": b / (ms * 1e-3) / 1e9, "frac_of_hbm": b / (ms * 1e-3) / 1e9 / hbm,
+                      "device_status": sorted(_lib.device_status()), "peak_source": src}))
+
+
 def run_tp_decode(args):
     """Llama-3-8B-architecture (or --arch) random-init Q8_0 decode, tensor-parallel over the ranks this
     program was launched with (torch.distributed.run; a plain launch is world 1).  KV caches pre-filled
@@ -293,6 +323,11 @@ def main(argv=None):
     p.add_argument("--warmup", type=int, default=1)
     g = sub.add_parser("gemv-sweep")
     g.add_argument("--batch", type=int, nargs="+", default=[1, 4, 16, 64])
+    m = sub.add_parser("gemm")
+    m.add_argument("-m", type=int, required=True); m.add_argument("-k", type=int, required=True)
+    m.add_argument("-t", type=int, required=True)
+    m.add_argument("--variant", type=int, default=0, help="lt_q8_gemm_tc variant; -1 = lt_q8_gemv dispatch")
+    m.add_argument("--steps", type=int, default=2); m.add_argument("--warmup", type=int, default=1)
     t = sub.add_parser("tp-decode")
     t.add_argument("--arch", default="llama-3-8b")
     t.add_argument("--batch", type=int, nargs="+", default=[1, 32])
@@ -309,6 +344,8 @@ def main(argv=None):
         run_prefill(args)
     elif args.cmd == "tp-decode":
         run_tp_decode(args)
+    elif args.cmd == "gemm":
+        run_gemm(args)
     else:
         run_gemv_sweep(args)
 
