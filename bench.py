@@ -14,10 +14,11 @@ Printed JSON line (rank 0):
   e2e          tok/s through the reference-facing call GraphRunner.replay_token(tok): per
                token the host looks up the embedding row, copies it to the device (E*4 bytes),
                launches the graph, synchronises and reads the chosen token back (4 bytes).
-  roofline     the Q8_0 GEMV kernel: algorithmic bytes of all GEMV launches of one token
-               (34 bytes per 32 weights + activation and result vectors) divided by the time
-               of exactly those launches replayed back to back (a captured GEMV-only chain,
-               CUDA events on its stream), against the measured HBM copy bandwidth.
+  roofline     the decode step as a whole: algorithmic bytes of one token (34 bytes per 32 weights of
+               every matrix + the fp32 KV rows read once per KV head) divided by the device time per
+               token (CUDA events on the replay stream), against the measured HBM copy bandwidth;
+               traffic = DRAM bytes of one token's launches from an ncu capture of this command.  The
+               one launch that is bandwidth-bound by itself, the LM-head GEMV, is also timed alone.
   cpu_baseline the CPU port of the same path (oracle/) timed on this box's host cores on a
                bounded sample (N=1 only).
 With N > 1 every rank runs an independent replica of the model (the 0.5B model does not
