@@ -263,3 +263,24 @@ def test_qwen05b_greedy_128_tokens_identical_to_reference_kernels(oracle):
           f"max logit drift vs CPU oracle {drift:.4f}")
     assert drift < 0.25
     assert agree >= n_new - 8
+
+
+def test_generate_from_gguf_equals_engine_on_the_same_weights(tmp_path):
+    # the reference's runner entry points: write a synthetic model as GGUF, load it back as Q8_0 blocks,
+    # generate through the graph runner, compare with eager decoding on the original arrays
+    from llamatov_b200 import decode_fact, llamatov_run as R
+    m, w, cfg = _fresh("tiny-qwen64", seed=11)
+    a = cfg["arch"]
+    md = {"general.architecture": a, f"{a}.block_count": cfg["n_layers"], f"{a}.attention.head_count": cfg["n_head"],
+          f"{a}.attention.head_count_kv": cfg["n_head_kv"], f"{a}.embedding_length": cfg["n_embd"],
+          f"{a}.rope.freq_base": float(cfg["rope_theta"]), f"{a}.attention.layer_norm_rms_epsilon": float(cfg["norm_eps"])}
+    path = str(tmp_path / "m.gguf")
+    R.write_gguf(path, md, w)
+    prompt = _prompt(m["cfg"]["vocab"], 6, seed=4)
+    want, _, _ = _run_gpu_eager(w, cfg, prompt, 9)
+    dr.reset_engine_state()
+    got = R.generate(path, prompt, 10, verbose=False)
+    assert got == want
+    dr.reset_engine_state()
+    got2 = decode_fact.decode(path, prompt, 10)
+    assert got2 == want
