@@ -277,7 +277,7 @@ def test_generate_from_gguf_equals_engine_on_the_same_weights(tmp_path):
     path = str(tmp_path / "m.gguf")
     R.write_gguf(path, md, w)
     prompt = _prompt(m["cfg"]["vocab"], 6, seed=4)
-    want, _, _ = _run_gpu_eager(w, cfg, prompt, 9)
+    want, _, _ = _run_gpu_eager(w, cfg, prompt, 10)
     dr.reset_engine_state()
     got = R.generate(path, prompt, 10, verbose=False)
     assert got == want
