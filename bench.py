@@ -171,6 +171,90 @@ def run_reference(args, rank):
                       "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def run_config0(args):
+    """BASELINE config 0: the single Q8_0 GEMV y = W x, W 4864 x 896 (28 blocks per row, d = fp16(|N(0,1)| * 0.02),
+    q ~ U{-127..127}), x ~ N(0,1) fp32[896], numpy default_rng(0).  Prints one JSON line: the GPU result against
+    the CPU oracle (bit-exact target), against a float64 dequantise-and-dot, and against the reference's own
+    compiled CPU path (bpd_qmatmul_q8_0_llamafile_cpu from oracle/_ref/libbpd_cpu.so, a different fp32 order and
+    quantiser) where that library was built; the GEMV's steady-state bandwidth; the CPU path's time."""
+    import torch
+    from llamatov_b200 import _lib, synth
+    from oracle import oracle as o
+    M, K = 4864, 896
+    nb = K // 32
+    Wq, Wd, x = synth.gemv_case(M, K, seed=0)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    dWq = torch.from_numpy(Wq).cuda(); dWd = torch.from_numpy(Wd.view(np.int16)).cuda()
+    dx = torch.from_numpy(x[0]).cuda()
+    xq = torch.empty(K, dtype=torch.int8, device="cuda"); xd = torch.empty(nb, dtype=torch.int16, device="cuda")
+    y = torch.empty(M, dtype=torch.float32, device="cuda")
+    _lib.call("lt_quant_q8", dx.data_ptr(), xq.data_ptr(), xd.data_ptr(), K, 1, st)
+    _lib.call("lt_q8_gemv", dWq.data_ptr(), dWd.data_ptr(), xq.data_ptr(), xd.data_ptr(), None, y.data_ptr(), M, K, 1, st)
+    torch.cuda.synchronize()
+    yg = y.cpu().numpy()
+    oq, od = o.quant_q8(x[0])
+    want = np.asarray(o.q8_gemv(Wq, Wd, oq, od, M, K), np.float32)
+    quant_equal = bool(np.array_equal(xq.cpu().numpy(), oq) and np.array_equal(xd.cpu().numpy().view(np.uint16), od.view(np.uint16)))
+    ulp = int(np.max(np.abs(yg.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))))
+    Wf = Wq.reshape(M, nb, 32).astype(np.float64) * Wd.reshape(M, nb, 1).astype(np.float64)
+    y64 = Wf.reshape(M, K) @ x[0].astype(np.float64)
+    den = float(np.max(np.abs(y64)))
+    rel64 = float(np.max(np.abs(yg - y64)) / den)
+    # steady-state bandwidth: captured chain over rotating copies (no launch finds its matrix in L2)
+    R = 64
+    Wqs = dWq.repeat(R, 1); Wds = dWd.repeat(R, 1)
+    side = torch.cuda.Stream()
+
+    def run(i):
+        _lib.call("lt_q8_gemv", Wqs[i % R].data_ptr(), Wds[i % R].data_ptr(), xq.data_ptr(), xd.data_ptr(), None,
+                  y.data_ptr(), M, K, 1, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i in range(2 * R):
+            run(i)
+    with torch.cuda.stream(side):
+        for _ in range(max(3, args.warmup)):
+            g.replay()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+    torch.cuda.synchronize()
+    us = 1000.0 * e0.elapsed_time(e1) / (10 * 2 * R)
+    peak, peak_src = _peaks()
+    gbs = gemv_bytes(M, K) / (us * 1e-6) / 1e9
+    out = {"metric": "Q8_0 GEMV HBM GB/s (4864x896, batch 1)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+           "us_per_launch": us, "higher_is_better": True, "dtype": "int8*int8->int32, fp32 accumulate", "data": "synthetic",
+           "config": {"workload": "single Q8_0 GEMV 4864x896, x ~ N(0,1), numpy default_rng(0)"},
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                        "traffic": None, "peak_source": peak_src},
+           "parity": {"activation_quant_bytes_equal_oracle": quant_equal, "max_ulp_vs_oracle": ulp,
+                      "max_rel_vs_float64_dequant_dot": rel64}}
+    ref_so = os.path.join(ROOT, "oracle", "_ref", "libbpd_cpu.so")
+    if os.path.exists(ref_so):
+        L = ctypes.CDLL(ref_so)
+        fn = L.bpd_qmatmul_q8_0_llamafile_cpu
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        fn.restype = None
+        blocks = np.empty((M * nb, 34), np.uint8)
+        blocks[:, :2] = Wd.view(np.uint8).reshape(M * nb, 2); blocks[:, 2:] = Wq.view(np.uint8).reshape(M * nb, 32)
+        xa = np.ascontiguousarray(x[0], np.float32); ya = np.zeros(M, np.float32)
+        fn(blocks.ctypes.data, xa.ctypes.data, ya.ctypes.data, M, 1, K)
+        t0 = time.perf_counter(); n = 0
+        while time.perf_counter() - t0 < 2.0:
+            fn(blocks.ctypes.data, xa.ctypes.data, ya.ctypes.data, M, 1, K); n += 1
+        dt = (time.perf_counter() - t0) / n
+        out["parity"]["max_rel_vs_reference_cpu_path"] = float(np.max(np.abs(yg - ya)) / den)
+        out["cpu_baseline"] = {"value": gemv_bytes(M, K) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "reference",
+                               "sample": f"{n} calls of bpd_qmatmul_q8_0_llamafile_cpu (bpd-substrate/bench/bpd_cpu.c:4419, "
+                                         "single-threaded) on the same matrix", "us_per_call": dt * 1e6}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -178,6 +262,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config0", action="store_true", help="the single-GEMV case (BASELINE config 0) instead of decode")
     ap.add_argument("--step-mode", default=None, choices=["pdl", "persistent", "per-op"],
                     help="how the captured decode step is built (default: the engine's default)")
     args = ap.parse_args()
@@ -185,6 +270,10 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.config0:
+        if rank == 0:
+            run_config0(args)
         return
     if args.warmup < 3:
         args.warmup = 3
@@ -308,7 +397,7 @@ def main():
                 "algorithmic_bytes_per_token": step_bytes,
                 "us_per_token": 1000.0 * dev_ms / K,
                 "peak_source": peak_src,
-                "lm_head_gemv_alone": {"kernel": "lt::k_q8_gemv<4,1>", "shape": [N_, K_], "us": lm_us,
+                "lm_head_gemv_alone": {"kernel": "lt::k_q8_gemv1<4,1>", "shape": [N_, K_], "us": lm_us,
                                        "achieved": lm_gbs, "frac": lm_gbs / peak}}
 
     value = world * K / (dev_ms * 1e-3)

@@ -258,7 +258,8 @@ int lt_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, co
  *                       lens[b] = length after the append.  Three launches (scores over position
  *                       chunks, softmax per head, V sum per output element) so that a long context
  *                       is scanned by many CTAs; every fold keeps the frozen order, results are
- *                       bit-identical to lt_attn_decode_masked.  scratch holds
+ *                       bit-identical to lt_attn_decode_masked.  Xq / Xd (both or neither): the Q8_0
+ *                       quantisation of the output rows (lt_quant_q8) written by the same launch.  scratch holds
  *                       lt_attn_decode_batch_scratch_floats(nh, max_seq, B) floats, 16-byte aligned. */
 int lt_rope_batch(float* X, int ld, const int* pos, int nrows, int n_head, int hd, float theta, void* stream);
 int lt_append_kv_batch(float* kbase, const float* ksrc, float* vbase, const float* vsrc, int src_ld, int* lens,
@@ -266,7 +267,12 @@ int lt_append_kv_batch(float* kbase, const float* ksrc, float* vbase, const floa
 long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B);
 int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* V, const int* lens, float* OUT,
                          int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
-                         void* stream);
+                         int8_t* Xq, uint16_t* Xd, void* stream);
+/* lt_rope_batch on the q and k heads of row b at position lens[b], then lt_append_kv_batch of the row's k|v
+ * part, in one launch; a row is q heads | k heads | v heads, ld floats apart.  ticket: B ints of device
+ * scratch, zero before the first call (the kernel leaves them zero). */
+int lt_rope_append_batch(float* X, int ld, int n_qhead, int n_kvhead, int hd, float theta, float* kbase,
+                         float* vbase, int* lens, int max_seq, int B, int* ticket, void* stream);
 
 /* ---- all-reduce over the GPUs of one node, fused with the residual add ---------------------
  * No counterpart in the reference (it is single-GPU).  For the tensor-parallel decode step:

@@ -43,7 +43,8 @@ SIGNATURES = {
     "lt_attn_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "lt_rope_batch": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv_batch": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
-    "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp],
+    "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
+    "lt_rope_append_batch": [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp, _vp],
     "lt_comm_alloc": [_i, _i, _vp, _vp],
     "lt_comm_connect": [_vp, _i, _vp],
     "lt_comm_free": [_vp],

@@ -59,6 +59,53 @@ __global__ void k_append_kv_batch(float* __restrict__ kbase, const float* __rest
     }
 }
 
+// ------------------------------------------------------------------ rope + append in one launch
+// grid (chunks, B): a CTA rotates 256 (x1, x2) pairs of the row's q and k heads at position lens[b];
+// rotated k pairs and the CTA's slice of the v row go straight to the cache at that position.  The
+// last CTA of a sequence to finish (a ticket per sequence, self-resetting) advances the length, when
+// every CTA of the sequence has long read it.  Same values as k_rope_batch + k_append_kv_batch.
+__global__ void __launch_bounds__(256)
+k_rope_append_batch(float* __restrict__ X, int ld, int n_qhead, int n_kvhead, int hd, float theta,
+                    float* __restrict__ kbase, float* __restrict__ vbase, int* __restrict__ lens, int max_seq,
+                    int* __restrict__ ticket, int* status) {
+    const int b = blockIdx.y;
+    const int L = lens[b];
+    const bool ok = L >= 0 && L < max_seq;
+    const int half = hd / 2;
+    float* row = X + (long)b * ld;
+    const int pairs = (n_qhead + n_kvhead) * half;
+    const int width = n_kvhead * hd;
+    const long off = ((long)b * max_seq + (ok ? L : 0)) * width;
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < pairs) {
+        const int head = i / half, j = i - head * half;
+        const long base = (long)head * hd;
+        float o1, o2;
+        rope_pair(row[base + j], row[base + j + half], j, hd, theta, L, o1, o2);
+        row[base + j] = o1;
+        row[base + j + half] = o2;
+        if (ok && head >= n_qhead) {
+            const long kb = off + (long)(head - n_qhead) * hd;
+            kbase[kb + j] = o1;
+            kbase[kb + j + half] = o2;
+        }
+    }
+    if (ok) {   // this CTA's slice of the v row
+        const float* vsrc = row + (long)(n_qhead + n_kvhead) * hd;
+        for (int c = blockIdx.x * 256 + threadIdx.x; c < width; c += gridDim.x * 256) vbase[off + c] = vsrc[c];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int t = atomicAdd(&ticket[b], 1);
+        if (t == (int)gridDim.x - 1) {
+            ticket[b] = 0;
+            if (!ok) atomicOr(status, (int)LT_STATUS_KV_OVERFLOW);
+            else lens[b] = L + 1;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ attention, phase 1: scores
 // grid (position chunks, nkv, B); S[(b*nh + h)*s_ld + t]
 __global__ void __launch_bounds__(BT)
@@ -171,7 +218,8 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 template <int PV_STAGES>
 __global__ void __launch_bounds__(32 * MAX_REP)
 k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
-          const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq) {
+          const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq,
+          int8_t* __restrict__ Xq, __half* __restrict__ Xd) {
     extern __shared__ __align__(16) float pv_smem[];
     float (*vt)[PV_TT][32] = (float (*)[PV_TT][32])pv_smem;                                  // [stage][t][d]
     float (*pt)[MAX_REP][PV_TT] = (float (*)[MAX_REP][PV_TT])(pv_smem + PV_STAGES * PV_TT * 32);   // [stage][head][t]
@@ -230,7 +278,15 @@ k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, co
         for (; t < n; t++) acc = __fmaf_rn(pr[t], vc[t * 32], acc);
         __syncthreads();
     }
-    OUT[(long)b * out_ld + (long)h * hd + d0 + dl] = __fdiv_rn(acc, Z[(long)b * nh + h]);
+    const float o = __fdiv_rn(acc, Z[(long)b * nh + h]);
+    OUT[(long)b * out_ld + (long)h * hd + d0 + dl] = o;
+    if (Xq != nullptr) {   // a warp holds one whole 32-block of the attention row: quantise it here
+        __half dh;
+        const int q = quant_lane(o, &dh);
+        const long col = (long)h * hd + d0 + dl;
+        Xq[(long)b * nh * hd + col] = (int8_t)q;
+        if (dl == 0) Xd[((long)b * nh * hd + col) >> 5] = dh;
+    }
 }
 
 }  // namespace lt
@@ -260,6 +316,20 @@ extern "C" int lt_append_kv_batch(float* kbase, const float* ksrc, float* vbase,
     return check_launch("lt_append_kv_batch");
 }
 
+extern "C" int lt_rope_append_batch(float* X, int ld, int n_qhead, int n_kvhead, int hd, float theta, float* kbase,
+                                    float* vbase, int* lens, int max_seq, int B, int* ticket, void* stream) {
+    LT_REQUIRE(X && kbase && vbase && lens && ticket, "lt_rope_append_batch: null pointer");
+    LT_REQUIRE(n_qhead > 0 && n_kvhead > 0 && hd > 0 && hd % 2 == 0 && B > 0 && max_seq > 0 &&
+                   ld >= (n_qhead + 2 * n_kvhead) * hd,
+               "lt_rope_append_batch: n_qhead=%d n_kvhead=%d hd=%d ld=%d B=%d max_seq=%d", n_qhead, n_kvhead, hd, ld, B, max_seq);
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_rope_append_batch: status word unavailable");
+    const int pairs = (n_qhead + n_kvhead) * (hd / 2);
+    k_rope_append_batch<<<dim3((pairs + 255) / 256, B), 256, 0, (cudaStream_t)stream>>>(
+        X, ld, n_qhead, n_kvhead, hd, theta, kbase, vbase, lens, max_seq, ticket, st);
+    return check_launch("lt_rope_append_batch");
+}
+
 extern "C" long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B) {
     const long s_ld = ((long)max_seq + 3) & ~3L;
     return (long)B * nh * s_ld + (long)B * nh;
@@ -267,7 +337,8 @@ extern "C" long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B) 
 
 extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* V, const int* lens,
                                     float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale,
-                                    int max_seq, int B, void* stream) {
+                                    int max_seq, int B, int8_t* Xq, uint16_t* Xd, void* stream) {
+    LT_REQUIRE((Xq == nullptr) == (Xd == nullptr), "lt_attn_decode_batch: Xq and Xd are given together or not at all");
     LT_REQUIRE(Q && K && V && lens && OUT && scratch, "lt_attn_decode_batch: null pointer");
     LT_REQUIRE(hd > 0 && hd % 32 == 0, "lt_attn_decode_batch: hd=%d must be a positive multiple of 32", hd);
     LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= MAX_REP,
@@ -294,9 +365,9 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
     k_attn_softmax<<<dim3(nh, B), BT, (size_t)max_seq * sizeof(float), s>>>(S, s_ld, lens, Z, nh, max_seq);
     if ((long)(hd / 32) * nkv * B >= 592)
         k_attn_pv<2><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(2), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
-                                                                        max_seq);
+                                                                        max_seq, Xq, (__half*)Xd);
     else
         k_attn_pv<4><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(4), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
-                                                                        max_seq);
+                                                                        max_seq, Xq, (__half*)Xd);
     return check_launch("lt_attn_decode_batch", 3);
 }

@@ -205,6 +205,7 @@ class TPDecoder:
         self.scratch = torch.empty(n, **f32)
         self.amax_part = torch.empty(_lib.lib().lt_argmax_scratch_bytes() // 4 * B, **f32)
         self.loc_idx = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        self.ticket = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self.pair = torch.zeros((B, 2), **f32)                   # (value, global index as float bits) per sequence
         self.gath = torch.zeros((world, B, 2), **f32)
         self.graph = None
@@ -330,14 +331,13 @@ class TPDecoder:
             self._norm_quant(self.x, ly["attn_norm"])
             self._gemm(ly["qkv"], self.qkv, B)
             lens = self.lens[il]
-            _lib.call("lt_rope_batch", self.qkv.data_ptr(), qld, lens.data_ptr(), B, p.nh_l + p.nkv_l, hd, theta, st())
-            _lib.call("lt_append_kv_batch", self.kc[il].data_ptr(), self.qkv.data_ptr() + p.nq_l * 4,
-                      self.vc[il].data_ptr(), self.qkv.data_ptr() + (p.nq_l + p.nk_l) * 4, qld, lens.data_ptr(),
-                      p.nk_l, self.max_seq, B, 1, st())
+            _lib.call("lt_rope_append_batch", self.qkv.data_ptr(), qld, p.nh_l, p.nkv_l, hd, theta,
+                      self.kc[il].data_ptr(), self.vc[il].data_ptr(), lens.data_ptr(), self.max_seq, B,
+                      self.ticket.data_ptr(), st())
+            # attention output and its Q8_0 quantisation (the o_proj input) from one launch chain
             _lib.call("lt_attn_decode_batch", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(), self.vc[il].data_ptr(),
                       lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(), hd, p.nh_l, p.nkv_l,
-                      scale, self.max_seq, B, st())
-            _lib.call("lt_quant_q8", self.att.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), p.nq_l, B, st())
+                      scale, self.max_seq, B, self.xq.data_ptr(), self.xd.data_ptr(), st())
             self._row_split(ly["o"], self.x, self.x1)
             self._norm_quant(self.x1, ly["ffn_norm"])
             self._gemm(ly["gateup"], self.gu, B)

@@ -27,9 +27,16 @@ def test_batched_attention_equals_one_sequence_attention(hd, nh, nkv, max_seq, l
     nscr = _lib.lib().lt_attn_decode_batch_scratch_floats(nh, max_seq, B)
     scratch = torch.empty(nscr, dtype=torch.float32, device="cuda")
     out = torch.full((B * nh * hd,), float("nan"), device="cuda")
+    xq = torch.empty(B * nh * hd, dtype=torch.int8, device="cuda")
+    xd = torch.empty(B * nh * hd // 32, dtype=torch.int16, device="cuda")
     _lib.call("lt_attn_decode_batch", dQ.data_ptr(), nh * hd, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(),
-              out.data_ptr(), nh * hd, scratch.data_ptr(), hd, nh, nkv, scale, max_seq, B, stream())
+              out.data_ptr(), nh * hd, scratch.data_ptr(), hd, nh, nkv, scale, max_seq, B, xq.data_ptr(), xd.data_ptr(),
+              stream())
     got = host(out).reshape(B, nh * hd)
+    # the quantised rows equal lt_quant_q8 of the output
+    xq2 = torch.empty_like(xq); xd2 = torch.empty_like(xd)
+    _lib.call("lt_quant_q8", out.data_ptr(), xq2.data_ptr(), xd2.data_ptr(), nh * hd, B, stream())
+    assert np.array_equal(host(xq), host(xq2)) and np.array_equal(host(xd), host(xd2))
     one = torch.empty(nh * hd, device="cuda")
     for b in range(B):
         _lib.call("lt_attn_decode_masked", dQ[b * nh * hd:].data_ptr(), dK[b * max_seq * width:].data_ptr(),
@@ -68,3 +75,17 @@ def test_batched_rope_and_append():
         assert np.array_equal(bits(k[b, L]), bits(got[b, nh * hd:(nh + nkv) * hd]))
         assert np.array_equal(bits(v[b, L]), bits(got[b, (nh + nkv) * hd:]))
         assert np.count_nonzero(k[b].any(axis=1)) == 1
+    # the fused launch: same rows, caches and lengths as the two launches
+    dX2 = dev(X.reshape(-1))
+    kc2 = torch.zeros_like(kc); vc2 = torch.zeros_like(vc)
+    lens2 = torch.tensor([0, 3, 15, 16, 7], dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(B, dtype=torch.int32, device="cuda")
+    _lib.call("lt_rope_append_batch", dX2.data_ptr(), ld, nh, nkv, hd, 5e5, kc2.data_ptr(), vc2.data_ptr(),
+              lens2.data_ptr(), max_seq, B, ticket.data_ptr(), stream())
+    assert ticket.tolist() == [0] * B
+    assert _lib.device_status() == {"kv_overflow"}
+    assert lens2.tolist() == [1, 4, 16, 16, 8]
+    g2 = host(dX2).reshape(B, ld)
+    for b in (0, 1, 2, 4):
+        assert np.array_equal(bits(g2[b]), bits(got[b]))
+    assert np.array_equal(bits(host(kc2)), bits(host(kc))) and np.array_equal(bits(host(vc2)), bits(host(vc)))
