@@ -274,6 +274,20 @@ int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, const float* 
 int lt_rope_append_batch(float* X, int ld, int n_qhead, int n_kvhead, int hd, float theta, float* kbase,
                          float* vbase, int* lens, int max_seq, int B, int* ticket, void* stream);
 
+/* lt_attn_decode_split: decode attention in the reference's second declared order,
+ * reduction_order(attn_decode_split, ...) (bpd/lib/ir_param_axes.pl:307-346; kernel text
+ * bpd/kernelgen/experimental/attn_decode_split.cu, launched with 64 threads by
+ * bpd/kernelgen/referee/gatebench_attn_split.py): nsplit contiguous ranges of ceil(L/nsplit) positions, each
+ * with its own max / exponentials / 64-lane Z / left-fold V sum, combined by exp(local max - global max) in
+ * ascending range order.  nsplit is part of the order (fix it per captured graph); nsplit = 1 gives the bits
+ * of lt_attn_decode_masked.  The reference keeps this order banked, not wired into production; here it is
+ * opt-in for long contexts, where it shortens the dependent V-sum chain to L/nsplit.  Same cache layout and
+ * arguments as lt_attn_decode_batch; scratch holds lt_attn_decode_split_scratch_floats(nh, hd, nsplit, B). */
+long lt_attn_decode_split_scratch_floats(int nh, int hd, int nsplit, int B);
+int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* V, const int* lens, float* OUT,
+                         int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
+                         int nsplit, int8_t* Xq, uint16_t* Xd, void* stream);
+
 /* ---- all-reduce over the GPUs of one node, fused with the residual add ---------------------
  * No counterpart in the reference (it is single-GPU).  For the tensor-parallel decode step:
  * out = resid + (part_0 + part_1 + ... in rank order), the same bits on every rank.  Each rank owns

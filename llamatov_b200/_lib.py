@@ -44,6 +44,7 @@ SIGNATURES = {
     "lt_rope_batch": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv_batch": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
+    "lt_attn_decode_split": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp],
     "lt_rope_append_batch": [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp, _vp],
     "lt_comm_alloc": [_i, _i, _vp, _vp],
     "lt_comm_connect": [_vp, _i, _vp],
@@ -59,7 +60,8 @@ SIGNATURES = {
 _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}
 # name -> (argtypes, restype) for the entries that return something other than a status code
-_QUERIES = {"lt_attn_decode_batch_scratch_floats": ([_i, _i, _i], ctypes.c_long)}
+_QUERIES = {"lt_attn_decode_batch_scratch_floats": ([_i, _i, _i], ctypes.c_long),
+            "lt_attn_decode_split_scratch_floats": ([_i, _i, _i, _i], ctypes.c_long)}
 
 
 def lib():

@@ -220,9 +220,9 @@ __global__ void __launch_bounds__(32 * MAX_REP)
 k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
           const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq,
           int8_t* __restrict__ Xq, __half* __restrict__ Xd) {
-    extern __shared__ __align__(16) float pv_smem[];
-    float (*vt)[PV_TT][32] = (float (*)[PV_TT][32])pv_smem;                                  // [stage][t][d]
-    float (*pt)[MAX_REP][PV_TT] = (float (*)[MAX_REP][PV_TT])(pv_smem + PV_STAGES * PV_TT * 32);   // [stage][head][t]
+    extern __shared__ __align__(16) float pv_buf[];
+    float (*vt)[PV_TT][32] = (float (*)[PV_TT][32])pv_buf;                                  // [stage][t][d]
+    float (*pt)[MAX_REP][PV_TT] = (float (*)[MAX_REP][PV_TT])(pv_buf + PV_STAGES * PV_TT * 32);   // [stage][head][t]
     const int b = blockIdx.z, hk = blockIdx.y;
     const int rep = nh / nkv;
     const int dl = threadIdx.x & 31, r = threadIdx.x >> 5;
@@ -286,6 +286,157 @@ k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, co
         const long col = (long)h * hd + d0 + dl;
         Xq[(long)b * nh * hd + col] = (int8_t)q;
         if (dl == 0) Xd[((long)b * nh * hd + col) >> 5] = dh;
+    }
+}
+
+// ------------------------------------------------------------------ attention, declared split order
+// The reference's second declared order for decode attention, reduction_order(attn_decode_split, ...)
+// (bpd/lib/ir_param_axes.pl:307-346; kernel text bpd/kernelgen/experimental/attn_decode_split.cu, launched
+// with 64 threads by bpd/kernelgen/referee/gatebench_attn_split.py): the positions are cut into S contiguous
+// ranges of ceil(L/S); each range takes its own max, exponentiates against it, sums Z on 64 strided lanes +
+// tree and left-folds its V sum; a second launch rescales the ranges by exp(local max - global max) and
+// adds them in ascending range order.  S is part of the order (fix it per captured graph).  It is a
+// re-canonicalisation of the one-pass order, not a faster way to the same bits; what it buys is that the
+// dependent V-sum chain is L/S long.
+// grid (S, nkv, B); a CTA serves the rep query heads of its KV head.  scratch: partM, partZ [B][nh][S],
+// partO [B][nh][S][hd].
+__global__ void __launch_bounds__(1024)
+k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
+             const int* __restrict__ lens, float* __restrict__ partM, float* __restrict__ partZ,
+             float* __restrict__ partO, int hd, int nh, int nkv, float scale, int max_seq, int per_max, int* status) {
+    extern __shared__ __align__(16) float sp_smem[];
+    const int S = gridDim.x, sp = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int rep = nh / nkv;
+    float* qs = sp_smem;                 // [rep][hd]
+    float* red = qs + rep * hd;          // [rep][64]
+    float* mz = red + rep * 64;          // [rep] local max
+    float* sh = mz + ((rep + 3) & ~3);   // [rep][per_max] scores, then exponentials
+    const int tid = threadIdx.x;
+    int L = lens[b];
+    if (L < 0 || L > max_seq) {
+        if (tid == 0 && sp == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
+        L = L < 0 ? 0 : max_seq;
+    }
+    const int per = (L + S - 1) / S;
+    const int p0 = sp * per;
+    int p1 = p0 + per;
+    if (p1 > L) p1 = L;
+    const int rangeN = p1 > p0 ? p1 - p0 : 0;
+    for (int i = tid; i < rep * hd; i += blockDim.x) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    __syncthreads();
+    // scores of the range, once: s = fold_i fma(q[i], K[t, i], s), then * scale
+    for (int t = p0 + tid; t < p1; t += blockDim.x) {
+        const float4* Kt = (const float4*)(K + (((long)b * max_seq + t) * nkv + hk) * hd);
+        float s[MAX_REP];
+#pragma unroll
+        for (int r = 0; r < MAX_REP; r++) s[r] = 0.0f;
+        for (int i0 = 0; i0 < (hd >> 2); i0 += 8) {
+            float4 kk[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) kk[u] = Kt[i0 + u];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+#pragma unroll
+                for (int r = 0; r < MAX_REP; r++) {
+                    if (r < rep) {
+                        const float4 qq = ((const float4*)(qs + r * hd))[i0 + u];
+                        s[r] = __fmaf_rn(qq.x, kk[u].x, s[r]);
+                        s[r] = __fmaf_rn(qq.y, kk[u].y, s[r]);
+                        s[r] = __fmaf_rn(qq.z, kk[u].z, s[r]);
+                        s[r] = __fmaf_rn(qq.w, kk[u].w, s[r]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_REP; r++)
+            if (r < rep) sh[r * per_max + (t - p0)] = __fmul_rn(s[r], scale);
+    }
+    __syncthreads();
+    // per head on 64 lanes: local max, exponentials against it, Z (lane l sums t = l, l+64, ... of the range;
+    // tree 32, 16, ..., 1)
+    const int groups = blockDim.x >> 6, grp = tid >> 6, l64 = tid & 63;
+    for (int r0 = 0; r0 < rep; r0 += groups) {
+        const int r = r0 + grp;
+        const bool on = r < rep;
+        float* row = sh + (on ? r : 0) * per_max;
+        float m = -1e30f;
+        if (on)
+            for (int t = l64; t < rangeN; t += 64) m = fmaxf(m, row[t]);
+        if (on) red[r * 64 + l64] = m;
+        __syncthreads();
+        if (on && l64 < 32) {
+            float v = fmaxf(red[r * 64 + l64], red[r * 64 + l64 + 32]);
+#pragma unroll
+            for (int s2 = 16; s2 > 0; s2 >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s2));
+            if (l64 == 0) mz[r] = rangeN > 0 ? v : -1e30f;
+        }
+        __syncthreads();
+        float ls = 0.0f;
+        if (on) {
+            const float lmx = mz[r];
+            for (int t = l64; t < rangeN; t += 64) {
+                const float p = __expf(__fsub_rn(row[t], lmx));
+                row[t] = p;
+                ls = __fadd_rn(ls, p);
+            }
+            red[r * 64 + l64] = ls;
+        }
+        __syncthreads();
+        if (on && l64 < 32) {
+            float v = __fadd_rn(red[r * 64 + l64], red[r * 64 + l64 + 32]);
+            v = warp_tree_sum(v);
+            if (l64 == 0) {
+                const long o = ((long)b * nh + hk * rep + r) * S + sp;
+                partM[o] = mz[r];
+                partZ[o] = v;
+            }
+        }
+        __syncthreads();
+    }
+    // partial V sum: left fold over the range, one thread per (head, output element)
+    for (int i = tid; i < rep * hd; i += blockDim.x) {
+        const int r = i / hd, d = i - r * hd;
+        const float* row = sh + r * per_max;
+        const float* Vd = V + (((long)b * max_seq + p0) * nkv + hk) * hd + d;
+        const long vs = (long)nkv * hd;
+        float acc = 0.0f;
+        int t = 0;
+        for (; t + 8 <= rangeN; t += 8) {   // loads batched, fold order unchanged
+            float vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) vv[u] = Vd[(long)(t + u) * vs];
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc = __fmaf_rn(row[t + u], vv[u], acc);
+        }
+        for (; t < rangeN; t++) acc = __fmaf_rn(row[t], Vd[(long)t * vs], acc);
+        partO[(((long)b * nh + hk * rep + r) * S + sp) * hd + d] = acc;
+    }
+}
+
+// grid (nh, B), block hd: global max over the ranges, w = __expf(local max - global max),
+// Z = fold fma(w, partZ, Z), O = fold fma(w, partO, O) in ascending range order, OUT = O / Z
+__global__ void k_attn_split_combine(const float* __restrict__ partM, const float* __restrict__ partZ,
+                                     const float* __restrict__ partO, float* __restrict__ OUT, int out_ld, int hd, int nh,
+                                     int S, int8_t* __restrict__ Xq, __half* __restrict__ Xd) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const long o = ((long)b * nh + h) * S;
+    float M = -1e30f;
+    for (int sp = 0; sp < S; sp++) M = fmaxf(M, partM[o + sp]);
+    float Z = 0.0f, acc = 0.0f;
+    for (int sp = 0; sp < S; sp++) {
+        const float w = __expf(__fsub_rn(partM[o + sp], M));
+        Z = __fmaf_rn(w, partZ[o + sp], Z);
+        acc = __fmaf_rn(w, partO[(o + sp) * hd + d], acc);
+    }
+    const float y = __fdiv_rn(acc, Z);
+    OUT[(long)b * out_ld + (long)h * hd + d] = y;
+    if (Xq != nullptr) {   // hd is a multiple of 32: a warp holds one 32-block of the output row
+        __half dh;
+        const int q = quant_lane(y, &dh);
+        const long col = ((long)b * nh + h) * hd + d;
+        Xq[col] = (int8_t)q;
+        if ((d & 31) == 0) Xd[col >> 5] = dh;
     }
 }
 
@@ -370,4 +521,45 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
         k_attn_pv<4><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(4), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
                                                                         max_seq, Xq, (__half*)Xd);
     return check_launch("lt_attn_decode_batch", 3);
+}
+
+extern "C" long lt_attn_decode_split_scratch_floats(int nh, int hd, int nsplit, int B) {
+    return (long)B * nh * nsplit * (2 + (long)hd);
+}
+
+extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* V, const int* lens,
+                                    float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale,
+                                    int max_seq, int B, int nsplit, int8_t* Xq, uint16_t* Xd, void* stream) {
+    LT_REQUIRE(Q && K && V && lens && OUT && scratch, "lt_attn_decode_split: null pointer");
+    LT_REQUIRE(hd > 0 && hd % 32 == 0 && hd <= 1024, "lt_attn_decode_split: hd=%d must be a multiple of 32, at most 1024", hd);
+    LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= MAX_REP,
+               "lt_attn_decode_split: nh=%d must be a multiple of nkv=%d with at most %d query heads per KV head", nh, nkv, MAX_REP);
+    LT_REQUIRE(nsplit >= 1 && nsplit <= 1024, "lt_attn_decode_split: nsplit=%d (1..1024)", nsplit);
+    LT_REQUIRE(max_seq > 0 && B > 0 && B <= 65535, "lt_attn_decode_split: max_seq=%d B=%d", max_seq, B);
+    LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_decode_split: q_ld=%d out_ld=%d", q_ld, out_ld);
+    LT_REQUIRE((Xq == nullptr) == (Xd == nullptr), "lt_attn_decode_split: Xq and Xd are given together or not at all");
+    LT_REQUIRE(Xq == nullptr || out_ld == nh * hd, "lt_attn_decode_split: the quantised output needs out_ld == nh*hd");
+    LT_REQUIRE(aligned16(Q) && aligned16(K), "lt_attn_decode_split: Q and K must be 16-byte aligned");
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_attn_decode_split: status word unavailable");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int rep = nh / nkv;
+    const int per_max = (((max_seq + nsplit - 1) / nsplit) + 3) & ~3;
+    const size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max) * sizeof(float);
+    LT_REQUIRE(smem <= 200 * 1024, "lt_attn_decode_split: max_seq=%d / nsplit=%d needs %zu bytes of shared memory", max_seq, nsplit, smem);
+    static bool attr_done = false;
+    if (!attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    int threads = ((rep * hd + 31) / 32) * 32;
+    if (threads < 256) threads = 256;
+    if (threads > 1024) threads = 1024;
+    float* partM = scratch;
+    float* partZ = partM + (long)B * nh * nsplit;
+    float* partO = partZ + (long)B * nh * nsplit;
+    k_attn_split<<<dim3(nsplit, nkv, B), threads, smem, s>>>(Q, q_ld, K, V, lens, partM, partZ, partO, hd, nh, nkv, scale,
+                                                            max_seq, per_max, st);
+    k_attn_split_combine<<<dim3(nh, B), hd, 0, s>>>(partM, partZ, partO, OUT, out_ld, hd, nh, nsplit, Xq, (__half*)Xd);
+    return check_launch("lt_attn_decode_split", 2);
 }

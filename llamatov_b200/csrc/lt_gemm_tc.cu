@@ -62,15 +62,6 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 
 // Bounded wait.  *abort_flag (shared) is set by the first wait of the CTA that runs out of time;
 // from then on every wait returns immediately so that all roles run to the end of their loops.
-#ifdef LT_TC_PROF
-__device__ long long g_tc_prof[8];   // waits: 0 producer/empty, 1 mma/full, 2 mma/tempty, 3 epilogue/tfull, 4 kernel clocks
-#define LT_PROF_T0() const long long prof_t0 = clock64()
-#define LT_PROF_ADD(slot) atomicAdd((unsigned long long*)&g_tc_prof[slot], (unsigned long long)(clock64() - prof_t0))
-#else
-#define LT_PROF_T0()
-#define LT_PROF_ADD(slot)
-#endif
-
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                           int* status) {
@@ -247,9 +238,6 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = B->tmem_base;
-#ifdef LT_TC_PROF
-    const long long prof_k0 = clock64();
-#endif
 
     // chunks per tile: groups in bit-reversed order, rounds ascending; identical in all three roles
     if (warp == EW) {
@@ -264,11 +252,7 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     for (int b0 = CB * g; b0 < nb; b0 += 32, it++) {
                         const int s = it % NSTAGE;
                         unsigned char* st = base + s * C::STAGE;
-                        {
-                            LT_PROF_T0();
-                            mbar_wait<64>(&B->empty[s], ((it / NSTAGE) & 1) ^ 1, abort_flag, P.status);
-                            LT_PROF_ADD(0);
-                        }
+                        mbar_wait<64>(&B->empty[s], ((it / NSTAGE) & 1) ^ 1, abort_flag, P.status);
                         mbar_expect_tx(&B->full[s], C::W_STAGE + C::X_STAGE);
                         tma_load_2d(st, &tmW, b0 * 32, row0, &B->full[s]);
                         tma_load_2d(st + C::W_STAGE, &tmX, b0 * 32, t0, &B->full[s]);
@@ -292,16 +276,8 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             const unsigned total = (unsigned)my_tiles * chunks;
             for (unsigned it = (unsigned)(warp - (EW + 1)); it < total; it += MW) {
                 const unsigned s = it % NSTAGE, slot = it % NSLOT;
-                {
-                    LT_PROF_T0();
-                    mbar_wait<32>(&B->full[s], (it / NSTAGE) & 1, abort_flag, P.status);
-                    LT_PROF_ADD(1);
-                }
-                {
-                    LT_PROF_T0();
-                    mbar_wait<32>(&B->tempty[slot], ((it / NSLOT) & 1) ^ 1, abort_flag, P.status);
-                    LT_PROF_ADD(2);
-                }
+                mbar_wait<32>(&B->full[s], (it / NSTAGE) & 1, abort_flag, P.status);
+                mbar_wait<32>(&B->tempty[slot], ((it / NSLOT) & 1) ^ 1, abort_flag, P.status);
                 tc_fence_after();
                 // descriptors differ from the first stage's only in the start address (16-byte units)
                 const unsigned long long wd0 = wdesc0 + (unsigned long long)(s * (C::STAGE >> 4));
@@ -381,13 +357,7 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     // all CB blocks of the chunk in one round trip to tensor memory
                     const unsigned slot = it % NSLOT;
                     const unsigned taddr = tmem + lane_addr + slot * C::SLOT_COLS;
-                    {
-                        LT_PROF_T0();
-                        mbar_wait(&B->tfull[slot], (it / NSLOT) & 1, abort_flag, P.status);
-#ifdef LT_TC_PROF
-                        if (tid == 0) LT_PROF_ADD(3);
-#endif
-                    }
+                    mbar_wait(&B->tfull[slot], (it / NSLOT) & 1, abort_flag, P.status);
                     tc_fence_after();
 #pragma unroll
                     for (int h = 0; h < CB; h += LB) {   // LB blocks per round trip to tensor memory
@@ -470,9 +440,6 @@ k_q8_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     }
 
     // ---------------------------------------------------------------------- teardown
-#ifdef LT_TC_PROF
-    if (tid == 0) atomicAdd((unsigned long long*)&g_tc_prof[4], (unsigned long long)(clock64() - prof_k0));
-#endif
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && warp == EW && lane == 0) {
@@ -588,11 +555,3 @@ extern "C" int lt_q8_gemm_tc(const int8_t* Wq, const uint16_t* Wd, const int8_t*
     return LT_ERR_INVALID;
 }
 
-#ifdef LT_TC_PROF
-extern "C" int lt_tc_prof_read(long long* out8) {
-    cudaMemcpyFromSymbol(out8, lt::tc::g_tc_prof, sizeof(long long) * 8);
-    long long z[8] = {0};
-    cudaMemcpyToSymbol(lt::tc::g_tc_prof, z, sizeof(z));
-    return 0;
-}
-#endif

@@ -259,7 +259,20 @@ static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, 
         attr_done = true;
     }
     LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
-    int ctas = gemv_grid(((long)M + R - 1) / R);
+    // one wave: as many CTAs as are resident at once (by this instantiation's registers and shared memory),
+    // the warps loop over the rows; a multi-wave grid ends in a partly filled wave
+    static int per_sm = 0, sms = 0;
+    if (per_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U>, GEMV_THREADS, smem) != cudaSuccess ||
+            per_sm < 1)
+            per_sm = 1;
+    }
+    const long need = (((long)M + R - 1) / R + GEMV_WARPS - 1) / GEMV_WARPS;
+    const long cap = (long)sms * per_sm;
+    const int ctas = (int)(need < cap ? need : cap);
     k_q8_gemv1<R, U><<<(unsigned)ctas, GEMV_THREADS, smem, s>>>(Wq, (const __half*)Wd, Xq, (const __half*)Xd, Resid, Y,
                                                               M, K);
     return check_launch("lt_q8_gemv");

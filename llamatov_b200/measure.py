@@ -209,7 +209,8 @@ def run_tp_decode(args):
     wbytes = (L * ((nq + 2 * nk) * E + E * nq + 2 * F * E + E * F) + V * E) // 32 * 34
     for B in args.batch:
         max_seq = args.ctx + args.steps + 8
-        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=args.comm)
+        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=args.comm,
+                            attn_split=args.attn_split)
         dec.fill_cache(args.ctx, seed=1)
         start = np.random.default_rng(0).integers(0, V, size=B)
         dec.set_tokens(start)
@@ -264,7 +265,7 @@ def run_tp_decode(args):
             launches = dec.launches_per_step
             del dec
             torch.cuda.empty_cache()
-            ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0)
+            ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0, attn_split=args.attn_split)
             ref.fill_cache(args.ctx, seed=1)
             ref.set_tokens(start)
             warm_h = torch.stack(warm).cpu().numpy()
@@ -293,7 +294,8 @@ def run_tp_decode(args):
                 "metric": "decode tok/s (Q8_0, tensor-parallel)", "value": B * args.steps / (ms * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "ms_per_step": step_ms, "steps": args.steps, "warmup": args.warmup,
                 "config": {"workload": f"{args.arch} Q8_0 decode, batch {B}, context {args.ctx}, TP={world}",
-                           "layers": L, "launches_per_step": launches, "comm": args.comm if world > 1 else None},
+                           "layers": L, "launches_per_step": launches, "comm": args.comm if world > 1 else None,
+                           "attention_order": f"attn_decode_split, S={args.attn_split}" if args.attn_split else "one-pass (production)"},
                 "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
                              "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
                              "frac": step_bytes / (step_ms * 1e-3) / 1e9 / (hbm * world), "peak_source": src},
@@ -336,6 +338,8 @@ def main(argv=None):
     t.add_argument("--warmup", type=int, default=3)
     t.add_argument("--layers", type=int, default=0, help="fewer layers than the architecture (smoke runs)")
     t.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
+    t.add_argument("--attn-split", type=int, default=0,
+                   help="S > 0: decode attention in the reference's declared split order with S ranges; 0: one-pass order")
     t.add_argument("--check-world1", action="store_true", help="rank 0 re-runs at world 1 and compares the tokens")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

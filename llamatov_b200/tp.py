@@ -152,7 +152,7 @@ class TPDecoder:
     """
 
     def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
-                 comm="nccl"):
+                 comm="nccl", attn_split=0):
         self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
         self.max_seq = int(max_seq); self.group = group
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -201,7 +201,12 @@ class TPDecoder:
         self.xq = torch.empty(B * kmax, dtype=torch.int8, device=self.dev)
         self.xd = torch.empty(B * (kmax // 32), dtype=torch.int16, device=self.dev)
         self.logits = torch.empty((B, max(1, v1 - v0)), **f32)
+        # attn_split = S > 0: the reference's declared split order with S ranges (fixed for the captured graph);
+        # 0: the one-pass frozen order
+        self.attn_split = int(attn_split)
         n = _lib.lib().lt_attn_decode_batch_scratch_floats(p.nh_l, self.max_seq, B)
+        if self.attn_split > 0:
+            n = max(n, _lib.lib().lt_attn_decode_split_scratch_floats(p.nh_l, p.hd, self.attn_split, B))
         self.scratch = torch.empty(n, **f32)
         self.amax_part = torch.empty(_lib.lib().lt_argmax_scratch_bytes() // 4 * B, **f32)
         self.loc_idx = torch.zeros(B, dtype=torch.int32, device=self.dev)
@@ -335,9 +340,15 @@ class TPDecoder:
                       self.kc[il].data_ptr(), self.vc[il].data_ptr(), lens.data_ptr(), self.max_seq, B,
                       self.ticket.data_ptr(), st())
             # attention output and its Q8_0 quantisation (the o_proj input) from one launch chain
-            _lib.call("lt_attn_decode_batch", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(), self.vc[il].data_ptr(),
-                      lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(), hd, p.nh_l, p.nkv_l,
-                      scale, self.max_seq, B, self.xq.data_ptr(), self.xd.data_ptr(), st())
+            if self.attn_split > 0:
+                _lib.call("lt_attn_decode_split", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(),
+                          self.vc[il].data_ptr(), lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(),
+                          hd, p.nh_l, p.nkv_l, scale, self.max_seq, B, self.attn_split, self.xq.data_ptr(),
+                          self.xd.data_ptr(), st())
+            else:
+                _lib.call("lt_attn_decode_batch", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(),
+                          self.vc[il].data_ptr(), lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(),
+                          hd, p.nh_l, p.nkv_l, scale, self.max_seq, B, self.xq.data_ptr(), self.xd.data_ptr(), st())
             self._row_split(ly["o"], self.x, self.x1)
             self._norm_quant(self.x1, ly["ffn_norm"])
             self._gemm(ly["gateup"], self.gu, B)

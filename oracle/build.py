@@ -116,6 +116,12 @@ def reference_kernel_sources(ref_root):
     }
     for maxt in (256, 512):
         src["attn_decode_masked_%d" % maxt] = consts["_ATTN_DECODE_MASKED_SRC_TMPL"] % {"MAXT": maxt}
+    # the banked split-order attention: a %-template in the reference's experimental directory
+    split = os.path.join(ref_root, "bpd", "kernelgen", "experimental", "attn_decode_split.cu")
+    if os.path.exists(split):
+        text = open(split).read()
+        for ns in (2, 4):
+            src["attn_decode_split_%d" % ns] = text % {"MAXT": 256, "NSPLIT": ns}
     hdr = "#include <cuda_fp16.h>\n"
     q8 = os.path.join(emit, "q8_0_from_facts.pl")
     b = {"BM": 16, "BK": 256, "BlockSz": 512}

@@ -19,6 +19,9 @@
  *   lto_rope               bpd/kernelgen/emitters/rope_from_facts.pl:48-65
  *   lto_append_kv_incr     bpd/lib/dev_residency.py:303-315
  *   lto_attn_decode_masked bpd/lib/dev_residency.py:1956-2009
+ *   lto_attn_decode_split  bpd/kernelgen/experimental/attn_decode_split.cu (declared order
+ *                          bpd/lib/ir_param_axes.pl:307-346; 64-thread launch of
+ *                          bpd/kernelgen/referee/gatebench_attn_split.py)
  *   lto_argmax             bpd/lib/dev_residency.py:226-271
  *   lto_embed_q8           bpd/lib/dev_residency.py:1357-1358 (row of the dequantised table)
  *   lto_decode_token       bpd/lib/dev_residency.py:1381-1477,1596-1623 (op sequence)
@@ -333,6 +336,67 @@ void lto_attn_decode_masked(const float* Q, const float* K, const float* V, int 
     }
     free(sh);
 }
+
+/* The second declared order: S contiguous ranges of ceil(L/S) positions; per range local max,
+ * expf against it, Z on 64 strided lanes + tree (32..1), left-fold V sum; combine in ascending
+ * range order with w = expf(local max - global max), Z = fma(w, partZ, Z), O = fma(w, partO, O). */
+void lto_attn_decode_split(const float* Q, const float* K, const float* V, int L, float* OUT,
+                           int hd, int nh, int nkv, float scale, int S) {
+    int rep = nh / nkv;
+    int per = (L + S - 1) / S;
+    float* sh = (float*)malloc(sizeof(float) * (size_t)(per > 0 ? per : 1));
+    float* pM = (float*)malloc(sizeof(float) * (size_t)S);
+    float* pZ = (float*)malloc(sizeof(float) * (size_t)S);
+    float* pO = (float*)malloc(sizeof(float) * (size_t)S * hd);
+    for (int h = 0; h < nh; h++) {
+        int hk = h / rep;
+        const float* qh = Q + (long)h * hd;
+        for (int sp = 0; sp < S; sp++) {
+            int p0 = sp * per, p1 = p0 + per;
+            if (p1 > L) p1 = L;
+            int n = p1 > p0 ? p1 - p0 : 0;
+            float m = -1e30f;
+            for (int t = p0; t < p1; t++) {
+                const float* Kt = K + ((long)t * nkv + hk) * hd;
+                float s = 0.0f;
+                for (int i = 0; i < hd; i++) s = fmaf(qh[i], Kt[i], s);
+                s = s * scale;
+                sh[t - p0] = s;
+                m = fmaxf(m, s);
+            }
+            float lmx = n > 0 ? m : -1e30f;
+            pM[sp] = lmx;
+            for (int t = 0; t < n; t++) sh[t] = expf(sh[t] - lmx);
+            float red[64];
+            for (int r = 0; r < 64; r++) {
+                float ls = 0.0f;
+                for (int t = r; t < n; t += 64) ls += sh[t];
+                red[r] = ls;
+            }
+            for (int s2 = 32; s2 > 0; s2 >>= 1)
+                for (int r = 0; r < s2; r++) red[r] += red[r + s2];
+            pZ[sp] = red[0];
+            for (int d = 0; d < hd; d++) {
+                float acc = 0.0f;
+                for (int t = p0; t < p1; t++) acc = fmaf(sh[t - p0], V[((long)t * nkv + hk) * hd + d], acc);
+                pO[(long)sp * hd + d] = acc;
+            }
+        }
+        float M = -1e30f;
+        for (int sp = 0; sp < S; sp++) M = fmaxf(M, pM[sp]);
+        for (int d = 0; d < hd; d++) {
+            float Z = 0.0f, acc = 0.0f;
+            for (int sp = 0; sp < S; sp++) {
+                float w = expf(pM[sp] - M);
+                Z = fmaf(w, pZ[sp], Z);
+                acc = fmaf(w, pO[(long)sp * hd + d], acc);
+            }
+            OUT[(long)h * hd + d] = acc / Z;
+        }
+    }
+    free(sh); free(pM); free(pZ); free(pO);
+}
+
 
 /* ---------------------------------------------------------------- argmax */
 

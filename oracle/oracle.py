@@ -161,6 +161,16 @@ def attn_decode_masked(q, kc, vc, L, hd, nh, nkv, scale, maxt):
     return out
 
 
+def attn_decode_split(q, kc, vc, L, hd, nh, nkv, scale, nsplit):
+    """Decode attention in the declared split order (one sequence)."""
+    q = _f32(q).reshape(-1); kc = _f32(kc).reshape(-1); vc = _f32(vc).reshape(-1)
+    out = np.empty(nh * hd, np.float32)
+    lib().lto_attn_decode_split(_p(q, c_f32p), _p(kc, c_f32p), _p(vc, c_f32p), ctypes.c_int(L),
+                                _p(out, c_f32p), ctypes.c_int(hd), ctypes.c_int(nh), ctypes.c_int(nkv),
+                                ctypes.c_float(scale), ctypes.c_int(nsplit))
+    return out
+
+
 def argmax(x):
     x = _f32(x).reshape(-1)
     return int(lib().lto_argmax(_p(x, c_f32p), ctypes.c_int(x.size)))

@@ -119,6 +119,16 @@ def attn_decode_masked(Q, K, V, length, OUT, hd, nh, nkv, scale, maxt):
             [Q, K, V, length, OUT, hd, nh, nkv, float(scale)])
 
 
+def attn_decode_split(Q, K, V, length, partM, partZ, partO, OUT, hd, nh, nkv, scale, nsplit, maxt=256):
+    """k_attn_decode_split + k_attn_decode_combine with the referee's launch geometry: 64 threads per
+    (head, range) block (bpd/kernelgen/referee/gatebench_attn_split.py)."""
+    assert hd <= 64, "the reference launches this kernel with 64 threads: hd <= 64"
+    name = f"attn_decode_split_{nsplit}"
+    _launch(_func(name, "k_attn_decode_split"), nh * nsplit, 64, maxt * 4 + 1024 * 4,
+            [Q, K, V, length, partM, partZ, partO, hd, nh, nkv, float(scale)])
+    _launch(_func(name, "k_attn_decode_combine"), nh, hd, 0, [partM, partZ, partO, OUT, hd, nh])
+
+
 def argmax2(x, n, pval, pidx, out):
     """k_argmax_s1 + k_argmax_s2, 256 stage-1 blocks (launch: bpd/lib/dev_residency.py:1096-1103)."""
     _launch(_func("argmax2", "k_argmax_s1"), 256, 256, 0, [x, n, 256, pval, pidx])

@@ -1,5 +1,7 @@
 """GPU: the batched / long-context decode operators against the one-sequence operators they
 must reproduce bit for bit."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -89,3 +91,70 @@ def test_batched_rope_and_append():
     for b in (0, 1, 2, 4):
         assert np.array_equal(bits(g2[b]), bits(got[b]))
     assert np.array_equal(bits(host(kc2)), bits(host(kc))) and np.array_equal(bits(host(vc2)), bits(host(vc)))
+
+
+def _split_case(hd, nh, nkv, max_seq, lens, seed):
+    rng = np.random.default_rng(seed)
+    B = len(lens)
+    width = nkv * hd
+    K = (rng.standard_normal((B, max_seq, width)) * 0.3).astype(np.float32)
+    V = (rng.standard_normal((B, max_seq, width)) * 0.3).astype(np.float32)
+    for b, L in enumerate(lens):
+        K[b, L:] = np.nan; V[b, L:] = np.nan
+    Q = (rng.standard_normal((B, nh * hd)) * 0.3).astype(np.float32)
+    return Q, K, V
+
+
+def _gpu_split(Q, K, V, lens, hd, nh, nkv, max_seq, ns, quant=False):
+    B = len(lens)
+    dK, dV, dQ = dev(K.reshape(-1)), dev(V.reshape(-1)), dev(Q.reshape(-1))
+    dl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(_lib.lib().lt_attn_decode_split_scratch_floats(nh, hd, ns, B), device="cuda")
+    out = torch.full((B * nh * hd,), float("nan"), device="cuda")
+    xq = torch.empty(B * nh * hd, dtype=torch.int8, device="cuda") if quant else None
+    xd = torch.empty(B * nh * hd // 32, dtype=torch.int16, device="cuda") if quant else None
+    _lib.call("lt_attn_decode_split", dQ.data_ptr(), nh * hd, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(), out.data_ptr(),
+              nh * hd, scratch.data_ptr(), hd, nh, nkv, float(np.float32(hd ** -0.5)), max_seq, B, ns,
+              None if xq is None else xq.data_ptr(), None if xd is None else xd.data_ptr(), stream())
+    return out, xq, xd, (dQ, dK, dV, dl)
+
+
+@pytest.mark.parametrize("ns", [2, 4])
+@pytest.mark.parametrize("L", [1, 3, 40, 64, 120, 255, 256])
+def test_split_order_attention_equals_the_reference_kernel(ns, L):
+    # the reference's own split kernel (compiled for this GPU) with the referee's 64-thread launch
+    from oracle import ref_device as ref
+    if not ref.available() or not os.path.exists(os.path.join(ref.REF_DIR, f"attn_decode_split_{ns}.cubin")):
+        pytest.skip("reference kernels not built")
+    hd, nh, nkv, max_seq = 64, 14, 2, 256
+    Q, K, V = _split_case(hd, nh, nkv, max_seq, [L], seed=L)
+    out, _, _, (dQ, dK, dV, dl) = _gpu_split(Q, K, V, [L], hd, nh, nkv, max_seq, ns)
+    pm = torch.empty(nh * ns, device="cuda"); pz = torch.empty(nh * ns, device="cuda")
+    po = torch.empty(nh * ns * hd, device="cuda"); want = torch.empty(nh * hd, device="cuda")
+    ref.attn_decode_split(dQ, dK, dV, dl, pm, pz, po, want, hd, nh, nkv, float(np.float32(hd ** -0.5)), ns, max_seq)
+    assert np.array_equal(bits(host(out)), bits(host(want)))
+    assert _lib.device_status() == set()
+
+
+@pytest.mark.parametrize("hd,nh,nkv,max_seq,lens,ns", [(128, 32, 8, 4352, [4100, 1000, 7], 16), (64, 14, 2, 300, [300, 33], 3),
+                                                      (128, 4, 1, 4352, [4097], 32)])
+def test_split_order_attention_vs_oracle_and_one_range_equals_frozen_order(oracle, hd, nh, nkv, max_seq, lens, ns):
+    Q, K, V = _split_case(hd, nh, nkv, max_seq, lens, seed=ns)
+    B = len(lens)
+    out, xq, xd, (dQ, dK, dV, dl) = _gpu_split(Q, K, V, lens, hd, nh, nkv, max_seq, ns, quant=True)
+    got = host(out).reshape(B, nh * hd)
+    scale = float(np.float32(hd ** -0.5))
+    for b, L in enumerate(lens):
+        want = oracle.attn_decode_split(Q[b], np.nan_to_num(K[b]), np.nan_to_num(V[b]), L, hd, nh, nkv, scale, ns)
+        assert np.max(np.abs(got[b] - want)) < 5e-6          # __expf vs libm
+    xq2 = torch.empty_like(xq); xd2 = torch.empty_like(xd)
+    _lib.call("lt_quant_q8", out.data_ptr(), xq2.data_ptr(), xd2.data_ptr(), nh * hd, B, stream())
+    assert np.array_equal(host(xq), host(xq2)) and np.array_equal(host(xd), host(xd2))
+    # one range: the bits of the frozen one-pass order
+    one, _, _, _ = _gpu_split(Q, K, V, lens, hd, nh, nkv, max_seq, 1)
+    frozen = torch.empty(B * nh * hd, device="cuda")
+    scr = torch.empty(_lib.lib().lt_attn_decode_batch_scratch_floats(nh, max_seq, B), device="cuda")
+    _lib.call("lt_attn_decode_batch", dQ.data_ptr(), nh * hd, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(),
+              frozen.data_ptr(), nh * hd, scr.data_ptr(), hd, nh, nkv, scale, max_seq, B, None, None, stream())
+    assert np.array_equal(bits(host(one)), bits(host(frozen)))
+    assert _lib.device_status() == set()
