@@ -249,6 +249,15 @@ def run_config0(args):
             fn(blocks.ctypes.data, xa.ctypes.data, ya.ctypes.data, M, 1, K); n += 1
         dt = (time.perf_counter() - t0) / n
         out["parity"]["max_rel_vs_reference_cpu_path"] = float(np.max(np.abs(yg - ya)) / den)
+        # the same GEMV in the CPU library's own quantiser and fold order (parity mode): bit-exact target
+        xq2 = torch.empty(K, dtype=torch.int8, device="cuda"); xd2 = torch.empty(nb, dtype=torch.int16, device="cuda")
+        y2 = torch.empty(M, dtype=torch.float32, device="cuda")
+        _lib.call("lt_quant_q8_ggml", dx.data_ptr(), xq2.data_ptr(), xd2.data_ptr(), K, 1, st)
+        _lib.call("lt_q8_gemm_ggml", dWq.data_ptr(), dWd.data_ptr(), xq2.data_ptr(), xd2.data_ptr(), y2.data_ptr(), M, K, 1, st)
+        torch.cuda.synchronize()
+        y2h = y2.cpu().numpy()
+        out["parity"]["ggml_order_mode_max_ulp_vs_reference_cpu_path"] = int(np.max(np.abs(
+            y2h.view(np.int32).astype(np.int64) - ya.view(np.int32).astype(np.int64))))
         out["cpu_baseline"] = {"value": gemv_bytes(M, K) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "reference",
                                "sample": f"{n} calls of bpd_qmatmul_q8_0_llamafile_cpu (bpd-substrate/bench/bpd_cpu.c:4419, "
                                          "single-threaded) on the same matrix", "us_per_call": dt * 1e6}

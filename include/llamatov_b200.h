@@ -288,6 +288,17 @@ int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* 
                          int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
                          int nsplit, int8_t* Xq, uint16_t* Xd, void* stream);
 
+/* ---- parity mode: the fold order of the reference's compiled CPU path ---------------------------
+ * lt_quant_q8_ggml / lt_q8_gemm_ggml reproduce bpd_quant_q8_0_cpu and bpd_qmatmul_q8_0_llamafile_cpu
+ * (bpd-substrate/bench/bpd_cpu.c:4096-4126,4419-4447; bpd_gemm_q8_0_cpu.c:53-132,205-260) bit for bit:
+ * q = rint(x * 127/amax); 8 float lanes per result, multiply then add (two roundings), hsum_float_8; one
+ * token (or an odd last token) folds block pairs into lane halves, tokens in tiles fold every block into
+ * all 8 lanes.  Y[t*M + n].  Not used by the decode engine (which keeps the resident engine's declared
+ * order, lt_q8_gemv); for comparing a GPU result with that CPU library. */
+int lt_quant_q8_ggml(const float* X, int8_t* Xq, uint16_t* Xd, int K, int rows, void* stream);
+int lt_q8_gemm_ggml(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, float* Y,
+                    int M, int K, int T, void* stream);
+
 /* ---- all-reduce over the GPUs of one node, fused with the residual add ---------------------
  * No counterpart in the reference (it is single-GPU).  For the tensor-parallel decode step:
  * out = resid + (part_0 + part_1 + ... in rank order), the same bits on every rank.  Each rank owns

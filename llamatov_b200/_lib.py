@@ -26,6 +26,8 @@ SIGNATURES = {
     "lt_add": [_vp, _vp, _vp, _i, _vp],
     "lt_q8_gemv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_q8_gemm_tc": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "lt_quant_q8_ggml": [_vp, _vp, _vp, _i, _i, _vp],
+    "lt_q8_gemm_ggml": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_rmsnorm": [_vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_rope": [_vp, _vp, _i, _i, _i, _f, _vp],

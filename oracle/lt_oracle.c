@@ -15,6 +15,11 @@
  *                          (declared order + canonical-serial rendering), epilogue :412
  *   lto_q8_gemv_leftfold   bpd/kernelgen/emitters/q8_0_from_facts.pl:525-540 (thread-per-row
  *                          dp4a/scalar modes used by the host-roundtrip path)
+ *   lto_quant_q8_ggml      bpd-substrate/bench/bpd_cpu.c:4096-4126 (the compiled CPU path's quantiser:
+ *                          q = rint(x * (127/amax)))
+ *   lto_q8_gemm_ggml       bpd-substrate/bench/bpd_gemm_q8_0_cpu.c:53-78 (one token: 8 lanes, block pairs,
+ *                          mul then add, hsum_float_8), :80-132 (tiles of 2 or 4 tokens: 8 lanes per block
+ *                          halves) and the token grouping of the dispatcher :205-260
  *   lto_rmsnorm            bpd/kernelgen/emitters/norm_softmax_from_facts.pl:49,117-144
  *   lto_rope               bpd/kernelgen/emitters/rope_from_facts.pl:48-65
  *   lto_append_kv_incr     bpd/lib/dev_residency.py:303-315
@@ -288,6 +293,77 @@ void lto_append_kv_incr(float* kbase, const float* ksrc, float* vbase, const flo
     memcpy(kbase + (long)L * width, ksrc, sizeof(float) * (size_t)width);
     memcpy(vbase + (long)L * width, vsrc, sizeof(float) * (size_t)width);
     *len = L + 1;
+}
+
+/* ---------------------------------------------------------------- the compiled CPU path's order ("ggml order") */
+
+/* Activation quantiser of the reference's C library: d = fp16(amax/127), id = 127/amax (0 when amax == 0),
+ * q = rint(x * id).  Differs from lto_quant_q8 (q = rint(x / f32(d))) in the last bit of some quants. */
+void lto_quant_q8_ggml(const float* x, int8_t* q, uint16_t* d, int K) {
+    int nb = K / 32;
+    for (int b = 0; b < nb; b++) {
+        const float* xb = x + (long)b * 32;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            float av = xb[j] < 0 ? -xb[j] : xb[j];
+            if (av > amax) amax = av;
+        }
+        d[b] = lto_f2h(amax / 127.f);
+        float id = (amax != 0.0f) ? 127.f / amax : 0.0f;
+        for (int j = 0; j < 32; j++) q[(long)b * 32 + j] = (int8_t)rintf(xb[j] * id);
+    }
+}
+
+static int isum4(const int8_t* w, const int8_t* a) {
+    return (int)w[0] * a[0] + (int)w[1] * a[1] + (int)w[2] * a[2] + (int)w[3] * a[3];
+}
+static float hsum8(const float* l) {   /* ((l4+l0)+(l6+l2)) + ((l5+l1)+(l7+l3)) */
+    float r0 = l[4] + l[0], r1 = l[5] + l[1], r2 = l[6] + l[2], r3 = l[7] + l[3];
+    float s0 = r0 + r2, s1 = r1 + r3;
+    return s0 + s1;
+}
+
+/* Y[t*M + n].  One token (or the odd last one): lanes 0-3 take the even blocks, lanes 4-7 the odd ones, lane k
+ * the bytes 4k..4k+3 of both 16-byte halves; acc = d*float(isum) + acc (two roundings).  Tokens in tiles of
+ * 4 or 2: every block feeds all 8 lanes (lanes 0-3 the first half, 4-7 the second half). */
+void lto_q8_gemm_ggml(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, float* Y,
+                      int M, int K, int T) {
+    int nb = K / 32;
+    for (int t = 0; t < T; t++) {
+        int vec = (T & 1) && t == T - 1;      /* the dispatcher's last group of one token */
+        const int8_t* xq = Xq + (long)t * K;
+        const uint16_t* xd = Xd + (long)t * nb;
+#pragma omp parallel for schedule(static)
+        for (int n = 0; n < M; n++) {
+            const int8_t* wq = Wq + (long)n * K;
+            const uint16_t* wd = Wd + (long)n * nb;
+            float l[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (vec) {
+                for (int b = 0; b + 1 < nb; b += 2) {
+                    for (int h = 0; h < 2; h++) {
+                        int bb = b + h;
+                        float dl = lto_h2f(wd[bb]) * lto_h2f(xd[bb]);
+                        for (int k = 0; k < 4; k++) {
+                            int is = isum4(wq + bb * 32 + 4 * k, xq + bb * 32 + 4 * k) +
+                                     isum4(wq + bb * 32 + 16 + 4 * k, xq + bb * 32 + 16 + 4 * k);
+                            float pr = dl * (float)is;
+                            l[4 * h + k] = pr + l[4 * h + k];
+                        }
+                    }
+                }
+            } else {
+                for (int b = 0; b < nb; b++) {
+                    float sc = lto_h2f(wd[b]) * lto_h2f(xd[b]);
+                    for (int k = 0; k < 8; k++) {
+                        int is = isum4(wq + b * 32 + 4 * k, xq + b * 32 + 4 * k);
+                        float pr = sc * (float)is;
+                        l[k] = pr + l[k];
+                    }
+                }
+            }
+            Y[(long)t * M + n] = hsum8(l);
+        }
+    }
 }
 
 /* ---------------------------------------------------------------- attention */

@@ -161,6 +161,27 @@ def attn_decode_masked(q, kc, vc, L, hd, nh, nkv, scale, maxt):
     return out
 
 
+def quant_q8_ggml(x):
+    """The reference C library's activation quantiser (q = rint(x * 127/amax))."""
+    x = _f32(x).reshape(-1)
+    K = x.size
+    q = np.empty(K, np.int8); d = np.empty(K // 32, np.uint16)
+    lib().lto_quant_q8_ggml(_p(x, c_f32p), _p(q, c_i8p), _p(d, c_u16p), ctypes.c_int(K))
+    return q, d.view(np.float16)
+
+
+def q8_gemm_ggml(Wq, Wd, Xq, Xd, M, K, T=1):
+    """Y [T, M] in the fold order of the reference's compiled CPU path."""
+    Wq, Wd = _w(Wq, Wd)
+    Xq = np.ascontiguousarray(Xq, np.int8).reshape(-1)
+    Xd = np.ascontiguousarray(Xd).reshape(-1)
+    Xd = Xd.view(np.uint16) if Xd.dtype != np.uint16 else Xd
+    y = np.empty(T * M, np.float32)
+    lib().lto_q8_gemm_ggml(_p(Wq, c_i8p), _p(Wd, c_u16p), _p(Xq, c_i8p), _p(Xd, c_u16p), _p(y, c_f32p),
+                           ctypes.c_int(M), ctypes.c_int(K), ctypes.c_int(T))
+    return y.reshape(T, M)
+
+
 def attn_decode_split(q, kc, vc, L, hd, nh, nkv, scale, nsplit):
     """Decode attention in the declared split order (one sequence)."""
     q = _f32(q).reshape(-1); kc = _f32(kc).reshape(-1); vc = _f32(vc).reshape(-1)

@@ -133,6 +133,26 @@ def test_tensor_core_gemm_bit_exact(oracle, M, K, T, variant):
     assert _lib.device_status() == set()
 
 
+@pytest.mark.parametrize("M,K,T", [(4864, 896, 1), (96, 896, 5), (64, 4864, 4), (33, 1024, 2), (50, 896, 7)])
+def test_ggml_order_mode_bit_exact(oracle, M, K, T):
+    # the fold order of the reference's compiled CPU path (the oracle restatement is pinned to that
+    # library bit for bit on the CPU, tests/test_oracle_golden.py)
+    Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=T)
+    dx = dev(x.reshape(-1))
+    xq = torch.empty(T * K, dtype=torch.int8, device="cuda"); xd = torch.empty(T * K // 32, dtype=torch.int16, device="cuda")
+    _lib.call("lt_quant_q8_ggml", dx.data_ptr(), xq.data_ptr(), xd.data_ptr(), K, T, stream())
+    oq = np.stack([oracle.quant_q8_ggml(x[t])[0] for t in range(T)])
+    od = np.stack([oracle.quant_q8_ggml(x[t])[1] for t in range(T)])
+    assert np.array_equal(host(xq).reshape(T, K), oq)
+    assert np.array_equal(host(xd, np.uint16).reshape(T, -1), od.view(np.uint16))
+    y = torch.empty(T * M, dtype=torch.float32, device="cuda")
+    dWq, dWd = dev(Wq), dev(Wd)
+    _lib.call("lt_q8_gemm_ggml", dWq.data_ptr(), dWd.data_ptr(), xq.data_ptr(), xd.data_ptr(), y.data_ptr(),
+              M, K, T, stream())
+    want = oracle.q8_gemm_ggml(Wq, Wd, oq, od, M, K, T)
+    assert np.array_equal(bits(host(y).reshape(T, M)), bits(want))
+
+
 def test_gemv_linearity_full_size():
     # size-independent property at the LM-head size: W(x1 quantised) + W(x2 quantised) rows are
     # independent of which other rows are computed (row-slice consistency), and the result does

@@ -256,3 +256,33 @@ def test_oracle_engine_runs_and_is_deterministic(oracle):
     # position 0: rope is the identity, so the cached K/V rows are the raw projections
     assert np.array_equal(e3.kc[0][0], qkv[nq:nq + nk])
     assert np.array_equal(e3.vc[0][0], qkv[nq + nk:])
+
+
+def test_ggml_order_restatement_equals_the_reference_cpu_library(oracle):
+    """oracle/_ref/libbpd_cpu.so is the reference's own C code compiled here: its quantiser and its Q8_0
+    matmul (one token, tiles, odd last token) against the restatement, bit for bit."""
+    import ctypes
+    from llamatov_b200 import synth
+    so = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libbpd_cpu.so")
+    if not os.path.exists(so):
+        pytest.skip("reference CPU library not built (no reference checkout)")
+    L = ctypes.CDLL(so)
+    mm = L.bpd_qmatmul_q8_0_llamafile_cpu; mm.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3; mm.restype = None
+    qf = L.bpd_quant_q8_0_cpu; qf.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]; qf.restype = None
+    for (M, K, T) in [(4864, 896, 1), (96, 896, 5), (64, 4864, 4), (33, 1024, 2), (50, 896, 7)]:
+        Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=T)
+        nb = K // 32
+        blocks = np.empty((M * nb, 34), np.uint8)
+        blocks[:, :2] = Wd.view(np.uint8).reshape(M * nb, 2); blocks[:, 2:] = Wq.view(np.uint8).reshape(M * nb, 32)
+        xa = np.ascontiguousarray(x, np.float32); ya = np.zeros(T * M, np.float32)
+        mm(blocks.ctypes.data, xa.ctypes.data, ya.ctypes.data, M, T, K)
+        qs, ds = [], []
+        for t in range(T):
+            q, d = oracle.quant_q8_ggml(x[t]); qs.append(q); ds.append(d)
+            raw = np.zeros(nb * 34, np.uint8)
+            qf(np.ascontiguousarray(x[t]).ctypes.data, raw.ctypes.data, K)
+            raw = raw.reshape(nb, 34)
+            assert np.array_equal(raw[:, 2:].copy().view(np.int8).reshape(-1), q)
+            assert np.array_equal(raw[:, :2].copy().view(np.uint16).reshape(-1), d.view(np.uint16))
+        y = oracle.q8_gemm_ggml(Wq, Wd, np.stack(qs), np.stack(ds), M, K, T)
+        assert np.array_equal(y.reshape(-1).view(np.uint32), ya.view(np.uint32)), (M, K, T)
