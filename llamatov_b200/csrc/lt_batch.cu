@@ -300,6 +300,8 @@ k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, co
 // dependent V-sum chain is L/S long.
 // grid (S, nkv, B); a CTA serves the rep query heads of its KV head.  scratch: partM, partZ [B][nh][S],
 // partO [B][nh][S][hd].
+constexpr int SPLIT_PT = 64;   // positions per staged V tile
+
 __global__ void __launch_bounds__(1024)
 k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
              const int* __restrict__ lens, float* __restrict__ partM, float* __restrict__ partZ,
@@ -394,24 +396,51 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
         }
         __syncthreads();
     }
-    // partial V sum: left fold over the range, one thread per (head, output element)
-    for (int i = tid; i < rep * hd; i += blockDim.x) {
-        const int r = i / hd, d = i - r * hd;
-        const float* row = sh + r * per_max;
-        const float* Vd = V + (((long)b * max_seq + p0) * nkv + hk) * hd + d;
-        const long vs = (long)nkv * hd;
-        float acc = 0.0f;
-        int t = 0;
-        for (; t + 8 <= rangeN; t += 8) {   // loads batched, fold order unchanged
-            float vv[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) vv[u] = Vd[(long)(t + u) * vs];
-#pragma unroll
-            for (int u = 0; u < 8; u++) acc = __fmaf_rn(row[t + u], vv[u], acc);
+    // partial V sum: left fold over the range, one thread per (head, output element).  The V rows of the
+    // range are staged in tiles of SPLIT_PT positions by asynchronous copies (all threads, coalesced), one
+    // tile ahead of the fold, so that the chain never waits on global memory.
+    float* vt = sh + (size_t)rep * per_max;   // [2][SPLIT_PT][hd]
+    const float* Vb = V + (((long)b * max_seq + p0) * nkv + hk) * hd;
+    const long vs = (long)nkv * hd;
+    const int cpr = hd >> 2;                  // 16-byte chunks per row
+    const int ntile = (rangeN + SPLIT_PT - 1) / SPLIT_PT;
+    auto stage = [&](int k) {
+        if (k < ntile) {
+            float* dst = vt + (size_t)(k & 1) * SPLIT_PT * hd;
+            const int t0 = k * SPLIT_PT;
+            for (int i = tid; i < SPLIT_PT * cpr; i += blockDim.x) {
+                const int row = i / cpr, c = i - row * cpr;
+                if (t0 + row < rangeN) cp_async16(dst + row * hd + c * 4, Vb + (long)(t0 + row) * vs + c * 4);
+            }
         }
-        for (; t < rangeN; t++) acc = __fmaf_rn(row[t], Vd[(long)t * vs], acc);
-        partO[(((long)b * nh + hk * rep + r) * S + sp) * hd + d] = acc;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const bool fold = tid < rep * hd;
+    const int fr = fold ? tid / hd : 0, fd = fold ? tid - fr * hd : 0;
+    const float* prow = sh + fr * per_max;
+    float acc = 0.0f;
+    stage(0);
+    for (int k = 0; k < ntile; k++) {
+        stage(k + 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        if (fold) {
+            const float* vc = vt + (size_t)(k & 1) * SPLIT_PT * hd + fd;
+            const float* pr = prow + k * SPLIT_PT;
+            const int n = rangeN - k * SPLIT_PT < SPLIT_PT ? rangeN - k * SPLIT_PT : SPLIT_PT;
+            int t = 0;
+            for (; t + 8 <= n; t += 8) {   // reads batched, fold order unchanged
+                float pp[8], vv[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) { pp[u] = pr[t + u]; vv[u] = vc[(t + u) * hd]; }
+#pragma unroll
+                for (int u = 0; u < 8; u++) acc = __fmaf_rn(pp[u], vv[u], acc);
+            }
+            for (; t < n; t++) acc = __fmaf_rn(pr[t], vc[t * hd], acc);
+        }
+        __syncthreads();
     }
+    if (fold) partO[(((long)b * nh + hk * rep + fr) * S + sp) * hd + fd] = acc;
 }
 
 // grid (nh, B), block hd: global max over the ranges, w = __expf(local max - global max),
@@ -539,13 +568,14 @@ extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, co
     LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_decode_split: q_ld=%d out_ld=%d", q_ld, out_ld);
     LT_REQUIRE((Xq == nullptr) == (Xd == nullptr), "lt_attn_decode_split: Xq and Xd are given together or not at all");
     LT_REQUIRE(Xq == nullptr || out_ld == nh * hd, "lt_attn_decode_split: the quantised output needs out_ld == nh*hd");
-    LT_REQUIRE(aligned16(Q) && aligned16(K), "lt_attn_decode_split: Q and K must be 16-byte aligned");
+    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "lt_attn_decode_split: Q, K and V must be 16-byte aligned");
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_attn_decode_split: status word unavailable");
     cudaStream_t s = (cudaStream_t)stream;
     const int rep = nh / nkv;
     const int per_max = (((max_seq + nsplit - 1) / nsplit) + 3) & ~3;
-    const size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max) * sizeof(float);
+    const size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max + 2 * (size_t)SPLIT_PT * hd) *
+                        sizeof(float);
     LT_REQUIRE(smem <= 200 * 1024, "lt_attn_decode_split: max_seq=%d / nsplit=%d needs %zu bytes of shared memory", max_seq, nsplit, smem);
     static bool attr_done = false;
     if (!attr_done) {
