@@ -124,6 +124,10 @@ def cpu_decode_baseline(model, prompt, budget_s=15.0, max_tokens=16):
     """tok/s of the CPU port (oracle engine, OpenMP over output rows) on a bounded sample."""
     from oracle import oracle as o
     from llamatov_b200 import synth
+    try:
+        o.set_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        o.set_threads(os.cpu_count() or 1)
     eng = o.OracleEngine(synth.oracle_model(model), max_seq=256)
     t0 = time.perf_counter()
     _, nxt = eng.step(prompt[0])
@@ -146,6 +150,10 @@ def run_reference(args, rank):
     model = synth.make_model(ARCH, seed=0)
     prompt = np.random.default_rng(0).integers(0, model["cfg"]["vocab"], size=PROMPT_LEN).tolist()
     from oracle import oracle as o
+    try:
+        o.set_threads(len(os.sched_getaffinity(0)))     # all host cores, whatever the launcher exported
+    except AttributeError:
+        o.set_threads(os.cpu_count() or 1)
     eng = o.OracleEngine(synth.oracle_model(model), max_seq=256)
     nxt = prompt[0]
     per_step = max(1, min(4, args.steps))       # tokens per "step" sample: bounded CPU work

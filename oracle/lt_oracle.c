@@ -568,6 +568,15 @@ int lto_decode_token(const lto_model* m, int tok, float* logits) {
     return best;
 }
 
+/* n > 0: use n OpenMP threads from now on (a launcher may have exported OMP_NUM_THREADS=1) */
+void lto_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int lto_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -216,6 +216,11 @@ def num_threads():
     return int(lib().lto_num_threads())
 
 
+def set_threads(n):
+    """Use n OpenMP threads (torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks)."""
+    lib().lto_set_threads(ctypes.c_int(int(n)))
+
+
 # ------------------------------------------------------------------ whole-model engine
 
 class _Q8W(ctypes.Structure):
