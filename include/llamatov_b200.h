@@ -302,22 +302,21 @@ int lt_q8_gemm_ggml(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, cons
 /* ---- all-reduce over the GPUs of one node, fused with the residual add ---------------------
  * No counterpart in the reference (it is single-GPU).  For the tensor-parallel decode step:
  * out = resid + (part_0 + part_1 + ... in rank order), the same bits on every rank.  Each rank owns
- * a staging buffer and flags that its peers map through CUDA IPC; one kernel per rank stores its
- * partial into every rank's staging memory (plain peer stores), signals, waits (bounded:
- * LT_STATUS_WAIT_TIMEOUT) for the others' flags in its own memory and folds the local copies.
- * One process per GPU.  Setup: every rank calls lt_comm_alloc (fills 128 handle bytes), the ranks
- * exchange the handle bytes by any host means, every rank calls lt_comm_connect with all of them
- * (world * 128 bytes, rank order), then a host barrier before the first lt_allreduce_add. */
+ * a staging buffer that its peers map through CUDA IPC; one kernel per rank stores its partial into
+ * every rank's staging memory as {value, call-count tag} words (plain peer stores), polls the words of
+ * all ranks in its own memory (bounded: LT_STATUS_WAIT_TIMEOUT) and folds them.  One process per GPU.
+ * Setup: every rank calls lt_comm_alloc (fills LT_COMM_HANDLE_BYTES handle bytes), the ranks exchange
+ * the handle bytes by any host means, every rank calls lt_comm_connect with all of them (world *
+ * LT_COMM_HANDLE_BYTES bytes, rank order), then a host barrier before the first lt_allreduce_add. */
 #define LT_COMM_MAX_RANKS 8
+#define LT_COMM_HANDLE_BYTES 64
 typedef struct lt_comm {
     int rank, world, max_n, max_ctas;
     float* stage[LT_COMM_MAX_RANKS];      /* stage[r]: rank r's staging buffer as mapped in this process */
-    unsigned int* flags[LT_COMM_MAX_RANKS];
     float* local_stage;
-    unsigned int* local_flags;
     unsigned int* ctr;                    /* per-CTA call counters (device) */
 } lt_comm;
-int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handles);
+int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handle);
 int lt_comm_connect(lt_comm* comm, int rank, const unsigned char* all_handles);
 int lt_comm_free(lt_comm* comm);
 int lt_allreduce_add(const lt_comm* comm, const float* part, const float* resid, float* out, int n,

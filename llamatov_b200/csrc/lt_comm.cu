@@ -2,19 +2,19 @@
 // residual add that follows it in the tensor-parallel decode step:
 //     out = resid + ((part_0 + part_1) + part_2 + ... )          (rank order, the same bits on every rank)
 //
-// Every rank owns a staging buffer and a flag array that its peers map through CUDA IPC.  One
-// kernel per rank: a CTA copies its chunk of the local partial into slot [my rank] of EVERY rank's
-// staging buffer with plain peer stores over NVLink, publishes a flag per destination
-// (release, system scope), waits until the flags of all ranks have arrived in its own memory
-// (acquire, bounded) and then folds the `world` local copies in rank order.  No data crosses
-// NVLink twice, nothing is read from a peer, no multicast object is involved.
+// Every rank owns a staging buffer that its peers map through CUDA IPC.  One kernel per rank: a thread
+// stores its four elements of the local partial into slot [my rank] of EVERY rank's staging buffer as
+// 8-byte words {value, tag} (plain peer stores over NVLink; the tag is the call count), then polls the
+// words of all ranks in its own memory until their tags match and folds the values in rank order.  Data
+// and "it has arrived" travel in the same aligned 8-byte store, so there is no fence and no separate
+// flag on the path.  No data crosses NVLink twice, nothing is read from a peer, no multicast object is
+// involved.  Waits are bounded (LT_STATUS_WAIT_TIMEOUT).
 //
-// Epochs: a CTA counts its own calls in device memory (the launch arguments of a captured graph
-// never change), flag values are those counts, and staging is double-buffered by the count's
-// parity: a rank can run at most one all-reduce ahead of its slowest peer, because finishing
-// call k needs every peer's flag for k, which a peer only sends after it has left call k-1.
-// One process per GPU; the kernels of different ranks wait on each other and therefore must
-// never share a GPU.
+// Tags: a CTA counts its own calls in device memory (the launch arguments of a captured graph never
+// change); staging is double-buffered by the count's parity: a rank can run at most one all-reduce ahead
+// of its slowest peer, because finishing call k needs every peer's words of call k, which a peer only
+// sends after it has left call k-1.  One process per GPU; the kernels of different ranks wait on each
+// other and therefore must never share a GPU.
 #include <string.h>
 
 #include "lt_common.cuh"
@@ -25,73 +25,69 @@ constexpr int COMM_THREADS = 256;
 constexpr int COMM_CHUNK = COMM_THREADS * 4;        // floats per CTA
 constexpr long long COMM_WAIT_LIMIT = 2000000000LL; // SM clocks (about a second) before a wait gives up
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 struct CommDev {
-    float* stage[LT_COMM_MAX_RANKS];     // stage[r]: rank r's staging buffer [2][world][max_n]
-    unsigned* flags[LT_COMM_MAX_RANKS];  // flags[r]: rank r's flags [2][world][max_ctas]
+    float2* stage[LT_COMM_MAX_RANKS];    // stage[r]: rank r's staging buffer [2][world][max_n] of {value, tag}
     unsigned* ctr;                       // this rank's call counters [max_ctas]
     int rank, world, max_n, max_ctas;
 };
+
+__device__ __forceinline__ float2 ld_volatile_f2(const float2* p) {
+    float2 v;
+    asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 __global__ void __launch_bounds__(COMM_THREADS)
 k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __restrict__ resid,
                 float* __restrict__ out, int n, int* status) {
     __shared__ unsigned s_epoch;
-    __shared__ int s_fail;
     const int c = blockIdx.x, tid = threadIdx.x;
-    if (tid == 0) {
-        s_epoch = C.ctr[c] + 1;
-        s_fail = 0;
-    }
+    if (tid == 0) s_epoch = C.ctr[c] + 1;
     __syncthreads();
     const unsigned epoch = s_epoch;
+    const float tag = __uint_as_float(epoch);
     const int par = (int)(epoch & 1u);
     const int i = c * COMM_CHUNK + tid * 4;
-    const long slot = ((long)par * C.world + C.rank) * C.max_n;
-    // 1. my chunk of the partial into slot [my rank] of every rank's staging buffer
     if (i < n) {
+        // 1. my four elements, tagged, into slot [my rank] of every rank's staging buffer
         const float4 v = *(const float4*)(part + i);
-        for (int r = 0; r < C.world; r++) *(float4*)(C.stage[r] + slot + i) = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    // 2. tell every rank that this chunk of mine has landed
-    if (tid < C.world) st_release_sys(C.flags[tid] + ((long)par * C.world + C.rank) * C.max_ctas + c, epoch);
-    // 3. wait for every rank's chunk in my own memory
-    if (tid < C.world) {
-        const unsigned* f = C.flags[C.rank] + ((long)par * C.world + tid) * C.max_ctas + c;
+        const long slot = ((long)par * C.world + C.rank) * C.max_n + i;
+        for (int r = 0; r < C.world; r++) {
+            float2* d = C.stage[r] + slot;
+            d[0] = make_float2(v.x, tag); d[1] = make_float2(v.y, tag);
+            d[2] = make_float2(v.z, tag); d[3] = make_float2(v.w, tag);
+        }
+        // 2. every rank's four elements from my own memory, folded in rank order
+        const float2* mine = C.stage[C.rank] + (long)par * C.world * C.max_n + i;
+        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        bool ok = true;
         const long long t0 = clock64();
-        while (ld_acquire_sys(f) != epoch) {
-            if (clock64() - t0 > COMM_WAIT_LIMIT) {
-                s_fail = 1;
-                atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
-                break;
+        for (int r = 0; r < C.world && ok; r++) {
+            const float2* src = mine + (long)r * C.max_n;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float2 w = ld_volatile_f2(src + e);
+                while (__float_as_uint(w.y) != epoch) {
+                    if (clock64() - t0 > COMM_WAIT_LIMIT) {
+                        atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    w = ld_volatile_f2(src + e);
+                }
+                a[e] = r == 0 ? w.x : __fadd_rn(a[e], w.x);
             }
         }
+        if (ok) {
+            float4 y = make_float4(a[0], a[1], a[2], a[3]);
+            if (resid != nullptr) {
+                const float4 x = *(const float4*)(resid + i);
+                y.x = __fadd_rn(x.x, y.x); y.y = __fadd_rn(x.y, y.y); y.z = __fadd_rn(x.z, y.z); y.w = __fadd_rn(x.w, y.w);
+            }
+            *(float4*)(out + i) = y;
+        }
     }
     __syncthreads();
-    // 4. fold the copies in rank order, add the residual
-    if (i < n && !s_fail) {
-        const float* mine = C.stage[C.rank] + (long)par * C.world * C.max_n + i;
-        float4 a = __ldcg((const float4*)mine);
-        for (int r = 1; r < C.world; r++) {
-            const float4 b = __ldcg((const float4*)(mine + (long)r * C.max_n));
-            a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
-        }
-        if (resid != nullptr) {
-            const float4 x = *(const float4*)(resid + i);
-            a.x = __fadd_rn(x.x, a.x); a.y = __fadd_rn(x.y, a.y); a.z = __fadd_rn(x.z, a.z); a.w = __fadd_rn(x.w, a.w);
-        }
-        *(float4*)(out + i) = a;
-    }
     if (tid == 0) C.ctr[c] = epoch;
 }
 
@@ -99,30 +95,25 @@ k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __
 
 using namespace lt;
 
-extern "C" int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handles) {
-    LT_REQUIRE(comm && handles, "lt_comm_alloc: null pointer");
+extern "C" int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handle) {
+    LT_REQUIRE(comm && handle, "lt_comm_alloc: null pointer");
     LT_REQUIRE(world >= 1 && world <= LT_COMM_MAX_RANKS, "lt_comm_alloc: world=%d (1..%d)", world, LT_COMM_MAX_RANKS);
     LT_REQUIRE(max_n > 0 && max_n % 4 == 0, "lt_comm_alloc: max_n=%d must be a positive multiple of 4", max_n);
     memset(comm, 0, sizeof(*comm));
     comm->world = world; comm->max_n = max_n;
     comm->max_ctas = (max_n + COMM_CHUNK - 1) / COMM_CHUNK;
-    const size_t sb = (size_t)2 * world * max_n * sizeof(float);
-    const size_t fb = (size_t)2 * world * comm->max_ctas * sizeof(unsigned);
-    void *s = nullptr, *f = nullptr, *c = nullptr;
+    const size_t sb = (size_t)2 * world * max_n * sizeof(float2);
+    void *s = nullptr, *c = nullptr;
     LT_CUDA(cudaMalloc(&s, sb));
-    LT_CUDA(cudaMalloc(&f, fb));
     LT_CUDA(cudaMalloc(&c, (size_t)comm->max_ctas * sizeof(unsigned)));
-    LT_CUDA(cudaMemset(s, 0, sb));
-    LT_CUDA(cudaMemset(f, 0, fb));
+    LT_CUDA(cudaMemset(s, 0, sb));          // tag 0 = never written (call counts start at 1)
     LT_CUDA(cudaMemset(c, 0, (size_t)comm->max_ctas * sizeof(unsigned)));
     LT_CUDA(cudaDeviceSynchronize());
-    comm->local_stage = (float*)s; comm->local_flags = (unsigned*)f; comm->ctr = (unsigned*)c;
-    cudaIpcMemHandle_t hs, hf;
+    comm->local_stage = (float*)s; comm->ctr = (unsigned*)c;
+    cudaIpcMemHandle_t hs;
     LT_CUDA(cudaIpcGetMemHandle(&hs, s));
-    LT_CUDA(cudaIpcGetMemHandle(&hf, f));
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-    memcpy(handles, &hs, 64);
-    memcpy(handles + 64, &hf, 64);
+    static_assert(sizeof(cudaIpcMemHandle_t) == LT_COMM_HANDLE_BYTES, "IPC handle size");
+    memcpy(handle, &hs, LT_COMM_HANDLE_BYTES);
     return LT_OK;
 }
 
@@ -133,16 +124,13 @@ extern "C" int lt_comm_connect(lt_comm* comm, int rank, const unsigned char* all
     for (int r = 0; r < comm->world; r++) {
         if (r == rank) {
             comm->stage[r] = comm->local_stage;
-            comm->flags[r] = comm->local_flags;
             continue;
         }
-        cudaIpcMemHandle_t hs, hf;
-        memcpy(&hs, all_handles + (size_t)r * 128, 64);
-        memcpy(&hf, all_handles + (size_t)r * 128 + 64, 64);
-        void *s = nullptr, *f = nullptr;
+        cudaIpcMemHandle_t hs;
+        memcpy(&hs, all_handles + (size_t)r * LT_COMM_HANDLE_BYTES, LT_COMM_HANDLE_BYTES);
+        void* s = nullptr;
         LT_CUDA(cudaIpcOpenMemHandle(&s, hs, cudaIpcMemLazyEnablePeerAccess));
-        LT_CUDA(cudaIpcOpenMemHandle(&f, hf, cudaIpcMemLazyEnablePeerAccess));
-        comm->stage[r] = (float*)s; comm->flags[r] = (unsigned*)f;
+        comm->stage[r] = (float*)s;
     }
     return LT_OK;
 }
@@ -152,10 +140,8 @@ extern "C" int lt_comm_free(lt_comm* comm) {
     for (int r = 0; r < comm->world; r++) {
         if (r == comm->rank) continue;
         if (comm->stage[r]) cudaIpcCloseMemHandle(comm->stage[r]);
-        if (comm->flags[r]) cudaIpcCloseMemHandle(comm->flags[r]);
     }
     if (comm->local_stage) cudaFree(comm->local_stage);
-    if (comm->local_flags) cudaFree(comm->local_flags);
     if (comm->ctr) cudaFree(comm->ctr);
     memset(comm, 0, sizeof(*comm));
     return LT_OK;
@@ -170,10 +156,7 @@ extern "C" int lt_allreduce_add(const lt_comm* comm, const float* part, const fl
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_allreduce_add: status word unavailable");
     CommDev C;
-    for (int r = 0; r < LT_COMM_MAX_RANKS; r++) {
-        C.stage[r] = comm->stage[r];
-        C.flags[r] = comm->flags[r];
-    }
+    for (int r = 0; r < LT_COMM_MAX_RANKS; r++) C.stage[r] = (float2*)comm->stage[r];
     C.ctr = comm->ctr; C.rank = comm->rank; C.world = comm->world; C.max_n = comm->max_n; C.max_ctas = comm->max_ctas;
     const int ctas = (n + COMM_CHUNK - 1) / COMM_CHUNK;
     k_allreduce_add<<<ctas, COMM_THREADS, 0, (cudaStream_t)stream>>>(C, part, resid, out, n, st);

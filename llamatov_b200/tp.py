@@ -106,8 +106,7 @@ def _stream():
 class _CommStruct(ctypes.Structure):
     """struct lt_comm of include/llamatov_b200.h."""
     _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("max_n", ctypes.c_int), ("max_ctas", ctypes.c_int),
-                ("stage", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8),
-                ("local_stage", ctypes.c_void_p), ("local_flags", ctypes.c_void_p), ("ctr", ctypes.c_void_p)]
+                ("stage", ctypes.c_void_p * 8), ("local_stage", ctypes.c_void_p), ("ctr", ctypes.c_void_p)]
 
 
 class P2PComm:
@@ -117,12 +116,12 @@ class P2PComm:
     def __init__(self, rank, world, max_n, group=None):
         import torch.distributed as dist
         self.c = _CommStruct()
-        handles = (ctypes.c_ubyte * 128)()
+        handles = (ctypes.c_ubyte * 64)()
         _lib.call("lt_comm_alloc", world, max_n, ctypes.byref(self.c), handles)
         mine = bytes(handles)
         gathered = [None] * world
         dist.all_gather_object(gathered, mine, group=group)
-        allh = (ctypes.c_ubyte * (128 * world)).from_buffer_copy(b"".join(gathered))
+        allh = (ctypes.c_ubyte * (64 * world)).from_buffer_copy(b"".join(gathered))
         _lib.call("lt_comm_connect", ctypes.byref(self.c), rank, allh)
         torch.cuda.synchronize()
         dist.barrier(group=group)          # every rank's buffers exist and are zero before the first store
