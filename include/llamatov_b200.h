@@ -46,6 +46,15 @@ const char* lt_version(void);
  * once, at capture). */
 unsigned long long lt_launch_count(void);
 
+/* Chained launches for the one-sequence decode operators (lt_q8_gemv with T = 1, lt_rmsnorm_q8_gemv,
+ * lt_rope_append_batch, lt_attn_decode_batch, lt_attn_decode_split, lt_silu_mul_quant_rows, lt_embed_q8_rows,
+ * lt_argmax, lt_add, lt_allreduce_add): when on, these kernels are enqueued with programmatic stream
+ * serialisation; each lets its successor be scheduled at once, fetches its first weight rows, and only then
+ * waits for its predecessor to complete, so launch latency and the head of the weight stream overlap the
+ * predecessor's tail.  Results are unchanged.  Process-wide, off by default; returns the previous setting.
+ * A captured graph keeps the setting it was recorded with. */
+int lt_set_chained_launch(int on);
+
 /* Reads the device status word of the current device into *h_status and clears it.
  * Synchronises `stream`.  Not capturable. */
 int lt_device_status(unsigned int* h_status, void* stream);
@@ -105,6 +114,14 @@ int lt_rmsnorm(const float* x, const float* w, float* y, int M, int N, float eps
  * bpd/kernelgen/referee/rms_quant_prod_ab.py); y may be NULL when only the quantised row is wanted. */
 int lt_rmsnorm_quant(const float* x, const float* w, float* y, int8_t* Xq, uint16_t* Xd, int M, int N, float eps,
                      void* stream);
+
+/* lt_rmsnorm + lt_quant_q8 + lt_q8_gemv (one column) in one launch, for the decode step's q|k|v and
+ * gate|up projections: the reference's RMS->quant seam and its QFUSED GEMV, which quantises x into shared
+ * memory itself (bpd/lib/dev_residency.py:937-948), taken one step further: every CTA normalises and quantises the K-vector X for itself in
+ * shared memory, with the same arithmetic as the separate launches, then folds its rows.
+ * Y[n] = sum over the Q8_0 row n and quant((X*inv)*normw) (+ Resid[n]); Y must not alias X. */
+int lt_rmsnorm_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const float* X, const float* normw, float eps,
+                       const float* Resid, float* Y, int M, int K, void* stream);
 
 /* ---- RoPE ------------------------------------------------------------------------------
  * replaces k_rope (bpd/kernelgen/emitters/rope_from_facts.pl:40-69; launched from

@@ -30,6 +30,7 @@ SIGNATURES = {
     "lt_q8_gemm_ggml": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_rmsnorm": [_vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "lt_rmsnorm_q8_gemv": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp],
     "lt_rope": [_vp, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_incr_len": [_vp, _vp],
@@ -63,7 +64,8 @@ _RESTYPES = {"lt_last_error": ctypes.c_char_p, "lt_version": ctypes.c_char_p,
              "lt_launch_count": ctypes.c_ulonglong}
 # name -> (argtypes, restype) for the entries that return something other than a status code
 _QUERIES = {"lt_attn_decode_batch_scratch_floats": ([_i, _i, _i], ctypes.c_long),
-            "lt_attn_decode_split_scratch_floats": ([_i, _i, _i, _i], ctypes.c_long)}
+            "lt_attn_decode_split_scratch_floats": ([_i, _i, _i, _i], ctypes.c_long),
+            "lt_set_chained_launch": ([_i], ctypes.c_int)}
 
 
 def lib():

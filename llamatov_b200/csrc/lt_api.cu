@@ -18,6 +18,9 @@ void set_error(const char* fmt, ...) {
 static unsigned long long g_launches = 0;
 void count_launches(int n) { __atomic_fetch_add(&g_launches, (unsigned long long)n, __ATOMIC_RELAXED); }
 
+static int g_chained = 0;
+bool chained_launch() { return __atomic_load_n(&g_chained, __ATOMIC_RELAXED) != 0; }
+
 __device__ int g_status_word = 0;
 
 int* device_status_ptr() {
@@ -41,6 +44,10 @@ extern "C" const char* lt_last_error(void) { return lt::g_err; }
 extern "C" const char* lt_version(void) { return "llamatov_b200 0.1 (sm_100a)"; }
 
 extern "C" unsigned long long lt_launch_count(void) { return __atomic_load_n(&lt::g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int lt_set_chained_launch(int on) {
+    return __atomic_exchange_n(&lt::g_chained, on ? 1 : 0, __ATOMIC_RELAXED);
+}
 
 extern "C" int lt_device_status(unsigned int* h_status, void* stream) {
     LT_REQUIRE(h_status != nullptr, "lt_device_status: null output");

@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(256)
 k_rope_append_batch(float* __restrict__ X, int ld, int n_qhead, int n_kvhead, int hd, float theta,
                     float* __restrict__ kbase, float* __restrict__ vbase, int* __restrict__ lens, int max_seq,
                     int* __restrict__ ticket, int* status) {
+    chain_release();
+    chain_wait();
     const int b = blockIdx.y;
     const int L = lens[b];
     const bool ok = L >= 0 && L < max_seq;
@@ -111,6 +113,8 @@ k_rope_append_batch(float* __restrict__ X, int ld, int n_qhead, int n_kvhead, in
 __global__ void __launch_bounds__(BT)
 k_attn_scores(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const int* __restrict__ lens,
               float* __restrict__ S, int s_ld, int hd, int nh, int nkv, float scale, int max_seq, int* status) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) float qs[];   // [rep][hd]
     const int b = blockIdx.z, hk = blockIdx.y;
     const int rep = nh / nkv;
@@ -156,6 +160,8 @@ k_attn_scores(const float* __restrict__ Q, int q_ld, const float* __restrict__ K
 __global__ void __launch_bounds__(BT)
 k_attn_softmax(float* __restrict__ S, int s_ld, const int* __restrict__ lens, float* __restrict__ Z, int nh,
                int max_seq) {
+    chain_release();
+    chain_wait();
     extern __shared__ float sh[];
     __shared__ float red[64];
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
@@ -220,6 +226,8 @@ __global__ void __launch_bounds__(32 * MAX_REP)
 k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
           const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq,
           int8_t* __restrict__ Xq, __half* __restrict__ Xd) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) float pv_buf[];
     float (*vt)[PV_TT][32] = (float (*)[PV_TT][32])pv_buf;                                  // [stage][t][d]
     float (*pt)[MAX_REP][PV_TT] = (float (*)[MAX_REP][PV_TT])(pv_buf + PV_STAGES * PV_TT * 32);   // [stage][head][t]
@@ -305,7 +313,10 @@ constexpr int SPLIT_PT = 64;   // positions per staged V tile
 __global__ void __launch_bounds__(1024)
 k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
              const int* __restrict__ lens, float* __restrict__ partM, float* __restrict__ partZ,
-             float* __restrict__ partO, int hd, int nh, int nkv, float scale, int max_seq, int per_max, int* status) {
+             float* __restrict__ partO, int hd, int nh, int nkv, float scale, int max_seq, int per_max, int kstage,
+             int* status) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) float sp_smem[];
     const int S = gridDim.x, sp = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int rep = nh / nkv;
@@ -324,18 +335,52 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
     int p1 = p0 + per;
     if (p1 > L) p1 = L;
     const int rangeN = p1 > p0 ? p1 - p0 : 0;
+    // Everything the CTA will read is requested at once with asynchronous copies: the K rows of the range
+    // (kstage: they fit beside the rest; 16-byte chunk c of row t lands at chunk c ^ (t & 7), so that the
+    // one-thread-per-position reads below are free of bank conflicts) and the first two V tiles.
+    float* vt = sh + (size_t)rep * per_max;   // [2][SPLIT_PT][hd]
+    float* ks = vt + 2 * (size_t)SPLIT_PT * hd;   // [per_max][hd], swizzled (kstage only)
+    const float* Vb = V + (((long)b * max_seq + p0) * nkv + hk) * hd;
+    const long vs = (long)nkv * hd;
+    const int cpr = hd >> 2;                  // 16-byte chunks per row
+    const int ntile = (rangeN + SPLIT_PT - 1) / SPLIT_PT;
+    auto stage = [&](int k) {
+        if (k < ntile) {
+            float* dst = vt + (size_t)(k & 1) * SPLIT_PT * hd;
+            const int t0 = k * SPLIT_PT;
+            for (int i = tid; i < SPLIT_PT * cpr; i += blockDim.x) {
+                const int row = i / cpr, c = i - row * cpr;
+                if (t0 + row < rangeN) cp_async16(dst + row * hd + c * 4, Vb + (long)(t0 + row) * vs + c * 4);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (kstage) {
+        const float* Kb = K + (((long)b * max_seq + p0) * nkv + hk) * hd;
+        for (int i = tid; i < rangeN * cpr; i += blockDim.x) {
+            const int row = i / cpr, c = i - row * cpr;
+            cp_async16(ks + (size_t)row * hd + ((c ^ (row & 7)) << 2), Kb + (long)row * vs + c * 4);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    stage(0);
+    stage(1);
     for (int i = tid; i < rep * hd; i += blockDim.x) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    asm volatile("cp.async.wait_group 2;" ::: "memory");     // the K rows have landed (the V tiles may be in flight)
     __syncthreads();
     // scores of the range, once: s = fold_i fma(q[i], K[t, i], s), then * scale
     for (int t = p0 + tid; t < p1; t += blockDim.x) {
-        const float4* Kt = (const float4*)(K + (((long)b * max_seq + t) * nkv + hk) * hd);
+        const int tl = t - p0;
+        const float4* Kt = kstage ? (const float4*)(ks + (size_t)tl * hd)
+                                  : (const float4*)(K + (((long)b * max_seq + t) * nkv + hk) * hd);
+        const int sw = kstage ? (tl & 7) : 0;
         float s[MAX_REP];
 #pragma unroll
         for (int r = 0; r < MAX_REP; r++) s[r] = 0.0f;
         for (int i0 = 0; i0 < (hd >> 2); i0 += 8) {
             float4 kk[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) kk[u] = Kt[i0 + u];
+            for (int u = 0; u < 8; u++) kk[u] = Kt[(i0 + u) ^ sw];
 #pragma unroll
             for (int u = 0; u < 8; u++) {
 #pragma unroll
@@ -352,7 +397,7 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
         }
 #pragma unroll
         for (int r = 0; r < MAX_REP; r++)
-            if (r < rep) sh[r * per_max + (t - p0)] = __fmul_rn(s[r], scale);
+            if (r < rep) sh[r * per_max + tl] = __fmul_rn(s[r], scale);
     }
     __syncthreads();
     // per head on 64 lanes: local max, exponentials against it, Z (lane l sums t = l, l+64, ... of the range;
@@ -397,32 +442,14 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
         __syncthreads();
     }
     // partial V sum: left fold over the range, one thread per (head, output element).  The V rows of the
-    // range are staged in tiles of SPLIT_PT positions by asynchronous copies (all threads, coalesced), one
-    // tile ahead of the fold, so that the chain never waits on global memory.
-    float* vt = sh + (size_t)rep * per_max;   // [2][SPLIT_PT][hd]
-    const float* Vb = V + (((long)b * max_seq + p0) * nkv + hk) * hd;
-    const long vs = (long)nkv * hd;
-    const int cpr = hd >> 2;                  // 16-byte chunks per row
-    const int ntile = (rangeN + SPLIT_PT - 1) / SPLIT_PT;
-    auto stage = [&](int k) {
-        if (k < ntile) {
-            float* dst = vt + (size_t)(k & 1) * SPLIT_PT * hd;
-            const int t0 = k * SPLIT_PT;
-            for (int i = tid; i < SPLIT_PT * cpr; i += blockDim.x) {
-                const int row = i / cpr, c = i - row * cpr;
-                if (t0 + row < rangeN) cp_async16(dst + row * hd + c * 4, Vb + (long)(t0 + row) * vs + c * 4);
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
+    // range arrive in tiles of SPLIT_PT positions (asynchronous copies by all threads, coalesced), two tiles
+    // ahead of the fold, so that the chain never waits on global memory.
     const bool fold = tid < rep * hd;
     const int fr = fold ? tid / hd : 0, fd = fold ? tid - fr * hd : 0;
     const float* prow = sh + fr * per_max;
     float acc = 0.0f;
-    stage(0);
     for (int k = 0; k < ntile; k++) {
-        stage(k + 1);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");     // tile k has landed, tile k+1 may be in flight
         __syncthreads();
         if (fold) {
             const float* vc = vt + (size_t)(k & 1) * SPLIT_PT * hd + fd;
@@ -439,7 +466,9 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
             for (; t < n; t++) acc = __fmaf_rn(pr[t], vc[t * hd], acc);
         }
         __syncthreads();
+        stage(k + 2);      // into the buffer just folded
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (fold) partO[(((long)b * nh + hk * rep + fr) * S + sp) * hd + fd] = acc;
 }
 
@@ -448,15 +477,28 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
 __global__ void k_attn_split_combine(const float* __restrict__ partM, const float* __restrict__ partZ,
                                      const float* __restrict__ partO, float* __restrict__ OUT, int out_ld, int hd, int nh,
                                      int S, int8_t* __restrict__ Xq, __half* __restrict__ Xd) {
+    chain_release();
+    chain_wait();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const long o = ((long)b * nh + h) * S;
     float M = -1e30f;
     for (int sp = 0; sp < S; sp++) M = fmaxf(M, partM[o + sp]);
     float Z = 0.0f, acc = 0.0f;
-    for (int sp = 0; sp < S; sp++) {
-        const float w = __expf(__fsub_rn(partM[o + sp], M));
-        Z = __fmaf_rn(w, partZ[o + sp], Z);
-        acc = __fmaf_rn(w, partO[(o + sp) * hd + d], acc);
+    for (int s0 = 0; s0 < S; s0 += 16) {      // 16 ranges' loads in flight together; fold order unchanged
+        float pm[16], pz[16], po[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const int sp = s0 + u < S ? s0 + u : S - 1;
+            pm[u] = partM[o + sp]; pz[u] = partZ[o + sp]; po[u] = partO[(o + sp) * hd + d];
+        }
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            if (s0 + u < S) {
+                const float w = __expf(__fsub_rn(pm[u], M));
+                Z = __fmaf_rn(w, pz[u], Z);
+                acc = __fmaf_rn(w, po[u], acc);
+            }
+        }
     }
     const float y = __fdiv_rn(acc, Z);
     OUT[(long)b * out_ld + (long)h * hd + d] = y;
@@ -505,9 +547,10 @@ extern "C" int lt_rope_append_batch(float* X, int ld, int n_qhead, int n_kvhead,
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_rope_append_batch: status word unavailable");
     const int pairs = (n_qhead + n_kvhead) * (hd / 2);
-    k_rope_append_batch<<<dim3((pairs + 255) / 256, B), 256, 0, (cudaStream_t)stream>>>(
-        X, ld, n_qhead, n_kvhead, hd, theta, kbase, vbase, lens, max_seq, ticket, st);
-    return check_launch("lt_rope_append_batch");
+    const cudaError_t e = launch_chained(k_rope_append_batch, dim3((pairs + 255) / 256, B), dim3(256), 0,
+                                         (cudaStream_t)stream, X, ld, n_qhead, n_kvhead, hd, theta, kbase, vbase, lens,
+                                         max_seq, ticket, st);
+    return check_launch("lt_rope_append_batch", 1, e);
 }
 
 extern "C" long lt_attn_decode_batch_scratch_floats(int nh, int max_seq, int B) {
@@ -540,16 +583,21 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
         LT_CUDA(cudaFuncSetAttribute(k_attn_pv<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(2)));
         attr_done = true;
     }
-    k_attn_scores<<<dim3((max_seq + BT - 1) / BT, nkv, B), BT, (size_t)rep * hd * sizeof(float), s>>>(
-        Q, q_ld, K, lens, S, s_ld, hd, nh, nkv, scale, max_seq, st);
-    k_attn_softmax<<<dim3(nh, B), BT, (size_t)max_seq * sizeof(float), s>>>(S, s_ld, lens, Z, nh, max_seq);
-    if ((long)(hd / 32) * nkv * B >= 592)
-        k_attn_pv<2><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(2), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
-                                                                        max_seq, Xq, (__half*)Xd);
-    else
-        k_attn_pv<4><<<dim3(hd / 32, nkv, B), 32 * rep, pv_smem(4), s>>>(S, s_ld, V, lens, Z, OUT, out_ld, hd, nh, nkv,
-                                                                        max_seq, Xq, (__half*)Xd);
-    return check_launch("lt_attn_decode_batch", 3);
+    cudaError_t e = launch_chained(k_attn_scores, dim3((max_seq + BT - 1) / BT, nkv, B), dim3(BT),
+                                   (size_t)rep * hd * sizeof(float), s, Q, q_ld, K, lens, S, s_ld, hd, nh, nkv, scale,
+                                   max_seq, st);
+    if (e == cudaSuccess)
+        e = launch_chained(k_attn_softmax, dim3(nh, B), dim3(BT), (size_t)max_seq * sizeof(float), s, S, s_ld, lens, Z, nh,
+                           max_seq);
+    if (e == cudaSuccess) {
+        if ((long)(hd / 32) * nkv * B >= 592)
+            e = launch_chained(k_attn_pv<2>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(2), s, S, s_ld, V, lens, Z, OUT,
+                               out_ld, hd, nh, nkv, max_seq, Xq, (__half*)Xd);
+        else
+            e = launch_chained(k_attn_pv<4>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(4), s, S, s_ld, V, lens, Z, OUT,
+                               out_ld, hd, nh, nkv, max_seq, Xq, (__half*)Xd);
+    }
+    return check_launch("lt_attn_decode_batch", 3, e);
 }
 
 extern "C" long lt_attn_decode_split_scratch_floats(int nh, int hd, int nsplit, int B) {
@@ -574,12 +622,16 @@ extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, co
     cudaStream_t s = (cudaStream_t)stream;
     const int rep = nh / nkv;
     const int per_max = (((max_seq + nsplit - 1) / nsplit) + 3) & ~3;
-    const size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max + 2 * (size_t)SPLIT_PT * hd) *
-                        sizeof(float);
+    size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max + 2 * (size_t)SPLIT_PT * hd) *
+                  sizeof(float);
     LT_REQUIRE(smem <= 200 * 1024, "lt_attn_decode_split: max_seq=%d / nsplit=%d needs %zu bytes of shared memory", max_seq, nsplit, smem);
+    // the K rows of a range are staged in shared memory too when they fit beside the rest
+    const size_t kbytes = (size_t)per_max * hd * sizeof(float);
+    const int kstage = smem + kbytes <= 227 * 1024 ? 1 : 0;
+    if (kstage) smem += kbytes;
     static bool attr_done = false;
     if (!attr_done) {
-        LT_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LT_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_done = true;
     }
     int threads = ((rep * hd + 31) / 32) * 32;
@@ -588,8 +640,10 @@ extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, co
     float* partM = scratch;
     float* partZ = partM + (long)B * nh * nsplit;
     float* partO = partZ + (long)B * nh * nsplit;
-    k_attn_split<<<dim3(nsplit, nkv, B), threads, smem, s>>>(Q, q_ld, K, V, lens, partM, partZ, partO, hd, nh, nkv, scale,
-                                                            max_seq, per_max, st);
-    k_attn_split_combine<<<dim3(nh, B), hd, 0, s>>>(partM, partZ, partO, OUT, out_ld, hd, nh, nsplit, Xq, (__half*)Xd);
-    return check_launch("lt_attn_decode_split", 2);
+    cudaError_t e = launch_chained(k_attn_split, dim3(nsplit, nkv, B), dim3(threads), smem, s, Q, q_ld, K, V, lens, partM,
+                                   partZ, partO, hd, nh, nkv, scale, max_seq, per_max, kstage, st);
+    if (e == cudaSuccess)
+        e = launch_chained(k_attn_split_combine, dim3(nh, B), dim3(hd), 0, s, partM, partZ, partO, OUT, out_ld, hd, nh,
+                           nsplit, Xq, (__half*)Xd);
+    return check_launch("lt_attn_decode_split", 2, e);
 }

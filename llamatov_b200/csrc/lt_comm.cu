@@ -40,6 +40,8 @@ __device__ __forceinline__ float2 ld_volatile_f2(const float2* p) {
 __global__ void __launch_bounds__(COMM_THREADS)
 k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __restrict__ resid,
                 float* __restrict__ out, int n, int* status) {
+    chain_release();
+    chain_wait();
     __shared__ unsigned s_epoch;
     const int c = blockIdx.x, tid = threadIdx.x;
     if (tid == 0) s_epoch = C.ctr[c] + 1;
@@ -159,6 +161,7 @@ extern "C" int lt_allreduce_add(const lt_comm* comm, const float* part, const fl
     for (int r = 0; r < LT_COMM_MAX_RANKS; r++) C.stage[r] = (float2*)comm->stage[r];
     C.ctr = comm->ctr; C.rank = comm->rank; C.world = comm->world; C.max_n = comm->max_n; C.max_ctas = comm->max_ctas;
     const int ctas = (n + COMM_CHUNK - 1) / COMM_CHUNK;
-    k_allreduce_add<<<ctas, COMM_THREADS, 0, (cudaStream_t)stream>>>(C, part, resid, out, n, st);
-    return check_launch("lt_allreduce_add");
+    const cudaError_t e = launch_chained(k_allreduce_add, dim3(ctas), dim3(COMM_THREADS), 0, (cudaStream_t)stream, C, part,
+                                         resid, out, n, st);
+    return check_launch("lt_allreduce_add", 1, e);
 }

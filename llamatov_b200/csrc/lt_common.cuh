@@ -20,14 +20,42 @@ int* device_status_ptr();
 // Number of kernel launches this library has enqueued in this process (lt_launch_count()).
 void count_launches(int n);
 
-inline int check_launch(const char* what, int n = 1) {
+inline int check_launch(const char* what, int n = 1, cudaError_t launched = cudaSuccess) {
     count_launches(n);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launched != cudaSuccess ? launched : cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
         return LT_ERR_CUDA;
     }
     return LT_OK;
+}
+
+// Chained launches (lt_set_chained_launch): kernels of the one-sequence decode operators are enqueued with
+// programmatic stream serialisation, so that a kernel's CTAs may become resident while its predecessor in
+// the stream is still running.  Such a kernel calls chain_release() at its start (lets ITS successor be
+// scheduled), may fetch what no predecessor writes (weights) and calls chain_wait() before it touches
+// anything else; chain_wait() returns when the predecessor has completed and its writes are visible.  Both
+// calls do nothing in a kernel that was launched the ordinary way.
+bool chained_launch();
+
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... P, typename... A>
+inline cudaError_t launch_chained(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    if (chained_launch()) {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
 }
 
 #define LT_REQUIRE(cond, ...)                 \

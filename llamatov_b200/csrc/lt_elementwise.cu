@@ -41,6 +41,8 @@ __global__ void k_silu_mul(const float* __restrict__ g, const float* __restrict_
 }
 
 __global__ void k_add(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, int n) {
+    chain_release();
+    chain_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = __fadd_rn(a[i], b[i]);
 }
@@ -190,6 +192,8 @@ constexpr int ARGMAX_BLOCKS = 296;  // two per SM
 
 __global__ void __launch_bounds__(256) k_argmax_s1(const float* __restrict__ x, int n, float* __restrict__ pval,
                                                     int* __restrict__ pidx) {
+    chain_release();
+    chain_wait();
     Best m;
     m.v = -3.4e38f;
     m.i = 2147483647;
@@ -205,6 +209,8 @@ __global__ void __launch_bounds__(256) k_argmax_s1(const float* __restrict__ x, 
 
 __global__ void __launch_bounds__(256) k_argmax_s2(const float* __restrict__ pval, const int* __restrict__ pidx,
                                                     int nparts, int* __restrict__ out_idx) {
+    chain_release();
+    chain_wait();
     Best m;
     m.v = -3.4e38f;
     m.i = 2147483647;
@@ -278,8 +284,8 @@ extern "C" int lt_silu_mul(const float* g, const float* u, float* y, int n, void
 
 extern "C" int lt_add(const float* a, const float* b, float* y, int n, void* stream) {
     LT_REQUIRE(a && b && y && n > 0, "lt_add: bad argument");
-    k_add<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(a, b, y, n);
-    return check_launch("lt_add");
+    const cudaError_t e = launch_chained(k_add, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, a, b, y, n);
+    return check_launch("lt_add", 1, e);
 }
 
 extern "C" int lt_rmsnorm(const float* x, const float* w, float* y, int M, int N, float eps, void* stream) {
@@ -331,9 +337,10 @@ extern "C" int lt_argmax(const float* x, int n, void* partials, int* out_idx, vo
     int* pidx = (int*)(pval + ARGMAX_BLOCKS);
     int blocks = (n + 255) / 256;
     if (blocks > ARGMAX_BLOCKS) blocks = ARGMAX_BLOCKS;
-    k_argmax_s1<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, n, pval, pidx);
-    k_argmax_s2<<<1, 256, 0, (cudaStream_t)stream>>>(pval, pidx, blocks, out_idx);
-    return check_launch("lt_argmax", 2);
+    cudaError_t e = launch_chained(k_argmax_s1, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, n, pval, pidx);
+    if (e == cudaSuccess)
+        e = launch_chained(k_argmax_s2, dim3(1), dim3(256), 0, (cudaStream_t)stream, pval, pidx, blocks, out_idx);
+    return check_launch("lt_argmax", 2, e);
 }
 
 extern "C" int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out, int E, int V,

@@ -13,6 +13,7 @@
 // exactly the lane of the contract, so the per-lane fold and the shuffle tree need no
 // re-association.  Warps walk the matrix with a grid stride sized to the SM count.
 #include "lt_common.cuh"
+#include "lt_device_ops.cuh"
 
 namespace lt {
 
@@ -101,50 +102,99 @@ k_q8_gemv(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const in
 // rows and keeps U rounds of every row's blocks in flight (R * U * 34 bytes per lane) before it
 // folds them, so short matrices are one or two round trips to memory instead of K/1024.  The
 // fold itself walks the rounds in ascending block order, the lane chain of the contract.
-template <int R, int U>
+//
+// PRO: the activation arrives as an fp32 vector and is RMS-normalised and quantised here, by every CTA
+// for itself (the arithmetic of lt_rmsnorm + lt_quant_q8), while the first rows of every warp are on their
+// way from DRAM to L2; Xq then names the fp32 vector, Xd the norm weight.
+template <int R, int U, bool PRO>
 __global__ void __launch_bounds__(GEMV_THREADS)
-k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const int8_t* __restrict__ Xq,
-           const __half* __restrict__ Xd, const float* __restrict__ Resid, float* __restrict__ Y, int M, int K) {
+k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const void* __restrict__ Xq_,
+           const void* __restrict__ Xd_, float eps, const float* __restrict__ Resid, float* __restrict__ Y, int M,
+           int K) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nb = K >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long warps_total = (long)gridDim.x * GEMV_WARPS;
     const long gwarp = (long)blockIdx.x * GEMV_WARPS + warp;
-    {
-        const int4* src = (const int4*)Xq;
+    int4 w0[U][R], w1[U][R];
+    unsigned short wd[U][R];
+    // the tile (rows r0 .. r0+R-1, blocks b0, b0+32, ..) of this lane
+    auto load_tile = [&](long r0, int b0) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + 32 * u;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const long row = r0 + r;
+                if (b < nb && row < M) {
+                    const int8_t* p = Wq + row * K + (long)b * 32;
+                    w0[u][r] = ld_stream_v4(p);
+                    w1[u][r] = ld_stream_v4(p + 16);
+                    wd[u][r] = ld_stream_u16(Wd + row * nb + b);
+                } else {
+                    w0[u][r] = make_int4(0, 0, 0, 0);
+                    w1[u][r] = make_int4(0, 0, 0, 0);
+                    wd[u][r] = 0;
+                }
+            }
+        }
+    };
+    // Weights do not depend on the predecessor in the stream: the first tile is requested before the wait,
+    // and the second one is pulled into L2, so the head of the weight stream overlaps the predecessor's tail
+    // (chained launch) and the activation prologue.
+    chain_release();
+    const long r_first = gwarp * R;
+    if (r_first < M) {
+        load_tile(r_first, lane);
+        long r2 = r_first;
+        int b2 = lane + 32 * U;
+        if (b2 >= nb) { r2 += warps_total * R; b2 = lane; }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+                if (b2 + 32 * u < nb && r2 + r < M)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(Wq + (r2 + r) * K + (long)(b2 + 32 * u) * 32));
+    }
+    // shared (PRO): sXq[K] | sXd[nb] (pad 16) | sred[272] | sF[K] | sW[K]
+    float* sred = (float*)(smem + (((size_t)K + nb * 2 + 15) & ~(size_t)15));
+    float* sF = sred + 272;
+    float* sW = sF + K;
+    if (PRO) {      // the norm weight is a constant of the model: on its way before the wait
+        const float* normw = (const float*)Xd_;
+        for (int c = threadIdx.x; c < (K >> 2); c += GEMV_THREADS)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(sW + c * 4)),
+                         "l"(normw + c * 4) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    chain_wait();
+    if (PRO) {
+        const float4* X4 = (const float4*)Xq_;
+        for (int c = threadIdx.x; c < (K >> 2); c += GEMV_THREADS) ((float4*)sF)[c] = X4[c];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float ss = block_rms_sumsq(sF, K, sred);
+        const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)K), eps));
+        block_quant(sF, sW, inv, K, (int8_t*)smem, (__half*)(smem + K));
+    } else {
+        const int4* src = (const int4*)Xq_;
         int4* dst = (int4*)smem;
         for (int i = threadIdx.x; i < (K >> 4); i += GEMV_THREADS) dst[i] = src[i];
         __half* dsth = (__half*)(smem + K);
+        const __half* Xd = (const __half*)Xd_;
         for (int i = threadIdx.x; i < nb; i += GEMV_THREADS) dsth[i] = Xd[i];
     }
     __syncthreads();
     const __half* xds = (const __half*)(smem + K);
 
-    for (long r0 = gwarp * R; r0 < M; r0 += warps_total * R) {
+    bool loaded = true;
+    for (long r0 = r_first; r0 < M; r0 += warps_total * R) {
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; r++) acc[r] = 0.0f;
         for (int b0 = lane; b0 < nb; b0 += 32 * U) {
-            int4 w0[U][R], w1[U][R];
-            unsigned short wd[U][R];
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int b = b0 + 32 * u;
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    const long row = r0 + r;
-                    if (b < nb && row < M) {
-                        const int8_t* p = Wq + row * K + (long)b * 32;
-                        w0[u][r] = ld_stream_v4(p);
-                        w1[u][r] = ld_stream_v4(p + 16);
-                        wd[u][r] = ld_stream_u16(Wd + row * nb + b);
-                    } else {
-                        w0[u][r] = make_int4(0, 0, 0, 0);
-                        w1[u][r] = make_int4(0, 0, 0, 0);
-                        wd[u][r] = 0;
-                    }
-                }
-            }
+            if (!loaded) load_tile(r0, b0);
+            loaded = false;
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int b = b0 + 32 * u;
@@ -248,53 +298,56 @@ static int launch_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, c
     return check_launch("lt_q8_gemv");
 }
 
-template <int R, int U>
-static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+template <int R, int U, bool PRO>
+static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, const void* Xd, float eps,
                         const float* Resid, float* Y, int M, int K, cudaStream_t s) {
     const int nb = K / 32;
-    const size_t smem = (size_t)((K + nb * 2 + 15) / 16) * 16;
+    const size_t smem = (size_t)((K + nb * 2 + 15) / 16) * 16 + (PRO ? (size_t)(272 + 2 * K) * 4 : 0);
     static bool attr_done = false;
     if (smem > 48 * 1024 && !attr_done) {
-        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done = true;
     }
     LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
     // one wave: as many CTAs as are resident at once (by this instantiation's registers and shared memory),
     // the warps loop over the rows; a multi-wave grid ends in a partly filled wave
     static int per_sm = 0, sms = 0;
-    if (per_sm == 0) {
+    static size_t per_sm_smem = 0;
+    if (per_sm == 0 || per_sm_smem != smem) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U>, GEMV_THREADS, smem) != cudaSuccess ||
-            per_sm < 1)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U, PRO>, GEMV_THREADS, smem) !=
+                cudaSuccess || per_sm < 1)
             per_sm = 1;
+        per_sm_smem = smem;
     }
     const long need = (((long)M + R - 1) / R + GEMV_WARPS - 1) / GEMV_WARPS;
     const long cap = (long)sms * per_sm;
     const int ctas = (int)(need < cap ? need : cap);
-    k_q8_gemv1<R, U><<<(unsigned)ctas, GEMV_THREADS, smem, s>>>(Wq, (const __half*)Wd, Xq, (const __half*)Xd, Resid, Y,
-                                                              M, K);
-    return check_launch("lt_q8_gemv");
+    const cudaError_t e = launch_chained(k_q8_gemv1<R, U, PRO>, dim3((unsigned)ctas), dim3(GEMV_THREADS), smem, s, Wq,
+                                         (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K);
+    return check_launch("lt_q8_gemv", 1, e);
 }
 
 // rows per warp by matrix height (enough warps to fill the GPU), rounds in flight by row length
-static int dispatch_gemv1(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
+template <bool PRO>
+static int dispatch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, const void* Xd, float eps,
                           const float* Resid, float* Y, int M, int K, cudaStream_t s) {
     const int rounds = (K / 32 + 31) / 32;
     if (M >= 32768) {
-        if (rounds >= 2) return launch_gemv1<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-        return launch_gemv1<4, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+        if (rounds >= 2) return launch_gemv1<4, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+        return launch_gemv1<4, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
     }
     if (M >= 8192) {
-        if (rounds >= 3) return launch_gemv1<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-        if (rounds == 2) return launch_gemv1<2, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-        return launch_gemv1<2, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+        if (rounds >= 3) return launch_gemv1<2, 4, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+        if (rounds == 2) return launch_gemv1<2, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+        return launch_gemv1<2, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
     }
-    if (rounds >= 5) return launch_gemv1<1, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-    if (rounds >= 3) return launch_gemv1<1, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-    if (rounds == 2) return launch_gemv1<1, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
-    return launch_gemv1<1, 1>(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    if (rounds >= 5) return launch_gemv1<1, 8, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+    if (rounds >= 3) return launch_gemv1<1, 4, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+    if (rounds == 2) return launch_gemv1<1, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+    return launch_gemv1<1, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
 }
 
 }  // namespace lt
@@ -311,7 +364,7 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
                "lt_q8_gemv: scale pointers must be 2-byte aligned");
     LT_REQUIRE(T == 1 || Resid == nullptr || Y != Resid, "lt_q8_gemv: Y may alias Resid only when T == 1");
     cudaStream_t s = (cudaStream_t)stream;
-    if (T == 1) return dispatch_gemv1(Wq, Wd, Xq, Xd, Resid, Y, M, K, s);
+    if (T == 1) return dispatch_gemv1<false>(Wq, Wd, Xq, Xd, 0.0f, Resid, Y, M, K, s);
     if (T <= 2) return launch_gemv<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 4) return launch_gemv<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 8) return launch_gemv<2, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
@@ -332,4 +385,16 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
         if (rc != LT_OK) return rc;
     }
     return LT_OK;
+}
+
+extern "C" int lt_rmsnorm_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const float* X, const float* normw, float eps,
+                                  const float* Resid, float* Y, int M, int K, void* stream) {
+    LT_REQUIRE(Wq && Wd && X && normw && Y, "lt_rmsnorm_q8_gemv: null pointer");
+    LT_REQUIRE(M > 0, "lt_rmsnorm_q8_gemv: M=%d must be positive", M);
+    LT_REQUIRE(K > 0 && K % 32 == 0, "lt_rmsnorm_q8_gemv: K=%d must be a positive multiple of 32", K);
+    LT_REQUIRE(aligned16(Wq), "lt_rmsnorm_q8_gemv: Wq must be 16-byte aligned");
+    LT_REQUIRE((reinterpret_cast<uintptr_t>(Wd) & 1u) == 0, "lt_rmsnorm_q8_gemv: Wd must be 2-byte aligned");
+    LT_REQUIRE(Y != X, "lt_rmsnorm_q8_gemv: Y must not alias X (every CTA reads all of X)");
+    LT_REQUIRE(aligned16(X) && aligned16(normw), "lt_rmsnorm_q8_gemv: X and normw must be 16-byte aligned");
+    return dispatch_gemv1<true>(Wq, Wd, X, normw, eps, Resid, Y, M, K, (cudaStream_t)stream);
 }

@@ -15,6 +15,8 @@ namespace lt {
 __global__ void k_embed_q8_rows(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd,
                                 const int* __restrict__ toks, float* __restrict__ out, int E, int V, int nrows,
                                 int* status) {
+    chain_release();
+    chain_wait();
     const int r = blockIdx.x;
     if (r >= nrows) return;
     int t = toks[r];
@@ -76,6 +78,8 @@ __global__ void k_add_len(int* len, int n, int max_seq) {
 // ------------------------------------------------------------------ silu * up -> quant, strided rows
 __global__ void k_silu_mul_quant_rows(const float* __restrict__ G, const float* __restrict__ U, int ld,
                                       int8_t* __restrict__ Xq, __half* __restrict__ Xd, int K, int rows) {
+    chain_release();
+    chain_wait();
     const int nb = K >> 5;
     const long blk = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -265,8 +269,9 @@ extern "C" int lt_embed_q8_rows(const int8_t* Wq, const uint16_t* Wd, const int*
     LT_REQUIRE(E > 0 && E % 32 == 0 && V > 0 && nrows > 0, "lt_embed_q8_rows: E=%d (multiple of 32) V=%d nrows=%d", E, V, nrows);
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_embed_q8_rows: status word unavailable");
-    k_embed_q8_rows<<<nrows, 256, 0, (cudaStream_t)stream>>>(Wq, (const __half*)Wd, toks, out, E, V, nrows, st);
-    return check_launch("lt_embed_q8_rows");
+    const cudaError_t e = launch_chained(k_embed_q8_rows, dim3(nrows), dim3(256), 0, (cudaStream_t)stream, Wq,
+                                         (const __half*)Wd, toks, out, E, V, nrows, st);
+    return check_launch("lt_embed_q8_rows", 1, e);
 }
 
 extern "C" int lt_rope_rows(float* X, int ld, const int* pos0, int nrows, int n_head, int hd, float theta,
@@ -304,9 +309,9 @@ extern "C" int lt_silu_mul_quant_rows(const float* g, const float* u, int ld, in
     LT_REQUIRE(g && u && Xq && Xd, "lt_silu_mul_quant_rows: null pointer");
     LT_REQUIRE(K > 0 && K % 32 == 0 && rows > 0 && ld >= K, "lt_silu_mul_quant_rows: K=%d rows=%d ld=%d", K, rows, ld);
     const long blocks32 = (long)rows * (K / 32);
-    k_silu_mul_quant_rows<<<(unsigned)((blocks32 + 7) / 8), 256, 0, (cudaStream_t)stream>>>(g, u, ld, Xq, (__half*)Xd, K,
-                                                                                         rows);
-    return check_launch("lt_silu_mul_quant_rows");
+    const cudaError_t e = launch_chained(k_silu_mul_quant_rows, dim3((unsigned)((blocks32 + 7) / 8)), dim3(256), 0,
+                                         (cudaStream_t)stream, g, u, ld, Xq, (__half*)Xd, K, rows);
+    return check_launch("lt_silu_mul_quant_rows", 1, e);
 }
 
 extern "C" int lt_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,

@@ -151,7 +151,8 @@ class TPDecoder:
     """
 
     def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
-                 comm="nccl", attn_split=0):
+                 comm="nccl", attn_split=0, chained=False):
+        self.chained = bool(chained)
         self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
         self.max_seq = int(max_seq); self.group = group
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -301,6 +302,16 @@ class TPDecoder:
             _lib.call("lt_rmsnorm", x.data_ptr(), w.data_ptr(), self.h.data_ptr(), B, E, eps, _stream())
             _lib.call("lt_quant_q8", self.h.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(), E, B, _stream())
 
+    def _norm_gemm(self, x, w, W, y):
+        """y = W . quant(rmsnorm(x) * w) for the B rows; one launch for a single sequence (the projection's
+        CTAs normalise and quantise the row themselves), else the quantiser launch(es) and the GEMM."""
+        if self.B == 1:
+            _lib.call("lt_rmsnorm_q8_gemv", W.q.data_ptr(), W.d.data_ptr(), x.data_ptr(), w.data_ptr(),
+                      float(self.cfg["norm_eps"]), None, y.data_ptr(), W.N, W.K, _stream())
+        else:
+            self._norm_quant(x, w)
+            self._gemm(W, y, self.B)
+
     def _allreduce(self, t):
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
@@ -322,7 +333,15 @@ class TPDecoder:
             _lib.call("lt_add", resid.data_ptr(), self.part.data_ptr(), out.data_ptr(), B * E, _stream())
 
     def step(self):
-        """One greedy decode step for the B sequences: tokens in self.tok -> next tokens in self.tok."""
+        """One greedy decode step for the B sequences: tokens in self.tok -> next tokens in self.tok.
+        With chained=True the one-sequence operators are enqueued as chained launches (lt_set_chained_launch)."""
+        prev = _lib.lib().lt_set_chained_launch(1 if self.chained else 0)
+        try:
+            self._step()
+        finally:
+            _lib.lib().lt_set_chained_launch(prev)
+
+    def _step(self):
         p, cfg, B = self.plan, self.cfg, self.B
         E, hd = p.E, p.hd
         eps, theta = float(cfg["norm_eps"]), float(cfg["rope_theta"])
@@ -332,8 +351,7 @@ class TPDecoder:
         _lib.call("lt_embed_q8_rows", self.embd.q.data_ptr(), self.embd.d.data_ptr(), self.tok.data_ptr(),
                   self.x.data_ptr(), E, p.V, B, st())
         for il, ly in enumerate(self.layers):
-            self._norm_quant(self.x, ly["attn_norm"])
-            self._gemm(ly["qkv"], self.qkv, B)
+            self._norm_gemm(self.x, ly["attn_norm"], ly["qkv"], self.qkv)
             lens = self.lens[il]
             _lib.call("lt_rope_append_batch", self.qkv.data_ptr(), qld, p.nh_l, p.nkv_l, hd, theta,
                       self.kc[il].data_ptr(), self.vc[il].data_ptr(), lens.data_ptr(), self.max_seq, B,
@@ -349,13 +367,11 @@ class TPDecoder:
                           self.vc[il].data_ptr(), lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(),
                           hd, p.nh_l, p.nkv_l, scale, self.max_seq, B, self.xq.data_ptr(), self.xd.data_ptr(), st())
             self._row_split(ly["o"], self.x, self.x1)
-            self._norm_quant(self.x1, ly["ffn_norm"])
-            self._gemm(ly["gateup"], self.gu, B)
+            self._norm_gemm(self.x1, ly["ffn_norm"], ly["gateup"], self.gu)
             _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
                       self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
             self._row_split(ly["down"], self.x1, self.x)
-        self._norm_quant(self.x, self.out_norm)
-        self._gemm(self.lm, self.logits, B)
+        self._norm_gemm(self.x, self.out_norm, self.lm, self.logits)
         nv = self.lm.N
         stride = _lib.lib().lt_argmax_scratch_bytes() // 4
         for b in range(B):

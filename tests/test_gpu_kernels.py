@@ -220,6 +220,30 @@ def test_rmsnorm_quant_equals_the_two_launches():
     assert np.array_equal(host(xq), host(xq2)) and np.array_equal(host(xd), host(xd2))
 
 
+@pytest.mark.parametrize("M,K", [(1152, 896), (9728, 896), (6144, 4096), (28672, 4096), (151936, 896), (40, 14336)])
+def test_rmsnorm_q8_gemv_equals_the_three_launches(M, K):
+    """The projection with the RMSNorm + quantiser prologue gives the bits of lt_rmsnorm, lt_quant_q8, lt_q8_gemv."""
+    rng = np.random.default_rng(M + K)
+    Wq = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    Wd = (np.abs(rng.standard_normal((M, K // 32))) * 0.02).astype(np.float16)
+    x = rng.standard_normal(K).astype(np.float32) * 2
+    w = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    res = rng.standard_normal(M).astype(np.float32)
+    dWq, dWd, dx, dw, dres = dev(Wq.reshape(-1)), dev(Wd.view(np.int16).reshape(-1)), dev(x), dev(w), dev(res)
+    h = torch.empty(K, device="cuda")
+    xq = torch.empty(K, dtype=torch.int8, device="cuda"); xd = torch.empty(K // 32, dtype=torch.int16, device="cuda")
+    y = torch.empty(M, device="cuda"); y2 = torch.empty(M, device="cuda")
+    for resid in (None, dres):
+        rp = None if resid is None else resid.data_ptr()
+        _lib.call("lt_rmsnorm", dx.data_ptr(), dw.data_ptr(), h.data_ptr(), 1, K, 1e-5, stream())
+        _lib.call("lt_quant_q8", h.data_ptr(), xq.data_ptr(), xd.data_ptr(), K, 1, stream())
+        _lib.call("lt_q8_gemv", dWq.data_ptr(), dWd.data_ptr(), xq.data_ptr(), xd.data_ptr(), rp, y.data_ptr(), M, K, 1,
+                  stream())
+        _lib.call("lt_rmsnorm_q8_gemv", dWq.data_ptr(), dWd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 1e-5, rp,
+                  y2.data_ptr(), M, K, stream())
+        assert np.array_equal(bits(host(y)), bits(host(y2)))
+
+
 @pytest.mark.parametrize("theta,hd,nh", [(1e6, 64, 16), (5e5, 128, 40)])
 def test_rope(oracle, theta, hd, nh):
     rng = np.random.default_rng(int(hd))

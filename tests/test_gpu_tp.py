@@ -69,6 +69,30 @@ def test_batch_equals_sequences_one_by_one_and_graph_equals_eager():
     assert _lib.device_status() == set()
 
 
+@pytest.mark.parametrize("attn_split", [0, 4])
+def test_chained_launches_give_the_same_bits(attn_split):
+    """One sequence, eager and from a graph: programmatic launch chaining changes when kernels start, not what
+    they compute."""
+    m = synth.make_model("tiny-llama", seed=11)
+    out = {}
+    for chained in (False, True):
+        d = tp.TPDecoder(_cfg(m), batch=1, max_seq=64, model=m, attn_split=attn_split, chained=chained)
+        d.fill_cache(7, seed=4)
+        d.set_tokens([19])
+        toks, logits = [], []
+        for _ in range(5):
+            d.step()
+            torch.cuda.synchronize()
+            toks.append(int(d.tok[0].item())); logits.append(d.logits.cpu().numpy().copy())
+        d.capture()
+        torch.cuda.synchronize()
+        more = d.run(6)
+        out[chained] = (np.array(toks), np.concatenate(logits, axis=0), more, d.logits.cpu().numpy().copy())
+    for a, b in zip(out[False], out[True]):
+        assert np.array_equal(a.view(np.int32) if a.dtype == np.float32 else a, b.view(np.int32) if b.dtype == np.float32 else b)
+    assert _lib.device_status() == set()
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 

@@ -21,7 +21,9 @@ def main():
     m = synth.make_model("tiny-llama", seed=8)
     res = {}
     for comm in ("nccl", "p2p"):
-        d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m, comm=comm)
+        # batch 2 runs the batched operators; the chained-launch form is exercised with the peer-store all-reduce
+        d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=2, max_seq=64, model=m, comm=comm,
+                         chained=(comm == "p2p"))
         d.fill_cache(6, seed=2)
         d.set_tokens([5, 600])
         toks, logits = [], []
@@ -32,8 +34,22 @@ def main():
         d.capture()
         more = d.run(3)
         res[comm] = (np.stack(toks), np.concatenate(logits, axis=0), more)
+    # one sequence: the chained one-sequence operators (fused norm + GEMV, peer-store all-reduce) against the
+    # plain launches with NCCL
+    one = {}
+    for comm in ("nccl", "p2p"):
+        d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=1, max_seq=64, model=m, comm=comm, attn_split=2,
+                         chained=(comm == "p2p"))
+        d.fill_cache(6, seed=3)
+        d.set_tokens([41])
+        d.step(); d.step()
+        torch.cuda.synchronize()
+        lg = d.logits.cpu().numpy().copy()
+        d.capture()
+        one[comm] = (lg, d.run(4))
+    one_same = all(np.array_equal(a, b) for a, b in zip(one["nccl"], one["p2p"]))
     status = _lib.device_status()
-    same = all(np.array_equal(a, b) for a, b in zip(res["nccl"], res["p2p"]))      # two ranks: one addition, same bits
+    same = one_same and all(np.array_equal(a, b) for a, b in zip(res["nccl"], res["p2p"]))      # two ranks: one addition, same bits
     toks, logits, more = res["p2p"]
     np.savez(os.path.join(out, f"rank{rank}.npz"), toks=toks, logits=logits, more=more, status=np.int32(len(status)),
              p2p_equals_nccl=np.int32(same))
