@@ -331,13 +331,22 @@ typedef struct lt_comm {
     int rank, world, max_n, max_ctas;
     float* stage[LT_COMM_MAX_RANKS];      /* stage[r]: rank r's staging buffer as mapped in this process */
     float* local_stage;
-    unsigned int* ctr;                    /* per-CTA call counters (device) */
+    unsigned int* ctr;                    /* exchange counters (device): per all-reduce CTA, then per GEMV row */
 } lt_comm;
 int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handle);
 int lt_comm_connect(lt_comm* comm, int rank, const unsigned char* all_handles);
 int lt_comm_free(lt_comm* comm);
 int lt_allreduce_add(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
                      void* stream);
+
+/* The tensor-parallel row-split projection (o_proj, down) of one sequence with the all-reduce inside the
+ * GEMV: this rank folds its K-slice of every row (lt_q8_gemv arithmetic), a warp stores each finished partial
+ * into every rank's staging memory at once and, when its rows are out, takes the partials of all ranks from
+ * its own staging memory: Y[n] = Resid[n] + ((part_0[n] + part_1[n]) + ...) in rank order, the same bits as
+ * lt_q8_gemv followed by lt_allreduce_add.  Same call sequence and the same M, K on every rank; M <= max_n of
+ * the comm; Y may alias Resid.  Bounded waits (LT_STATUS_WAIT_TIMEOUT). */
+int lt_q8_gemv_allreduce(const lt_comm* comm, const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq,
+                         const uint16_t* Xd, const float* Resid, float* Y, int M, int K, void* stream);
 
 /* ---- decode linear without caller scratch ----------------------------------------------
  * No counterpart in the reference (its engine allocates scratch with cuMemAlloc or from a

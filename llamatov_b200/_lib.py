@@ -30,6 +30,7 @@ SIGNATURES = {
     "lt_q8_gemm_ggml": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_rmsnorm": [_vp, _vp, _vp, _i, _i, _f, _vp],
     "lt_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "lt_q8_gemv_allreduce": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_rmsnorm_q8_gemv": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp],
     "lt_rope": [_vp, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],

@@ -14,6 +14,7 @@
 // re-association.  Warps walk the matrix with a grid stride sized to the SM count.
 #include "lt_common.cuh"
 #include "lt_device_ops.cuh"
+#include "lt_comm.cuh"
 
 namespace lt {
 
@@ -106,16 +107,29 @@ k_q8_gemv(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const in
 // PRO: the activation arrives as an fp32 vector and is RMS-normalised and quantised here, by every CTA
 // for itself (the arithmetic of lt_rmsnorm + lt_quant_q8), while the first rows of every warp are on their
 // way from DRAM to L2; Xq then names the fp32 vector, Xd the norm weight.
-template <int R, int U, bool PRO>
-__global__ void __launch_bounds__(GEMV_THREADS)
+//
+// Groups of R rows go to the warps with a grid stride (group cta*8 + warp, then + 8*grid): the warps of a CTA
+// read neighbouring rows and the matrix is swept front to back.  Dealing the rows so that every SM gets an
+// equal share (contiguous shares per CTA, or round-robin over CTAs first) was measured 10-20 % slower on the
+// large shapes: an SM then touches many distant pages at once.
+//
+// MODE 2 (tensor parallel, this rank holds a K-slice of the rows): the result of a row is a partial sum; the
+// warp pushes it into every rank's staging memory as soon as it is folded, and when all its rows are out it
+// takes the partials of all ranks from its own staging memory and writes
+// Y[n] = Resid[n] + ((part_0 + part_1) + ...) in rank order (lt_comm.cuh) -- the all-reduce rides in the GEMV,
+// the exchange overlaps the rest of the weight stream.
+constexpr int GEMV_PLAIN = 0, GEMV_NORM = 1, GEMV_ALLREDUCE = 2;
+template <int R, int U, int MODE>
+__global__ void __launch_bounds__(GEMV_THREADS, (R == 1 && U <= 4) ? 4 : 2)
 k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const void* __restrict__ Xq_,
            const void* __restrict__ Xd_, float eps, const float* __restrict__ Resid, float* __restrict__ Y, int M,
-           int K) {
+           int K, const CommDev C, int* status) {
+    constexpr bool PRO = MODE == GEMV_NORM;
     extern __shared__ __align__(16) unsigned char smem[];
     const int nb = K >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long warps_total = (long)gridDim.x * GEMV_WARPS;
-    const long gwarp = (long)blockIdx.x * GEMV_WARPS + warp;
+    const long groups = ((long)M + R - 1) / R;
+    const long g_step = (long)GEMV_WARPS * gridDim.x;
     int4 w0[U][R], w1[U][R];
     unsigned short wd[U][R];
     // the tile (rows r0 .. r0+R-1, blocks b0, b0+32, ..) of this lane
@@ -143,12 +157,13 @@ k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const v
     // and the second one is pulled into L2, so the head of the weight stream overlaps the predecessor's tail
     // (chained launch) and the activation prologue.
     chain_release();
-    const long r_first = gwarp * R;
-    if (r_first < M) {
+    const long g_first = (long)blockIdx.x * GEMV_WARPS + warp;
+    const long r_first = g_first * R;
+    if (g_first < groups) {
         load_tile(r_first, lane);
         long r2 = r_first;
         int b2 = lane + 32 * U;
-        if (b2 >= nb) { r2 += warps_total * R; b2 = lane; }
+        if (b2 >= nb) { r2 = (g_first + g_step) * R; b2 = lane; }
 #pragma unroll
         for (int u = 0; u < U; u++)
 #pragma unroll
@@ -186,9 +201,16 @@ k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const v
     }
     __syncthreads();
     const __half* xds = (const __half*)(smem + K);
+    const unsigned* rowctr = MODE == GEMV_ALLREDUCE ? C.ctr + C.max_ctas : nullptr;     // exchanges completed, per row
 
     bool loaded = true;
-    for (long r0 = r_first; r0 < M; r0 += warps_total * R) {
+    for (long g = g_first; g < groups; g += g_step) {
+        const long r0 = g * R;
+        unsigned number[R];
+        if (MODE == GEMV_ALLREDUCE) {     // asked for early: the answer is there when the row is folded
+#pragma unroll
+            for (int r = 0; r < R; r++) number[r] = r0 + r < M ? rowctr[r0 + r] + 1u : 0u;
+        }
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; r++) acc[r] = 0.0f;
@@ -214,8 +236,35 @@ k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const v
             float v = warp_tree_sum(acc[r]);
             const long row = r0 + r;
             if (lane == 0 && row < M) {
-                if (Resid != nullptr) v = __fadd_rn(v, Resid[row]);
-                Y[row] = v;
+                if (MODE == GEMV_ALLREDUCE) {
+                    comm_push(C, COMM_USER_GEMV, number[r], row, v);
+                } else {
+                    if (Resid != nullptr) v = __fadd_rn(v, Resid[row]);
+                    Y[row] = v;
+                }
+            }
+        }
+    }
+    if (MODE == GEMV_ALLREDUCE) {
+        // the rows of this warp, one per lane: partials of all ranks in rank order, then the residual
+        const long n_rows = g_first < groups ? ((groups - g_first + g_step - 1) / g_step) * R : 0;
+        const long long t0 = clock64();
+        for (long idx = lane; idx < n_rows; idx += 32) {
+            const long row = (g_first + (idx / R) * g_step) * R + idx % R;
+            if (row < M) {
+                const unsigned num = rowctr[row] + 1u;
+                float a = 0.0f;
+                bool ok = true;
+                for (int r = 0; r < C.world && ok; r++) {
+                    float x = 0.0f;
+                    ok = comm_take(C, COMM_USER_GEMV, num, r, row, t0, status, x);
+                    a = r == 0 ? x : __fadd_rn(a, x);
+                }
+                if (ok) {
+                    if (Resid != nullptr) a = __fadd_rn(Resid[row], a);
+                    Y[row] = a;
+                    const_cast<unsigned*>(rowctr)[row] = num;
+                }
             }
         }
     }
@@ -298,56 +347,65 @@ static int launch_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, c
     return check_launch("lt_q8_gemv");
 }
 
-template <int R, int U, bool PRO>
+template <int R, int U, int MODE>
 static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, const void* Xd, float eps,
-                        const float* Resid, float* Y, int M, int K, cudaStream_t s) {
+                        const float* Resid, float* Y, int M, int K, const CommDev& C, cudaStream_t s) {
+    constexpr bool PRO = MODE == GEMV_NORM;
     const int nb = K / 32;
     const size_t smem = (size_t)((K + nb * 2 + 15) / 16) * 16 + (PRO ? (size_t)(272 + 2 * K) * 4 : 0);
     static bool attr_done = false;
     if (smem > 48 * 1024 && !attr_done) {
-        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_done = true;
     }
     LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
-    // one wave: as many CTAs as are resident at once (by this instantiation's registers and shared memory),
-    // the warps loop over the rows; a multi-wave grid ends in a partly filled wave
+    // one wave: as many CTAs as are resident at once (by this instantiation's registers and shared memory)
     static int per_sm = 0, sms = 0;
     static size_t per_sm_smem = 0;
     if (per_sm == 0 || per_sm_smem != smem) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U, PRO>, GEMV_THREADS, smem) !=
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U, MODE>, GEMV_THREADS, smem) !=
                 cudaSuccess || per_sm < 1)
             per_sm = 1;
         per_sm_smem = smem;
     }
+    // CTAs for one round of all warps, at most the resident wave (the warps loop).  With the all-reduce
+    // epilogue every CTA must be resident (CTAs of different ranks wait on each other): never more than a wave.
     const long need = (((long)M + R - 1) / R + GEMV_WARPS - 1) / GEMV_WARPS;
     const long cap = (long)sms * per_sm;
     const int ctas = (int)(need < cap ? need : cap);
-    const cudaError_t e = launch_chained(k_q8_gemv1<R, U, PRO>, dim3((unsigned)ctas), dim3(GEMV_THREADS), smem, s, Wq,
-                                         (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K);
+    int* st = nullptr;
+    if (MODE == GEMV_ALLREDUCE) {
+        st = device_status_ptr();
+        LT_REQUIRE(st != nullptr, "lt_q8_gemv_allreduce: status word unavailable");
+    }
+    const cudaError_t e = launch_chained(k_q8_gemv1<R, U, MODE>, dim3((unsigned)ctas), dim3(GEMV_THREADS), smem, s, Wq,
+                                         (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K, C, st);
     return check_launch("lt_q8_gemv", 1, e);
 }
 
 // rows per warp by matrix height (enough warps to fill the GPU), rounds in flight by row length
-template <bool PRO>
+template <int MODE>
 static int dispatch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, const void* Xd, float eps,
-                          const float* Resid, float* Y, int M, int K, cudaStream_t s) {
+                          const float* Resid, float* Y, int M, int K, const CommDev& C, cudaStream_t s) {
     const int rounds = (K / 32 + 31) / 32;
-    if (M >= 32768) {
-        if (rounds >= 2) return launch_gemv1<4, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-        return launch_gemv1<4, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+    if (MODE != GEMV_ALLREDUCE) {
+        if (M >= 32768) {
+            if (rounds >= 2) return launch_gemv1<4, 2, MODE == GEMV_ALLREDUCE ? GEMV_PLAIN : MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+            return launch_gemv1<4, 1, MODE == GEMV_ALLREDUCE ? GEMV_PLAIN : MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+        }
+        if (M >= 8192) {
+            if (rounds >= 3) return launch_gemv1<2, 4, MODE == GEMV_ALLREDUCE ? GEMV_PLAIN : MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+            if (rounds == 2) return launch_gemv1<2, 2, MODE == GEMV_ALLREDUCE ? GEMV_PLAIN : MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+            return launch_gemv1<2, 1, MODE == GEMV_ALLREDUCE ? GEMV_PLAIN : MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+        }
     }
-    if (M >= 8192) {
-        if (rounds >= 3) return launch_gemv1<2, 4, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-        if (rounds == 2) return launch_gemv1<2, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-        return launch_gemv1<2, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-    }
-    if (rounds >= 5) return launch_gemv1<1, 8, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-    if (rounds >= 3) return launch_gemv1<1, 4, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-    if (rounds == 2) return launch_gemv1<1, 2, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
-    return launch_gemv1<1, 1, PRO>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, s);
+    if (rounds >= 5) return launch_gemv1<1, 8, MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+    if (rounds >= 3) return launch_gemv1<1, 4, MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+    if (rounds == 2) return launch_gemv1<1, 2, MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
+    return launch_gemv1<1, 1, MODE>(Wq, Wd, Xq, Xd, eps, Resid, Y, M, K, C, s);
 }
 
 }  // namespace lt
@@ -364,7 +422,7 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
                "lt_q8_gemv: scale pointers must be 2-byte aligned");
     LT_REQUIRE(T == 1 || Resid == nullptr || Y != Resid, "lt_q8_gemv: Y may alias Resid only when T == 1");
     cudaStream_t s = (cudaStream_t)stream;
-    if (T == 1) return dispatch_gemv1<false>(Wq, Wd, Xq, Xd, 0.0f, Resid, Y, M, K, s);
+    if (T == 1) return dispatch_gemv1<GEMV_PLAIN>(Wq, Wd, Xq, Xd, 0.0f, Resid, Y, M, K, CommDev{}, s);
     if (T <= 2) return launch_gemv<4, 2>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 4) return launch_gemv<2, 4>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
     if (T <= 8) return launch_gemv<2, 8>(Wq, Wd, Xq, Xd, Resid, Y, M, K, T, s);
@@ -396,5 +454,17 @@ extern "C" int lt_rmsnorm_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const fl
     LT_REQUIRE((reinterpret_cast<uintptr_t>(Wd) & 1u) == 0, "lt_rmsnorm_q8_gemv: Wd must be 2-byte aligned");
     LT_REQUIRE(Y != X, "lt_rmsnorm_q8_gemv: Y must not alias X (every CTA reads all of X)");
     LT_REQUIRE(aligned16(X) && aligned16(normw), "lt_rmsnorm_q8_gemv: X and normw must be 16-byte aligned");
-    return dispatch_gemv1<true>(Wq, Wd, X, normw, eps, Resid, Y, M, K, (cudaStream_t)stream);
+    return dispatch_gemv1<GEMV_NORM>(Wq, Wd, X, normw, eps, Resid, Y, M, K, CommDev{}, (cudaStream_t)stream);
+}
+
+extern "C" int lt_q8_gemv_allreduce(const lt_comm* comm, const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq,
+                                    const uint16_t* Xd, const float* Resid, float* Y, int M, int K, void* stream) {
+    LT_REQUIRE(comm && Wq && Wd && Xq && Xd && Y, "lt_q8_gemv_allreduce: null pointer");
+    LT_REQUIRE(comm->local_stage != nullptr && comm->world >= 1, "lt_q8_gemv_allreduce: comm is not connected");
+    LT_REQUIRE(M > 0 && M <= comm->max_n, "lt_q8_gemv_allreduce: M=%d must be positive, at most the comm's max_n=%d", M, comm->max_n);
+    LT_REQUIRE(K > 0 && K % 32 == 0, "lt_q8_gemv_allreduce: K=%d must be a positive multiple of 32", K);
+    LT_REQUIRE(aligned16(Wq) && aligned16(Xq), "lt_q8_gemv_allreduce: Wq and Xq must be 16-byte aligned");
+    LT_REQUIRE((reinterpret_cast<uintptr_t>(Wd) & 1u) == 0 && (reinterpret_cast<uintptr_t>(Xd) & 1u) == 0,
+               "lt_q8_gemv_allreduce: scale pointers must be 2-byte aligned");
+    return dispatch_gemv1<GEMV_ALLREDUCE>(Wq, Wd, Xq, Xd, 0.0f, Resid, Y, M, K, comm_dev(comm), (cudaStream_t)stream);
 }

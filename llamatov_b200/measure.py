@@ -210,7 +210,8 @@ def run_tp_decode(args):
     for B in args.batch:
         max_seq = args.ctx + args.steps + 8
         dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=args.comm,
-                            attn_split=args.attn_split, chained=bool(args.chained))
+                            attn_split=args.attn_split, chained=bool(args.chained),
+                            fused_allreduce=bool(args.fused_allreduce))
         dec.fill_cache(args.ctx, seed=1)
         start = np.random.default_rng(0).integers(0, V, size=B)
         dec.set_tokens(start)
@@ -295,6 +296,7 @@ def run_tp_decode(args):
                 "n_gpus": world, "ms_per_step": step_ms, "steps": args.steps, "warmup": args.warmup,
                 "config": {"workload": f"{args.arch} Q8_0 decode, batch {B}, context {args.ctx}, TP={world}",
                            "layers": L, "launches_per_step": launches, "comm": args.comm if world > 1 else None, "chained_launches": bool(args.chained),
+                           "allreduce_in_gemv": bool(args.fused_allreduce) and world > 1 and args.comm == "p2p" and B == 1,
                            "attention_order": f"attn_decode_split, S={args.attn_split}" if args.attn_split else "one-pass (production)"},
                 "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
                              "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
@@ -340,8 +342,12 @@ def main(argv=None):
     t.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
     t.add_argument("--attn-split", type=int, default=0,
                    help="S > 0: decode attention in the reference's declared split order with S ranges; 0: one-pass order")
-    t.add_argument("--chained", type=int, default=1,
-                   help="1: one-sequence operators as chained launches (lt_set_chained_launch); 0: ordinary launches")
+    t.add_argument("--fused-allreduce", type=int, default=1,
+                   help="comm p2p, batch 1: 1 = the row-split GEMVs exchange their partial rows themselves "
+                        "(lt_q8_gemv_allreduce); 0 = GEMV, then lt_allreduce_add")
+    t.add_argument("--chained", type=int, default=0,
+                   help="1: one-sequence operators as chained launches (lt_set_chained_launch; measured slower inside "
+                        "a captured graph); 0: ordinary launches")
     t.add_argument("--check-world1", action="store_true", help="rank 0 re-runs at world 1 and compares the tokens")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():

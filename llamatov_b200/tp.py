@@ -151,8 +151,9 @@ class TPDecoder:
     """
 
     def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
-                 comm="nccl", attn_split=0, chained=False):
+                 comm="nccl", attn_split=0, chained=False, fused_allreduce=True):
         self.chained = bool(chained)
+        self.fused_allreduce = bool(fused_allreduce)     # comm="p2p", one sequence: all-reduce inside the GEMV
         self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
         self.max_seq = int(max_seq); self.group = group
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -323,6 +324,11 @@ class TPDecoder:
         B, E = self.B, self.plan.E
         if self.world == 1:
             self._gemm(W, out, B, resid, E)
+        elif self.comm is not None and B == 1 and self.fused_allreduce:
+            # one sequence: the partial rows are exchanged by the GEMV itself
+            _lib.call("lt_q8_gemv_allreduce", ctypes.byref(self.comm.c), W.q.data_ptr(), W.d.data_ptr(),
+                      self.xq.data_ptr(), self.xd.data_ptr(), resid.data_ptr(), out.data_ptr(), W.N, W.K, _stream())
+            self.allreduce_calls += 1
         elif self.comm is not None:
             self._gemm(W, self.part, B)
             self.comm.allreduce_add(self.part, resid, out, B * E)
