@@ -120,7 +120,7 @@ k_q8_gemv(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const in
 // the exchange overlaps the rest of the weight stream.
 constexpr int GEMV_PLAIN = 0, GEMV_NORM = 1, GEMV_ALLREDUCE = 2;
 template <int R, int U, int MODE>
-__global__ void __launch_bounds__(GEMV_THREADS, (R == 1 && U <= 4) ? 4 : 2)
+__global__ void __launch_bounds__(GEMV_THREADS, (R == 1 && U <= 4) ? 4 : (R * U <= 4 ? 3 : 2))
 k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const void* __restrict__ Xq_,
            const void* __restrict__ Xd_, float eps, const float* __restrict__ Resid, float* __restrict__ Y, int M,
            int K, const CommDev C, int* status) {
