@@ -109,50 +109,67 @@ k_rope_append_batch(float* __restrict__ X, int ld, int n_qhead, int n_kvhead, in
 }
 
 // ------------------------------------------------------------------ attention, phase 1: scores
-// grid (position chunks, nkv, B); S[(b*nh + h)*s_ld + t]
+// grid (tiles of SC_PT positions, nkv, B); S[(b*nh + h)*s_ld + t].  The CTA brings its SC_PT K rows into shared
+// memory with asynchronous copies by all threads (coalesced; 16-byte chunk c of row p lands at chunk
+// c ^ (p & 7)), then a thread folds one (position, query head) score, s = fold_i fma(q[i], k[i], s), from
+// shared memory without bank conflicts.
+constexpr int SC_PT = 64;
+
+__device__ __forceinline__ void sc_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+
 __global__ void __launch_bounds__(BT)
 k_attn_scores(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const int* __restrict__ lens,
               float* __restrict__ S, int s_ld, int hd, int nh, int nkv, float scale, int max_seq, int* status) {
     chain_release();
     chain_wait();
-    extern __shared__ __align__(16) float qs[];   // [rep][hd]
+    extern __shared__ __align__(16) float sc_smem[];
     const int b = blockIdx.z, hk = blockIdx.y;
     const int rep = nh / nkv;
+    float* qs = sc_smem;                 // [rep][hd]
+    float* ks = qs + rep * hd;           // [SC_PT][hd], swizzled
     int L = lens[b];
     if (L < 0 || L > max_seq) {
         if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
         L = L < 0 ? 0 : max_seq;
     }
-    const int t = blockIdx.x * BT + threadIdx.x;
-    if (blockIdx.x * BT >= L) return;
+    const int t0 = blockIdx.x * SC_PT;
+    if (t0 >= L) return;
+    const int n = L - t0 < SC_PT ? L - t0 : SC_PT;
+    const int cpr = hd >> 2;
+    const float* Kb = K + (((long)b * max_seq + t0) * nkv + hk) * hd;
+    const long kstride = (long)nkv * hd;
+    for (int i = threadIdx.x; i < n * cpr; i += BT) {
+        const int row = i / cpr, c = i - row * cpr;
+        sc_cp_async16(ks + (size_t)row * hd + ((c ^ (row & 7)) << 2), Kb + (long)row * kstride + c * 4);
+    }
     for (int i = threadIdx.x; i < rep * hd; i += BT) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
-    if (t >= L) return;
-    const float4* Kt = (const float4*)(K + (((long)b * max_seq + t) * nkv + hk) * hd);
-    float s[MAX_REP];
+    const int p = threadIdx.x & (SC_PT - 1);
+    if (p >= n) return;
+    const float4* Kt = (const float4*)(ks + (size_t)p * hd);
+    const int sw = p & 7;
+    for (int r = threadIdx.x / SC_PT; r < rep; r += BT / SC_PT) {
+        const float4* qr = (const float4*)(qs + r * hd);
+        float s = 0.0f;
+        for (int i0 = 0; i0 < cpr; i0 += 8) {   // hd is a multiple of 32
+            float4 kk[8];
 #pragma unroll
-    for (int r = 0; r < MAX_REP; r++) s[r] = 0.0f;
-    for (int i0 = 0; i0 < (hd >> 2); i0 += 8) {   // hd is a multiple of 32: eight 16-byte loads in flight
-        float4 kk[8];
+            for (int u = 0; u < 8; u++) kk[u] = Kt[(i0 + u) ^ sw];
 #pragma unroll
-        for (int u = 0; u < 8; u++) kk[u] = Kt[i0 + u];
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-#pragma unroll
-            for (int r = 0; r < MAX_REP; r++) {
-                if (r < rep) {
-                    const float4 qq = ((const float4*)(qs + r * hd))[i0 + u];
-                    s[r] = __fmaf_rn(qq.x, kk[u].x, s[r]);
-                    s[r] = __fmaf_rn(qq.y, kk[u].y, s[r]);
-                    s[r] = __fmaf_rn(qq.z, kk[u].z, s[r]);
-                    s[r] = __fmaf_rn(qq.w, kk[u].w, s[r]);
-                }
+            for (int u = 0; u < 8; u++) {
+                const float4 qq = qr[i0 + u];
+                s = __fmaf_rn(qq.x, kk[u].x, s);
+                s = __fmaf_rn(qq.y, kk[u].y, s);
+                s = __fmaf_rn(qq.z, kk[u].z, s);
+                s = __fmaf_rn(qq.w, kk[u].w, s);
             }
         }
+        S[((long)b * nh + hk * rep + r) * s_ld + t0 + p] = __fmul_rn(s, scale);
     }
-#pragma unroll
-    for (int r = 0; r < MAX_REP; r++)
-        if (r < rep) S[((long)b * nh + hk * rep + r) * s_ld + t] = __fmul_rn(s[r], scale);
 }
 
 // ------------------------------------------------------------------ phase 2: softmax numerators and Z
@@ -211,17 +228,17 @@ k_attn_softmax(float* __restrict__ S, int s_ld, const int* __restrict__ lens, fl
 // dependent chain per output element; what can be spread is the loading: the CTA stages tiles of
 // PV_TT positions (its 32 columns of V, and the probabilities of its heads) in shared memory with
 // asynchronous copies, one tile ahead of the fold.
-constexpr int PV_TT = 128;    // positions per tile
+// PV_TT positions per tile: 128 when few CTAs stream the cache, 64 for a batch (smaller CTAs: all of them resident at once)
 // tiles in flight per CTA: 4 when few CTAs stream the cache (one sequence: each CTA's V stream is
 // latency-bound otherwise), 2 when the batch supplies CTAs enough and residency matters more
-constexpr size_t pv_smem(int stages) { return (size_t)stages * (PV_TT * 32 + MAX_REP * PV_TT) * sizeof(float); }
+constexpr size_t pv_smem(int stages, int tt) { return (size_t)stages * (tt * 32 + MAX_REP * tt) * sizeof(float); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src)
                  : "memory");
 }
 
-template <int PV_STAGES>
+template <int PV_STAGES, int PV_TT>
 __global__ void __launch_bounds__(32 * MAX_REP)
 k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, const int* __restrict__ lens,
           const float* __restrict__ Z, float* __restrict__ OUT, int out_ld, int hd, int nh, int nkv, int max_seq,
@@ -576,25 +593,27 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
     float* S = scratch;
     float* Z = scratch + (long)B * nh * s_ld;
     const int rep = nh / nkv;
+    const size_t sc_bytes = ((size_t)rep * hd + (size_t)SC_PT * hd) * sizeof(float);
+    LT_REQUIRE(sc_bytes <= 200 * 1024, "lt_attn_decode_batch: hd=%d needs %zu bytes of shared memory for a K tile", hd, sc_bytes);
     static bool attr_done = false;
     if (!attr_done) {
+        LT_CUDA(cudaFuncSetAttribute(k_attn_scores, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LT_CUDA(cudaFuncSetAttribute(k_attn_softmax, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(4)));
-        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(2)));
+        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<4, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(4, 128)));
+        LT_CUDA(cudaFuncSetAttribute(k_attn_pv<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(2, 64)));
         attr_done = true;
     }
-    cudaError_t e = launch_chained(k_attn_scores, dim3((max_seq + BT - 1) / BT, nkv, B), dim3(BT),
-                                   (size_t)rep * hd * sizeof(float), s, Q, q_ld, K, lens, S, s_ld, hd, nh, nkv, scale,
-                                   max_seq, st);
+    cudaError_t e = launch_chained(k_attn_scores, dim3((max_seq + SC_PT - 1) / SC_PT, nkv, B), dim3(BT), sc_bytes, s, Q,
+                                   q_ld, K, lens, S, s_ld, hd, nh, nkv, scale, max_seq, st);
     if (e == cudaSuccess)
         e = launch_chained(k_attn_softmax, dim3(nh, B), dim3(BT), (size_t)max_seq * sizeof(float), s, S, s_ld, lens, Z, nh,
                            max_seq);
     if (e == cudaSuccess) {
         if ((long)(hd / 32) * nkv * B >= 592)
-            e = launch_chained(k_attn_pv<2>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(2), s, S, s_ld, V, lens, Z, OUT,
+            e = launch_chained(k_attn_pv<2, 64>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(2, 64), s, S, s_ld, V, lens, Z, OUT,
                                out_ld, hd, nh, nkv, max_seq, Xq, (__half*)Xd);
         else
-            e = launch_chained(k_attn_pv<4>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(4), s, S, s_ld, V, lens, Z, OUT,
+            e = launch_chained(k_attn_pv<4, 128>, dim3(hd / 32, nkv, B), dim3(32 * rep), pv_smem(4, 128), s, S, s_ld, V, lens, Z, OUT,
                                out_ld, hd, nh, nkv, max_seq, Xq, (__half*)Xd);
     }
     return check_launch("lt_attn_decode_batch", 3, e);
