@@ -99,13 +99,26 @@ __global__ void __launch_bounds__(256) k_rmsnorm_quant(const float* __restrict__
     float ss = rms_sumsq_256(xr, N, sred);
     float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)N), eps));
     const int nb = N >> 5;
-    for (int j = threadIdx.x; j < N; j += 256) {
-        const float v = __fmul_rn(__fmul_rn(xr[j], inv), w[j]);
-        if (y != nullptr) y[(long)row * N + j] = v;
-        __half dh;
-        const int q = quant_lane(v, &dh);
-        Xq[(long)row * N + j] = (int8_t)q;
-        if ((threadIdx.x & 31) == 0) Xd[(long)row * nb + (j >> 5)] = dh;
+    for (int j0 = threadIdx.x; j0 < N; j0 += 256 * 8) {   // eight rounds of loads in flight, then their quantisers
+        float xv[8], wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int j = j0 + u * 256;
+            xv[u] = j < N ? xr[j] : 0.0f;
+            wv[u] = j < N ? w[j] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int j = j0 + u * 256;
+            if (j < N) {      // N is a multiple of 32: a warp is in or out as a whole
+                const float v = __fmul_rn(__fmul_rn(xv[u], inv), wv[u]);
+                if (y != nullptr) y[(long)row * N + j] = v;
+                __half dh;
+                const int q = quant_lane(v, &dh);
+                Xq[(long)row * N + j] = (int8_t)q;
+                if ((threadIdx.x & 31) == 0) Xd[(long)row * nb + (j >> 5)] = dh;
+            }
+        }
     }
 }
 
