@@ -880,8 +880,14 @@ class GraphRunner:
     def _launch(self, tok):
         assert self.captured, "call capture() before replay"
         row = _embedding_row(self.w, int(tok), self.E)
+        if getattr(self, "_pin_row", None) is None:     # page-locked staging: the copies below are truly asynchronous
+            self._pin_row = torch.empty(self.E, dtype=torch.float32).pin_memory()
+            self._pin_row_np = self._pin_row.numpy()
+            self._pin_idx = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._pin_idx_np = self._pin_idx.numpy()
+        np.copyto(self._pin_row_np, row)
         with torch.cuda.stream(self.stream):
-            _memcpy_htod(_RESID_IN.ptr, row, self.E * 4)
+            _memcpy_htod(_RESID_IN.ptr, self._pin_row_np, self.E * 4)
             self.graph.replay()
         for c in self.kv:
             c.length += 1
@@ -967,7 +973,9 @@ class GraphRunner:
         if not self.fused:          # the fused step already left the argmax in the buffer
             with torch.cuda.stream(self.stream):
                 argmax_dev(_LOGITS_BUF.ptr, _LOGITS_BUF.n, ab)
-        self.stream.synchronize()
-        idx = np.empty(1, np.int32)
-        _memcpy_dtoh(idx, ab, 4)
-        return int(idx[0])
+        with torch.cuda.stream(self.stream):
+            r = _rt().cudaMemcpyAsync(self._pin_idx_np.ctypes.data, _vp(ab), 4, 2, _stream())
+        if r != 0:
+            raise RuntimeError(f"cudaMemcpyAsync DtoH failed: {r}")
+        self.stream.synchronize()          # the one host wait of the step
+        return int(self._pin_idx_np[0])
