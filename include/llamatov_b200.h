@@ -304,6 +304,16 @@ long lt_attn_decode_split_scratch_floats(int nh, int hd, int nsplit, int B);
 int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* V, const int* lens, float* OUT,
                          int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq, int B,
                          int nsplit, int8_t* Xq, uint16_t* Xd, void* stream);
+/* lt_rope_append_batch followed by lt_attn_decode_split in the same two launches the attention needs anyway:
+ * X holds the rows q | k | v as the projection wrote them (ld floats apart); every CTA of the range kernel
+ * rotates its own query heads (k_rope at position lens[b]), the CTA whose range ends with the new position
+ * rotates the row's k head and appends k and v to the cache before it reads its range, and the last CTA of a
+ * sequence to finish advances lens[b].  X itself is not modified.  ticket: B ints of device scratch, zero
+ * before the first call (left zero).  Same values, cache rows and lengths as the two separate calls; a full
+ * cache sets LT_STATUS_KV_OVERFLOW and appends nothing. */
+int lt_rope_attn_decode_split(const float* X, int ld, float* K, float* V, int* lens, float* OUT, int out_ld,
+                              float* scratch, int hd, int nh, int nkv, float theta, float scale, int max_seq, int B,
+                              int nsplit, int* ticket, int8_t* Xq, uint16_t* Xd, void* stream);
 
 /* ---- parity mode: the fold order of the reference's compiled CPU path ---------------------------
  * lt_quant_q8_ggml / lt_q8_gemm_ggml reproduce bpd_quant_q8_0_cpu and bpd_qmatmul_q8_0_llamafile_cpu

@@ -49,6 +49,7 @@ SIGNATURES = {
     "lt_append_kv_batch": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "lt_attn_decode_batch": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
     "lt_attn_decode_split": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp],
+    "lt_rope_attn_decode_split": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _vp, _vp, _vp],
     "lt_rope_append_batch": [_vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp, _vp],
     "lt_comm_alloc": [_i, _i, _vp, _vp],
     "lt_comm_connect": [_vp, _i, _vp],

@@ -328,10 +328,15 @@ k_attn_pv(const float* __restrict__ P, int s_ld, const float* __restrict__ V, co
 constexpr int SPLIT_PT = 64;   // positions per staged V tile
 
 __global__ void __launch_bounds__(1024)
-k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
-             const int* __restrict__ lens, float* __restrict__ partM, float* __restrict__ partZ,
+k_attn_split(const float* Q, int q_ld, float* K, float* V,      // K, V, lens: written too when X != NULL, so no __restrict__
+             int* lens, float* __restrict__ partM, float* __restrict__ partZ,
              float* __restrict__ partO, int hd, int nh, int nkv, float scale, int max_seq, int per_max, int kstage,
-             int* status) {
+             int* status, const float* X, float theta, int* ticket) {
+    // X != NULL: the row arrives as q | k | v straight from the projection (q_ld floats apart, Q = X).  The CTA
+    // rotates its own query heads while its K rows are on the way (k_rope at position lens[b]); the CTA whose
+    // range ends with the new position rotates the row's k head and appends k and v to the cache first; the last
+    // CTA of the sequence to finish advances lens[b] (self-resetting ticket).  Same values as
+    // k_rope_append_batch followed by this kernel.
     chain_release();
     chain_wait();
     extern __shared__ __align__(16) float sp_smem[];
@@ -342,7 +347,10 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
     float* mz = red + rep * 64;          // [rep] local max
     float* sh = mz + ((rep + 3) & ~3);   // [rep][per_max] scores, then exponentials
     const int tid = threadIdx.x;
-    int L = lens[b];
+    const bool fused = X != nullptr;
+    const int L0 = lens[b];
+    const bool room = L0 >= 0 && L0 < max_seq;          // fused: the new row fits
+    int L = fused && room ? L0 + 1 : L0;
     if (L < 0 || L > max_seq) {
         if (tid == 0 && sp == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
         L = L < 0 ? 0 : max_seq;
@@ -352,6 +360,23 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
     int p1 = p0 + per;
     if (p1 > L) p1 = L;
     const int rangeN = p1 > p0 ? p1 - p0 : 0;
+    if (fused && room && L0 >= p0 && L0 < p1) {     // this CTA's range ends with the new position: append it first
+        const int half = hd >> 1;
+        const float* xr = X + (long)b * q_ld;
+        const float* ksrc = xr + (long)nh * hd + (long)hk * hd;
+        const float* vsrc = xr + (long)(nh + nkv) * hd + (long)hk * hd;
+        float* kdst = K + (((long)b * max_seq + L0) * nkv + hk) * hd;
+        float* vdst = V + (((long)b * max_seq + L0) * nkv + hk) * hd;
+        for (int j = tid; j < half; j += blockDim.x) {
+            float o1, o2;
+            rope_pair(ksrc[j], ksrc[j + half], j, hd, theta, L0, o1, o2);
+            kdst[j] = o1;
+            kdst[j + half] = o2;
+        }
+        for (int c = tid; c < hd; c += blockDim.x) vdst[c] = vsrc[c];
+        __threadfence();
+        __syncthreads();
+    }
     // Everything the CTA will read is requested at once with asynchronous copies: the K rows of the range
     // (kstage: they fit beside the rest; 16-byte chunk c of row t lands at chunk c ^ (t & 7), so that the
     // one-thread-per-position reads below are free of bank conflicts) and the first two V tiles.
@@ -382,7 +407,19 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
     asm volatile("cp.async.commit_group;" ::: "memory");
     stage(0);
     stage(1);
-    for (int i = tid; i < rep * hd; i += blockDim.x) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    if (fused) {
+        const int half = hd >> 1;
+        const float* qsrc = X + (long)b * q_ld + (long)hk * rep * hd;
+        for (int i = tid; i < rep * half; i += blockDim.x) {
+            const int r = i / half, j = i - r * half;
+            float o1, o2;
+            rope_pair(qsrc[r * hd + j], qsrc[r * hd + j + half], j, hd, theta, L0, o1, o2);
+            qs[r * hd + j] = o1;
+            qs[r * hd + j + half] = o2;
+        }
+    } else {
+        for (int i = tid; i < rep * hd; i += blockDim.x) qs[i] = Q[(long)b * q_ld + (long)hk * rep * hd + i];
+    }
     asm volatile("cp.async.wait_group 2;" ::: "memory");     // the K rows have landed (the V tiles may be in flight)
     __syncthreads();
     // scores of the range, once: s = fold_i fma(q[i], K[t, i], s), then * scale
@@ -487,6 +524,18 @@ k_attn_split(const float* __restrict__ Q, int q_ld, const float* __restrict__ K,
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (fold) partO[(((long)b * nh + hk * rep + fr) * S + sp) * hd + fd] = acc;
+    if (fused) {
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const int t = atomicAdd(&ticket[b], 1);
+            if (t == (int)(gridDim.x * gridDim.y) - 1) {
+                ticket[b] = 0;
+                if (room) lens[b] = L0 + 1;
+                else atomicOr(status, (int)LT_STATUS_KV_OVERFLOW);
+            }
+        }
+    }
 }
 
 // grid (nh, B), block hd: global max over the ranges, w = __expf(local max - global max),
@@ -623,27 +672,28 @@ extern "C" long lt_attn_decode_split_scratch_floats(int nh, int hd, int nsplit, 
     return (long)B * nh * nsplit * (2 + (long)hd);
 }
 
-extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* V, const int* lens,
-                                    float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale,
-                                    int max_seq, int B, int nsplit, int8_t* Xq, uint16_t* Xd, void* stream) {
-    LT_REQUIRE(Q && K && V && lens && OUT && scratch, "lt_attn_decode_split: null pointer");
-    LT_REQUIRE(hd > 0 && hd % 32 == 0 && hd <= 1024, "lt_attn_decode_split: hd=%d must be a multiple of 32, at most 1024", hd);
+static int attn_split_launch(const char* what, const float* Q, int q_ld, const float* K, const float* V, const int* lens,
+                             float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale, int max_seq,
+                             int B, int nsplit, int8_t* Xq, uint16_t* Xd, const float* X, float theta, int* ticket,
+                             void* stream) {
+    LT_REQUIRE(Q && K && V && lens && OUT && scratch, "%s: null pointer", what);
+    LT_REQUIRE(hd > 0 && hd % 32 == 0 && hd <= 1024, "%s: hd=%d must be a multiple of 32, at most 1024", what, hd);
     LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= MAX_REP,
-               "lt_attn_decode_split: nh=%d must be a multiple of nkv=%d with at most %d query heads per KV head", nh, nkv, MAX_REP);
-    LT_REQUIRE(nsplit >= 1 && nsplit <= 1024, "lt_attn_decode_split: nsplit=%d (1..1024)", nsplit);
-    LT_REQUIRE(max_seq > 0 && B > 0 && B <= 65535, "lt_attn_decode_split: max_seq=%d B=%d", max_seq, B);
-    LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_decode_split: q_ld=%d out_ld=%d", q_ld, out_ld);
-    LT_REQUIRE((Xq == nullptr) == (Xd == nullptr), "lt_attn_decode_split: Xq and Xd are given together or not at all");
-    LT_REQUIRE(Xq == nullptr || out_ld == nh * hd, "lt_attn_decode_split: the quantised output needs out_ld == nh*hd");
-    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "lt_attn_decode_split: Q, K and V must be 16-byte aligned");
+               "%s: nh=%d must be a multiple of nkv=%d with at most %d query heads per KV head", what, nh, nkv, MAX_REP);
+    LT_REQUIRE(nsplit >= 1 && nsplit <= 1024, "%s: nsplit=%d (1..1024)", what, nsplit);
+    LT_REQUIRE(max_seq > 0 && B > 0 && B <= 65535, "%s: max_seq=%d B=%d", what, max_seq, B);
+    LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "%s: q_ld=%d out_ld=%d", what, q_ld, out_ld);
+    LT_REQUIRE((Xq == nullptr) == (Xd == nullptr), "%s: Xq and Xd are given together or not at all", what);
+    LT_REQUIRE(Xq == nullptr || out_ld == nh * hd, "%s: the quantised output needs out_ld == nh*hd", what);
+    LT_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "%s: Q, K and V must be 16-byte aligned", what);
     int* st = device_status_ptr();
-    LT_REQUIRE(st != nullptr, "lt_attn_decode_split: status word unavailable");
+    LT_REQUIRE(st != nullptr, "%s: status word unavailable", what);
     cudaStream_t s = (cudaStream_t)stream;
     const int rep = nh / nkv;
     const int per_max = (((max_seq + nsplit - 1) / nsplit) + 3) & ~3;
     size_t smem = ((size_t)rep * hd + rep * 64 + ((rep + 3) & ~3) + (size_t)rep * per_max + 2 * (size_t)SPLIT_PT * hd) *
                   sizeof(float);
-    LT_REQUIRE(smem <= 200 * 1024, "lt_attn_decode_split: max_seq=%d / nsplit=%d needs %zu bytes of shared memory", max_seq, nsplit, smem);
+    LT_REQUIRE(smem <= 200 * 1024, "%s: max_seq=%d / nsplit=%d needs %zu bytes of shared memory", what, max_seq, nsplit, smem);
     // the K rows of a range are staged in shared memory too when they fit beside the rest
     const size_t kbytes = (size_t)per_max * hd * sizeof(float);
     const int kstage = smem + kbytes <= 227 * 1024 ? 1 : 0;
@@ -659,10 +709,27 @@ extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, co
     float* partM = scratch;
     float* partZ = partM + (long)B * nh * nsplit;
     float* partO = partZ + (long)B * nh * nsplit;
-    cudaError_t e = launch_chained(k_attn_split, dim3(nsplit, nkv, B), dim3(threads), smem, s, Q, q_ld, K, V, lens, partM,
-                                   partZ, partO, hd, nh, nkv, scale, max_seq, per_max, kstage, st);
+    cudaError_t e = launch_chained(k_attn_split, dim3(nsplit, nkv, B), dim3(threads), smem, s, Q, q_ld, (float*)K, (float*)V,
+                                   (int*)lens, partM, partZ, partO, hd, nh, nkv, scale, max_seq, per_max, kstage, st, X, theta,
+                                   ticket);
     if (e == cudaSuccess)
         e = launch_chained(k_attn_split_combine, dim3(nh, B), dim3(hd), 0, s, partM, partZ, partO, OUT, out_ld, hd, nh,
                            nsplit, Xq, (__half*)Xd);
-    return check_launch("lt_attn_decode_split", 2, e);
+    return check_launch(what, 2, e);
+}
+
+extern "C" int lt_attn_decode_split(const float* Q, int q_ld, const float* K, const float* V, const int* lens,
+                                    float* OUT, int out_ld, float* scratch, int hd, int nh, int nkv, float scale,
+                                    int max_seq, int B, int nsplit, int8_t* Xq, uint16_t* Xd, void* stream) {
+    return attn_split_launch("lt_attn_decode_split", Q, q_ld, K, V, lens, OUT, out_ld, scratch, hd, nh, nkv, scale, max_seq, B,
+                             nsplit, Xq, Xd, nullptr, 0.0f, nullptr, stream);
+}
+
+extern "C" int lt_rope_attn_decode_split(const float* X, int ld, float* K, float* V, int* lens, float* OUT, int out_ld,
+                                         float* scratch, int hd, int nh, int nkv, float theta, float scale, int max_seq,
+                                         int B, int nsplit, int* ticket, int8_t* Xq, uint16_t* Xd, void* stream) {
+    LT_REQUIRE(X && ticket, "lt_rope_attn_decode_split: null pointer");
+    LT_REQUIRE(ld >= (nh + 2 * nkv) * hd, "lt_rope_attn_decode_split: ld=%d is shorter than a q|k|v row", ld);
+    return attn_split_launch("lt_rope_attn_decode_split", X, ld, K, V, lens, OUT, out_ld, scratch, hd, nh, nkv, scale, max_seq,
+                             B, nsplit, Xq, Xd, X, theta, ticket, stream);
 }

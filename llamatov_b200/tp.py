@@ -153,6 +153,7 @@ class TPDecoder:
     def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
                  comm="nccl", attn_split=0, chained=False, fused_allreduce=True):
         self.chained = bool(chained)
+        self.fused_rope = True            # split order: rope + append inside the range kernel
         self.fused_allreduce = bool(fused_allreduce)     # comm="p2p", one sequence: all-reduce inside the GEMV
         self.cfg = dict(cfg); self.rank = rank; self.world = world; self.B = int(batch)
         self.max_seq = int(max_seq); self.group = group
@@ -359,6 +360,18 @@ class TPDecoder:
         for il, ly in enumerate(self.layers):
             self._norm_gemm(self.x, ly["attn_norm"], ly["qkv"], self.qkv)
             lens = self.lens[il]
+            if self.attn_split > 0 and self.fused_rope:
+                # rope, append and the attention ranges in one launch; the quantised output from the combine
+                _lib.call("lt_rope_attn_decode_split", self.qkv.data_ptr(), qld, self.kc[il].data_ptr(),
+                          self.vc[il].data_ptr(), lens.data_ptr(), self.att.data_ptr(), p.nq_l, self.scratch.data_ptr(),
+                          hd, p.nh_l, p.nkv_l, theta, scale, self.max_seq, B, self.attn_split, self.ticket.data_ptr(),
+                          self.xq.data_ptr(), self.xd.data_ptr(), st())
+                self._row_split(ly["o"], self.x, self.x1)
+                self._norm_gemm(self.x1, ly["ffn_norm"], ly["gateup"], self.gu)
+                _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
+                          self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
+                self._row_split(ly["down"], self.x1, self.x)
+                continue
             _lib.call("lt_rope_append_batch", self.qkv.data_ptr(), qld, p.nh_l, p.nkv_l, hd, theta,
                       self.kc[il].data_ptr(), self.vc[il].data_ptr(), lens.data_ptr(), self.max_seq, B,
                       self.ticket.data_ptr(), st())

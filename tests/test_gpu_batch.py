@@ -158,3 +158,46 @@ def test_split_order_attention_vs_oracle_and_one_range_equals_frozen_order(oracl
               frozen.data_ptr(), nh * hd, scr.data_ptr(), hd, nh, nkv, scale, max_seq, B, None, None, stream())
     assert np.array_equal(bits(host(one)), bits(host(frozen)))
     assert _lib.device_status() == set()
+
+
+@pytest.mark.parametrize("hd,nh,nkv,max_seq,lens,ns", [(128, 8, 2, 300, [257, 0, 31], 4), (64, 14, 2, 96, [95, 96, 5], 3),
+                                                        (128, 32, 8, 4200, [4096], 16)])
+def test_rope_append_inside_the_split_kernel_equals_the_separate_launches(hd, nh, nkv, max_seq, lens, ns):
+    """lt_rope_attn_decode_split == lt_rope_append_batch + lt_attn_decode_split: output bits, quantised output,
+    cache rows, lengths; a full cache (length == max_seq) appends nothing and is reported."""
+    rng = np.random.default_rng(hd + nh + ns)
+    B = len(lens)
+    ld = (nh + 2 * nkv) * hd
+    theta = 5e5
+    scale = float(np.float32(hd ** -0.5))
+    X = rng.standard_normal((B, ld)).astype(np.float32)
+    K = (rng.standard_normal((B, max_seq, nkv * hd)) * 0.3).astype(np.float32)
+    V = (rng.standard_normal((B, max_seq, nkv * hd)) * 0.3).astype(np.float32)
+    res = []
+    for fused in (False, True):
+        dX, dK, dV = dev(X.reshape(-1)), dev(K.reshape(-1)), dev(V.reshape(-1))
+        dl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        ticket = torch.zeros(B, dtype=torch.int32, device="cuda")
+        out = torch.zeros(B * nh * hd, device="cuda")
+        xq = torch.zeros(B * nh * hd, dtype=torch.int8, device="cuda")
+        xd = torch.zeros(B * nh * hd // 32, dtype=torch.int16, device="cuda")
+        scr = torch.empty(_lib.lib().lt_attn_decode_split_scratch_floats(nh, hd, ns, B), device="cuda")
+        for _ in range(2):       # two steps: the second one reads the row the first one appended
+            if fused:
+                _lib.call("lt_rope_attn_decode_split", dX.data_ptr(), ld, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(),
+                          out.data_ptr(), nh * hd, scr.data_ptr(), hd, nh, nkv, theta, scale, max_seq, B, ns,
+                          ticket.data_ptr(), xq.data_ptr(), xd.data_ptr(), stream())
+            else:
+                dXw = dX.clone()
+                _lib.call("lt_rope_append_batch", dXw.data_ptr(), ld, nh, nkv, hd, theta, dK.data_ptr(), dV.data_ptr(),
+                          dl.data_ptr(), max_seq, B, ticket.data_ptr(), stream())
+                _lib.call("lt_attn_decode_split", dXw.data_ptr(), ld, dK.data_ptr(), dV.data_ptr(), dl.data_ptr(),
+                          out.data_ptr(), nh * hd, scr.data_ptr(), hd, nh, nkv, scale, max_seq, B, ns, xq.data_ptr(),
+                          xd.data_ptr(), stream())
+        torch.cuda.synchronize()
+        status = _lib.device_status()
+        res.append((bits(host(out)), host(xq), host(xd), bits(host(dK)), bits(host(dV)), host(dl), host(ticket), status))
+    for a, b in zip(res[0][:7], res[1][:7]):
+        assert np.array_equal(a, b)
+    assert res[0][7] == res[1][7]
+    assert ("kv_overflow" in res[1][7]) == any(l >= max_seq - 1 for l in lens)
