@@ -184,15 +184,18 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
         __syncthreads();
     }
 
-    // V sum: thread = (row group, output element); each V row is read once for the group's rows
-    constexpr int NG = PF_THREADS / HD;      // row groups
+    // V sum: thread = (row group, two neighbouring output elements); a V row is read once per group as 8-byte
+    // loads and serves the group's rows, so the loop is bound by its FMAs, not by loads
+    constexpr int DV = 2;
+    constexpr int TPG = HD / DV;             // threads per row group
+    constexpr int NG = PF_THREADS / TPG;     // row groups
     constexpr int RPG = (QT + NG - 1) / NG;  // rows per group
-    const int g = tid / HD, d = tid - g * HD;
-    float acc[RPG];
+    const int g = tid / TPG, d = (tid - g * TPG) * DV;
+    float2 acc[RPG];
     int Lr[RPG];
 #pragma unroll
     for (int k = 0; k < RPG; k++) {
-        acc[k] = 0.0f;
+        acc[k] = make_float2(0.0f, 0.0f);
         const int qi = g + k * NG;
         Lr[k] = qi < nq ? L0 + r0 + qi + 1 : 0;
     }
@@ -202,29 +205,38 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     const int Lcommon = (L0 + r0 + 1) & ~3;
     int t = 0;
     for (; t < Lcommon; t += 4) {
-        const float v0 = Vd[(long)t * vstride], v1 = Vd[(long)(t + 1) * vstride];
-        const float v2 = Vd[(long)(t + 2) * vstride], v3 = Vd[(long)(t + 3) * vstride];
+        const float2 v0 = *(const float2*)(Vd + (long)t * vstride), v1 = *(const float2*)(Vd + (long)(t + 1) * vstride);
+        const float2 v2 = *(const float2*)(Vd + (long)(t + 2) * vstride), v3 = *(const float2*)(Vd + (long)(t + 3) * vstride);
 #pragma unroll
         for (int k = 0; k < RPG; k++) {
-            const float4 pr = *(const float4*)(sc + (g + k * NG) * ld + t);
-            acc[k] = __fmaf_rn(pr.x, v0, acc[k]);
-            acc[k] = __fmaf_rn(pr.y, v1, acc[k]);
-            acc[k] = __fmaf_rn(pr.z, v2, acc[k]);
-            acc[k] = __fmaf_rn(pr.w, v3, acc[k]);
+            if (g + k * NG < QT) {
+                const float4 pr = *(const float4*)(sc + (g + k * NG) * ld + t);
+                acc[k].x = __fmaf_rn(pr.x, v0.x, acc[k].x); acc[k].y = __fmaf_rn(pr.x, v0.y, acc[k].y);
+                acc[k].x = __fmaf_rn(pr.y, v1.x, acc[k].x); acc[k].y = __fmaf_rn(pr.y, v1.y, acc[k].y);
+                acc[k].x = __fmaf_rn(pr.z, v2.x, acc[k].x); acc[k].y = __fmaf_rn(pr.z, v2.y, acc[k].y);
+                acc[k].x = __fmaf_rn(pr.w, v3.x, acc[k].x); acc[k].y = __fmaf_rn(pr.w, v3.y, acc[k].y);
+            }
         }
     }
     for (; t < Lmax; t++) {   // the causal edge: row by row
-        const float v = Vd[(long)t * vstride];
+        const float2 v = *(const float2*)(Vd + (long)t * vstride);
 #pragma unroll
         for (int k = 0; k < RPG; k++) {
             const int qi = g + k * NG;
-            if (t < Lr[k]) acc[k] = __fmaf_rn(sc[qi * ld + t], v, acc[k]);
+            if (t < Lr[k]) {
+                const float pr = sc[qi * ld + t];
+                acc[k].x = __fmaf_rn(pr, v.x, acc[k].x);
+                acc[k].y = __fmaf_rn(pr, v.y, acc[k].y);
+            }
         }
     }
 #pragma unroll
     for (int k = 0; k < RPG; k++) {
         const int qi = g + k * NG;
-        if (qi < nq) OUT[(long)(r0 + qi) * out_ld + (long)h * HD + d] = __fdiv_rn(acc[k], zs[qi]);
+        if (qi < nq) {
+            const float z = zs[qi];
+            *(float2*)(OUT + (long)(r0 + qi) * out_ld + (long)h * HD + d) = make_float2(__fdiv_rn(acc[k].x, z), __fdiv_rn(acc[k].y, z));
+        }
     }
 }
 
@@ -250,7 +262,8 @@ template <int HD>
 static int pick_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
                              int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
     // query rows per tile: 8 while three CTAs of score rows fit an SM (the V sum and the softmax are
-    // chains of dependent operations, resident warps hide them), else 4; 16 only for short chunks
+    // chains of dependent operations, resident warps hide them), else 4; 16 only for short chunks (16 rows
+    // with one CTA per SM was measured 6 % slower at 2048 positions)
     const size_t per_row = (size_t)((maxt + 3) & ~3) + HD + 65;
     if (16 * per_row * sizeof(float) <= 72 * 1024)
         return launch_attn_prefill<HD, 16>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
@@ -321,6 +334,8 @@ extern "C" int lt_attn_prefill(const float* Q, int q_ld, const float* K, const f
     LT_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "lt_attn_prefill: nh=%d must be a positive multiple of nkv=%d", nh, nkv);
     LT_REQUIRE(nrows > 0 && maxt >= nrows && maxt <= 12000, "lt_attn_prefill: nrows=%d maxt=%d (maxt in nrows..12000)", nrows, maxt);
     LT_REQUIRE(q_ld >= nh * hd && out_ld >= nh * hd && q_ld % 4 == 0, "lt_attn_prefill: q_ld=%d out_ld=%d", q_ld, out_ld);
+    LT_REQUIRE(out_ld % 2 == 0 && (reinterpret_cast<uintptr_t>(OUT) & 7u) == 0 && (reinterpret_cast<uintptr_t>(V) & 7u) == 0,
+               "lt_attn_prefill: OUT and V must be 8-byte aligned, out_ld even");
     LT_REQUIRE(aligned16(Q) && aligned16(K), "lt_attn_prefill: Q and K must be 16-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return pick_attn_prefill<64>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
