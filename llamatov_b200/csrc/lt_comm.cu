@@ -28,17 +28,34 @@ k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __
     const int i = blockIdx.x * COMM_CHUNK + tid * 4;
     if (i < n) {
         const float4 v = *(const float4*)(part + i);
-        comm_push(C, U, number, i, v.x); comm_push(C, U, number, i + 1, v.y);
-        comm_push(C, U, number, i + 2, v.z); comm_push(C, U, number, i + 3, v.w);
+        {   // four tagged words as two 16-byte stores per rank (each 8-byte word still carries its own tag)
+            const long slot = comm_slot(C, U, number, C.rank, i);
+            const float tg = __uint_as_float(number);
+            const float4 w0 = make_float4(v.x, tg, v.y, tg), w1 = make_float4(v.z, tg, v.w, tg);
+            for (int r = 0; r < C.world; r++) {
+                float4* d = (float4*)(C.stage[r] + slot);
+                d[0] = w0;
+                d[1] = w1;
+            }
+        }
         float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         bool ok = true;
         const long long t0 = clock64();
         for (int r = 0; r < C.world && ok; r++) {
+            const float2* src = C.stage[C.rank] + comm_slot(C, U, number, r, i);
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                float x = 0.0f;
-                ok = ok && comm_take(C, U, number, r, i + e, t0, status, x);
-                a[e] = r == 0 ? x : __fadd_rn(a[e], x);
+            for (int e = 0; e < 4; e += 2) {      // two words per 16-byte load, both tags checked
+                float4 w = ld_volatile_f4(src + e);
+                while (__float_as_uint(w.y) != number || __float_as_uint(w.w) != number) {
+                    if (clock64() - t0 > COMM_WAIT_LIMIT) {
+                        atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    w = ld_volatile_f4(src + e);
+                }
+                a[e] = r == 0 ? w.x : __fadd_rn(a[e], w.x);
+                a[e + 1] = r == 0 ? w.z : __fadd_rn(a[e + 1], w.z);
             }
         }
         if (ok) {

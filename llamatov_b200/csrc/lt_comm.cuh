@@ -41,6 +41,12 @@ __device__ __forceinline__ float2 ld_volatile_f2(const float2* p) {
     return v;
 }
 
+__device__ __forceinline__ float4 ld_volatile_f4(const float2* p) {      // two neighbouring words, 16-byte aligned
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ long comm_slot(const CommDev& C, int user, unsigned number, int src, long i) {
     return (((long)user * 2 + (long)(number & 1u)) * C.world + src) * C.max_n + i;
 }
