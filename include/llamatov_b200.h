@@ -167,13 +167,20 @@ int lt_embed_q8(const int8_t* Wq, const uint16_t* Wd, const int* tok, float* out
  * attention -> quant -> o_proj GEMV + residual -> rmsnorm+quant -> gate|up GEMV -> silu*up
  * quant -> down GEMV + residual; then final rmsnorm+quant -> LM-head GEMV -> argmax.  The
  * arithmetic of every op is the per-op entry point's, so results are bit-identical to the
- * chain of per-op launches.  One CTA per SM, cooperative launch, weights streamed through a
- * shared-memory ring by bulk async copies; phases are chained through tagged activation words
- * in the workspaces instead of grid barriers.  Capturable.  Launches that share workspaces must
- * not overlap on the GPU.
+ * chain of per-op launches.  One CTA per SM, cooperative launch.  CTAs [0, nh) each serve one
+ * query head (its q rows and its KV group's k rows stay resident in shared memory, cached K rows
+ * in registers, cached V rows staged in shared memory: rmsnorm -> q,k -> rope -> append ->
+ * attention -> quantised head output without leaving the SM); the other CTAs own fixed row slices
+ * of the v rows, o_proj, gate|up (whole 32-row blocks), down and the LM head, streamed through a
+ * shared-memory ring by bulk async copies that run ahead of the dependency chain.  Four hand-overs
+ * per layer go through tagged 8-byte words in the workspaces (no grid barrier).  Capturable.
+ * Launches that share workspaces must not overlap on the GPU.
  *
  * All pointers are device pointers.  Each Q8_0 matrix must have a scale count (rows*K/32)
- * that is a multiple of 8 and 16-byte aligned bases.  max_seq must be a multiple of 4. */
+ * that is a multiple of 8 and 16-byte aligned bases.  Limits of this kernel: hd 32 or 64,
+ * E <= 1024, F <= 6816, nh*hd <= 3392, nh < number of SMs; lt_decode_step_supported() tells
+ * (1/0) whether a descriptor fits, lt_decode_step returns LT_ERR_UNSUPPORTED otherwise (use
+ * lt_decode_step_pdl then). */
 typedef struct lt_decode_layer {
     const float* attn_norm;    /* [E] */
     const int8_t* qkv_q;       /* [(nh+2*nkv)*hd, E] rows q|k|v */
@@ -202,28 +209,32 @@ typedef struct lt_decode_desc {
     const int8_t* emb_q;       /* [V, E] embedding table (needed when tok != NULL) */
     const uint16_t* emb_d;
     const float* x;            /* [E] input embedding row, read when tok == NULL (plain fp32, written by the host) */
-    void* ws_x;                /* tagged workspaces, 8 bytes per element {fp32 value, u32 tag}, zero before first use: [E] */
+    void* ws_x;                /* tagged workspaces, 8 bytes per element {payload, u32 tag}, zero before first use: [E] */
     void* ws_x1;               /* [E] */
-    void* ws_qkv;              /* [(nh+2*nkv)*hd] */
-    void* ws_att;              /* [nh*hd] */
-    void* ws_v;                /* [F] silu(gate)*up */
+    void* ws_qkv;              /* [(nh+2*nkv)*hd] (lt_decode_step keeps the new v row in the first nkv*hd elements) */
+    void* ws_att;              /* [nh*hd] (lt_decode_step: packed Q8_0, nh*hd/4 + nh*hd/32 elements used) */
+    void* ws_v;                /* [F] silu(gate)*up (lt_decode_step: packed Q8_0) */
     float* logits;             /* [V] */
     int* tok;                  /* device token: read at the start, overwritten with the argmax; NULL = x preloaded */
     int* out_tok;              /* argmax of the logits */
     int* history;              /* optional: history[*step] = token; *step += 1 */
     int* step;
-    unsigned int* sync;        /* [2] grid-barrier counters, zero before the first launch */
+    unsigned int* sync;        /* unused (kept for layout) */
     unsigned int* epoch;       /* [1] token counter that stamps the workspaces, zero before the first launch;
-                                  advanced by every launch (wraps after 2^32/(n_layers+1) tokens) */
+                                  advanced by every launch (wraps after 2^32/(n_layers+2) tokens) */
     float* part_val;           /* [lt_decode_num_ctas()] */
     int* part_idx;             /* [lt_decode_num_ctas()] */
     int* status;               /* device status word; NULL = the library's own */
     long long* trace;          /* optional [2][8192][2] (id, SM clock) stamps of CTA 0 and of the last CTA
                                   (diagnostics); NULL in production */
-    const lt_decode_layer* h_layers; /* HOST copy of the layer array (used by lt_decode_step_pdl) */
+    const lt_decode_layer* h_layers; /* HOST copy of the layer array (launch-time checks; walked by lt_decode_step_pdl) */
+    void* ws_part;             /* lt_decode_step: tagged workspace [2 * lt_decode_num_ctas()] for the per-CTA argmax results */
+    int poll_ns;               /* lt_decode_step: pause between two looks at words that have not arrived (0 = none) */
+    int reserved_;
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);
+int lt_decode_step_supported(const lt_decode_desc* h_desc);
 int lt_decode_num_ctas(void);
 
 /* The same step, same descriptor and bit-identical results, as a chain of fused kernels (five

@@ -58,6 +58,7 @@ SIGNATURES = {
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],
+    "lt_decode_step_supported": [_vp],
     "lt_decode_num_ctas": [],
     "lt_decode_step_pdl": [_vp, _vp],
     "lt_decode_pdl_num_parts": [],

@@ -644,13 +644,12 @@ extern "C" int lt_attn_decode_batch(const float* Q, int q_ld, const float* K, co
     const int rep = nh / nkv;
     const size_t sc_bytes = ((size_t)rep * hd + (size_t)SC_PT * hd) * sizeof(float);
     LT_REQUIRE(sc_bytes <= 200 * 1024, "lt_attn_decode_batch: hd=%d needs %zu bytes of shared memory for a K tile", hd, sc_bytes);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_attn_scores, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LT_CUDA(cudaFuncSetAttribute(k_attn_softmax, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LT_CUDA(cudaFuncSetAttribute(k_attn_pv<4, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(4, 128)));
         LT_CUDA(cudaFuncSetAttribute(k_attn_pv<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem(2, 64)));
-        attr_done = true;
     }
     cudaError_t e = launch_chained(k_attn_scores, dim3((max_seq + SC_PT - 1) / SC_PT, nkv, B), dim3(BT), sc_bytes, s, Q,
                                    q_ld, K, lens, S, s_ld, hd, nh, nkv, scale, max_seq, st);
@@ -698,10 +697,9 @@ static int attn_split_launch(const char* what, const float* Q, int q_ld, const f
     const size_t kbytes = (size_t)per_max * hd * sizeof(float);
     const int kstage = smem + kbytes <= 227 * 1024 ? 1 : 0;
     if (kstage) smem += kbytes;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr_done = true;
     }
     int threads = ((rep * hd + 31) / 32) * 32;
     if (threads < 256) threads = 256;

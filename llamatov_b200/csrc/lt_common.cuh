@@ -75,6 +75,21 @@ inline cudaError_t launch_chained(void (*kern)(P...), dim3 grid, dim3 block, siz
         }                                                                    \
     } while (0)
 
+// Per-device "done once" flags.  cudaFuncSetAttribute and occupancy are per-device properties, so a
+// launcher that caches either must key the cache by the current device (a process may drive several
+// GPUs).  first() returns true exactly once per device (racing threads may both see true: the guarded
+// calls are idempotent).
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool first() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+        if (done[dev]) return false;
+        done[dev] = true;
+        return true;
+    }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------- device helpers

@@ -510,10 +510,9 @@ static int launch(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const 
     if (rc != LT_OK) return rc;
     const size_t smem = 1024 + (size_t)C::NSTAGE * C::STAGE + 1024 + (size_t)nb * NT * 4;
     LT_REQUIRE(smem <= 220 * 1024, "lt_q8_gemm_tc: K=%d needs %zu bytes of shared memory per CTA", K, smem);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_q8_gemm_tc<NT, CB, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_done = true;
     }
     Params P;
     P.Wd = (const __half*)Wd; P.Xd = (const __half*)Xd; P.Resid = Resid; P.Y = Y;

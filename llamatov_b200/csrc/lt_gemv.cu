@@ -335,10 +335,9 @@ static int launch_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, c
     const int nb = K / 32;
     const int col_stride = ((K + nb * 2 + 15) / 16) * 16;
     const size_t smem = (size_t)col_stride * TB;
-    static bool attr_done = false;
-    if (smem > 48 * 1024 && !attr_done) {
+    static PerDeviceOnce attr_once;
+    if (smem > 48 * 1024 && attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_q8_gemv<R, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
     }
     LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
     int ctas = gemv_grid(((long)M + R - 1) / R);
@@ -353,24 +352,27 @@ static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, co
     constexpr bool PRO = MODE == GEMV_NORM;
     const int nb = K / 32;
     const size_t smem = (size_t)((K + nb * 2 + 15) / 16) * 16 + (PRO ? (size_t)(272 + 2 * K) * 4 : 0);
-    static bool attr_done = false;
-    if (smem > 48 * 1024 && !attr_done) {
+    static PerDeviceOnce attr_once;
+    if (smem > 48 * 1024 && attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_q8_gemv1<R, U, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
     }
     LT_REQUIRE(smem <= 200 * 1024, "lt_q8_gemv: K=%d needs %zu bytes of shared memory per CTA (limit 204800)", K, smem);
     // one wave: as many CTAs as are resident at once (by this instantiation's registers and shared memory)
-    static int per_sm = 0, sms = 0;
-    static size_t per_sm_smem = 0;
-    if (per_sm == 0 || per_sm_smem != smem) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_q8_gemv1<R, U, MODE>, GEMV_THREADS, smem) !=
-                cudaSuccess || per_sm < 1)
-            per_sm = 1;
-        per_sm_smem = smem;
+    // occupancy of this instantiation, cached per device and shared-memory size
+    struct Occ { int per_sm, sms; size_t smem; };
+    static Occ occ[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    Occ local = {};
+    Occ& oc = (dev >= 0 && dev < 64) ? occ[dev] : local;
+    if (oc.per_sm == 0 || oc.smem != smem) {
+        cudaDeviceGetAttribute(&oc.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&oc.per_sm, k_q8_gemv1<R, U, MODE>, GEMV_THREADS, smem) !=
+                cudaSuccess || oc.per_sm < 1)
+            oc.per_sm = 1;
+        oc.smem = smem;
     }
+    const int per_sm = oc.per_sm, sms = oc.sms;
     // CTAs for one round of all warps, at most the resident wave (the warps loop).  With the all-reduce
     // epilogue every CTA must be resident (CTAs of different ranks wait on each other): never more than a wave.
     const long need = (((long)M + R - 1) / R + GEMV_WARPS - 1) / GEMV_WARPS;

@@ -247,10 +247,9 @@ static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const f
     LT_REQUIRE(st != nullptr, "lt_attn_prefill: status word unavailable");
     const size_t smem = ((size_t)QT * HD + QT * 64 + QT + (size_t)QT * ((maxt + 3) & ~3)) * sizeof(float);
     LT_REQUIRE(smem <= 200 * 1024, "lt_attn_prefill: maxt=%d needs %zu bytes of shared memory", maxt, smem);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
         LT_CUDA(cudaFuncSetAttribute(k_attn_prefill<HD, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
     }
     dim3 grid((nrows + QT - 1) / QT, nh);
     k_attn_prefill<HD, QT><<<grid, PF_THREADS, smem, s>>>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt,

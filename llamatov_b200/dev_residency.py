@@ -708,7 +708,9 @@ def _compute_folded_logits(w, cfg, E):
 # lt_decode_step_pdl: 122 nodes) or as ONE persistent kernel ("persistent", lt_decode_step).
 # Same arithmetic, bit-identical results in every mode; the eager forward_pass_resident keeps
 # the per-op launches and is the parity baseline.
-_FUSED_STEP = "pdl"
+_FUSED_STEP = "persistent"
+# pause (ns) between two looks at hand-over words that have not arrived yet, in the one-kernel step
+_POLL_NS = 0
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -728,7 +730,7 @@ class _DecDesc(ctypes.Structure):
                [(n, ctypes.c_void_p) for n in (
                    "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "ws_x", "ws_x1", "ws_qkv", "ws_att",
                    "ws_v", "logits", "tok", "out_tok", "history", "step", "sync", "epoch", "part_val", "part_idx",
-                   "status", "trace", "h_layers")]
+                   "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("reserved_", ctypes.c_int)]
 
 
 class FusedDecodeStep:
@@ -772,6 +774,7 @@ class FusedDecodeStep:
         f32 = dict(dtype=torch.float32, device="cuda")
         # tagged workspaces: {value, tag} pairs, zero tags = "never written"
         self.ws = [torch.zeros(2 * n, **f32) for n in (E, E, nq + 2 * nk, nq, F)]
+        self.ws_part = torch.zeros(4 * nct, **f32)
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
         self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.part_val = torch.zeros(nct, **f32); self.part_idx = torch.zeros(nct, dtype=torch.int32, device="cuda")
@@ -788,8 +791,11 @@ class FusedDecodeStep:
                              None if tok_ptr is None else int(tok_ptr), _addr(out_tok),
                              None if history is None else int(history), None if step is None else int(step),
                              self.sync.data_ptr(), self.epoch.data_ptr(), self.part_val.data_ptr(),
-                             self.part_idx.data_ptr(), None, None, ctypes.addressof(self._layers_host))
+                             self.part_idx.data_ptr(), None, None, ctypes.addressof(self._layers_host),
+                             self.ws_part.data_ptr(), int(_POLL_NS), 0)
         self.mode = "persistent" if _FUSED_STEP is True else _FUSED_STEP
+        if self.mode == "persistent" and not _lib.lib().lt_decode_step_supported(ctypes.byref(self.desc)):
+            self.mode = "pdl"       # the one-kernel step keeps 2*hd rows of q|k|v resident per SM: small models only
 
     def enable_trace(self):
         """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""

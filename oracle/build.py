@@ -172,7 +172,9 @@ def build_ref(ref_root, force=False):
 
 
 def default_reference_root():
-    for cand in (os.environ.get("LLAMATOV_REFERENCE"), "/root/reference"):
+    # the LLAMATOV_REFERENCE variable, else a checkout named "reference" beside this repository
+    sibling = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
+    for cand in (os.environ.get("LLAMATOV_REFERENCE"), sibling):
         if cand and os.path.isdir(os.path.join(cand, "bpd", "lib")):
             return cand
     return None

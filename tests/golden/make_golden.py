@@ -44,8 +44,11 @@ def inputs_for_quant(rng):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("LLAMATOV_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("LLAMATOV_REFERENCE"),
+                    help="path of the reference checkout (or set LLAMATOV_REFERENCE)")
     a = ap.parse_args()
+    if not a.reference:
+        ap.error("give --reference or set LLAMATOV_REFERENCE")
     os.environ.setdefault("FACT_CUBIN_CACHE", tempfile.mkdtemp(prefix="fact_cubins_"))
     sys.path.insert(0, os.path.join(a.reference, "bpd", "lib"))
     sys.path.insert(0, os.path.join(a.reference, "bpd"))
