@@ -209,7 +209,10 @@ typedef struct lt_decode_desc {
     const int8_t* emb_q;       /* [V, E] embedding table (needed when tok != NULL) */
     const uint16_t* emb_d;
     const float* x;            /* [E] input embedding row, read when tok == NULL (plain fp32, written by the host) */
-    void* ws_x;                /* tagged workspaces, 8 bytes per element {payload, u32 tag}, zero before first use: [E] */
+    /* workspaces, 8 bytes per element, zero before first use.  lt_decode_step stores {payload, u32 tag}
+     * words and keeps R = lt_decode_ws_replicas() copies of ws_x, ws_x1, ws_att and ws_v (each SM polls
+     * one copy), so those four need R times the element counts given here. */
+    void* ws_x;                /* [E] */
     void* ws_x1;               /* [E] */
     void* ws_qkv;              /* [(nh+2*nkv)*hd] (lt_decode_step keeps the new v row in the first nkv*hd elements) */
     void* ws_att;              /* [nh*hd] (lt_decode_step: packed Q8_0, nh*hd/4 + nh*hd/32 elements used) */
@@ -229,12 +232,14 @@ typedef struct lt_decode_desc {
                                   (diagnostics); NULL in production */
     const lt_decode_layer* h_layers; /* HOST copy of the layer array (launch-time checks; walked by lt_decode_step_pdl) */
     void* ws_part;             /* lt_decode_step: tagged workspace [2 * lt_decode_num_ctas()] for the per-CTA argmax results */
-    int poll_ns;               /* lt_decode_step: pause between two looks at words that have not arrived (0 = none) */
-    int reserved_;
+    int poll_ns;               /* lt_decode_step: pause between two looks at hand-over words that have not arrived
+                                  (0 = none); with several looks in flight, their spacing */
+    int poll_looks;            /* lt_decode_step: looks in flight per waiting thread, 1..3 (0 = 1) */
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);
 int lt_decode_step_supported(const lt_decode_desc* h_desc);
+int lt_decode_ws_replicas(void);
 int lt_decode_num_ctas(void);
 
 /* The same step, same descriptor and bit-identical results, as a chain of fused kernels (five

@@ -60,6 +60,7 @@ SIGNATURES = {
     "lt_decode_step": [_vp, _vp],
     "lt_decode_step_supported": [_vp],
     "lt_decode_num_ctas": [],
+    "lt_decode_ws_replicas": [],
     "lt_decode_step_pdl": [_vp, _vp],
     "lt_decode_pdl_num_parts": [],
 }

@@ -52,7 +52,8 @@ constexpr int DEC_ILP = 4;                      // rows one warp folds together
 constexpr int DEC_MAX_LAYERS = 128;
 constexpr int DEC_XB = 4;                       // E <= 256 * DEC_XB (words of x polled per thread)
 constexpr int DEC_VB = 4;                       // F/4 + F/32 <= DEC_CTHREADS * DEC_VB
-constexpr int DEC_AB = 2;                       // nq/4 + nq/32 <= DEC_CTHREADS * DEC_AB
+constexpr int DEC_AB = 4;                       // nq/4 + nq/32 <= DEC_CTHREADS * DEC_AB
+constexpr int DEC_NREP = 32;                    // copies of every hand-over buffer (one per lane of the storing warp)
 constexpr long long DEC_WAIT_CLOCKS = 2000000000LL;   // ~1 s at 2 GHz
 constexpr long long DEC_DRAIN_CLOCKS = 4000000LL;     // ~2 ms: copies in flight after a give-up
 
@@ -101,6 +102,14 @@ __device__ __forceinline__ void st_tagged_u32(float2* p, unsigned v, unsigned ta
     __stcg(p, make_float2(__uint_as_float(v), __uint_as_float(tag)));
 }
 
+// A hand-over buffer of n words exists DEC_NREP times (replica r at g + r*n); CTA c reads replica
+// c % DEC_NREP, so that no L2 line is polled by more than a few SMs.  A warp stores one word to all
+// replicas with one instruction (lane = replica).
+__device__ __forceinline__ void st_tagged_all(float2* g, int n, int idx, unsigned payload, unsigned tag, int nrep) {
+    const int lane = threadIdx.x & 31;
+    if (lane < nrep) __stcg(g + (size_t)lane * n + idx, make_float2(__uint_as_float(payload), __uint_as_float(tag)));
+}
+
 struct Shared {
     unsigned long long full[DEC_MAX_STAGES];
     unsigned long long empty[DEC_MAX_STAGES];
@@ -108,15 +117,16 @@ struct Shared {
     unsigned long long att_done;            // attention CTA: layers finished, the big area is free for the LM ring
     float sred[256];                        // RMSNorm lane partials (the declared 256 lanes)
     float red[64], red2[64];                // softmax lane partials
-    float gate[32];                         // gate results of the current FFN block
-    float sv[2][32];                        // silu(gate)*up of the current / previous FFN block
+    float sv[2][32];                        // silu(gate)*up of the FFN blocks being folded
     float bias[256];                        // attention CTA: bias of its q rows, then of its k rows
     float qk[256];                          // attention CTA: q rows then k rows before rope
+    float vbias[64];                        // GEMV CTA: bias of its v rows
+    float vn[128];                          // attention CTA: the new v row of its group
     int lens[DEC_MAX_LAYERS];               // cache lengths at kernel entry
-    lt_decode_layer ly[2];                  // descriptor of the current and of the next layer
     float best_v[DEC_CWARPS];
     int best_i[DEC_CWARPS];
     volatile int abort_flag;
+    int nrep;                               // copies of the hand-over buffers in use (1..DEC_NREP)
 };
 
 __device__ __forceinline__ bool wait_expired(long long t0, unsigned& spins, Shared* S, int* status) {
@@ -133,7 +143,7 @@ __device__ __forceinline__ bool wait_expired(long long t0, unsigned& spins, Shar
 }
 
 // bounded wait on an mbarrier phase; returns false on expiry
-__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
+__device__ __forceinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, Shared* S, int* status) {
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity))
@@ -146,33 +156,37 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 }
 
 // Spin until every word this thread is responsible for carries the tag `want`.  The thread's
-// words are g[first + k*stride], k < B, as far as they lie below n (first < 0: none).  All
-// outstanding loads of a round are in flight together; threads spin independently (no barrier
-// inside the loop).  Returns false if the wait was given up.
-template <int B>
-__device__ __forceinline__ bool poll_words(const float2* __restrict__ g, int n, int first, int stride, unsigned want,
-                                           float2 (&v)[B], Shared* S, int* status, unsigned backoff_ns) {
-    bool have[B];
+// words are g[first + k*stride], k < nwords <= 4, as far as they lie below n (first < 0: none).
+// All outstanding loads of a look are in flight together; threads spin independently (no barrier
+// inside the loop); `pause_ns` is slept between two looks.  Returns false if the wait was given up.
+//
+// Everything in this kernel is inlined and must stay in registers: with the shared-memory carve-out
+// this kernel needs, L1 has next to nothing left, so a thread's stack (spills, arrays passed by
+// pointer to a real function) lives in L2 -- which the weight stream sweeps all the time -- and every
+// access to it is a memory round trip on the critical path.  (Measured: a few hundred bytes of stack
+// per thread made the step 1.6x slower.)
+__device__ __forceinline__ bool poll_words(const float2* __restrict__ g, int n, int first, int stride, int nwords,
+                                        unsigned want, float2* v, Shared* S, int* status, unsigned pause_ns) {
+    unsigned pending = 0;
 #pragma unroll
-    for (int k = 0; k < B; k++) {
-        have[k] = (first < 0) || (first + k * stride >= n);
+    for (int k = 0; k < 4; k++) {       // (constant indices: v stays in registers)
         v[k] = make_float2(0.0f, 0.0f);
+        if (k < nwords && first >= 0 && first + k * stride < n) pending |= 1u << k;
     }
+    if (!pending) return true;
     const long long t0 = clock64();
     unsigned spins = 0;
     for (;;) {
+        float2 w[4];
 #pragma unroll
-        for (int k = 0; k < B; k++)
-            if (!have[k]) v[k] = __ldcg(g + first + k * stride);
-        bool ok = true;
+        for (int k = 0; k < 4; k++)
+            if (pending & (1u << k)) w[k] = __ldcg(g + first + k * stride);
 #pragma unroll
-        for (int k = 0; k < B; k++) {
-            if (!have[k]) have[k] = (__float_as_uint(v[k].y) == want);
-            ok = ok && have[k];
-        }
-        if (ok) return true;
+        for (int k = 0; k < 4; k++)
+            if ((pending & (1u << k)) && __float_as_uint(w[k].y) == want) { v[k] = w[k]; pending &= ~(1u << k); }
+        if (!pending) return true;
         if (wait_expired(t0, spins, S, status)) return false;
-        if (backoff_ns) __nanosleep(backoff_ns);
+        if (pause_ns) __nanosleep(pause_ns);
     }
 }
 
@@ -210,12 +224,17 @@ __device__ __forceinline__ int rows_per_chunk(int K) {
     if (rc > DEC_CWARPS * DEC_ILP) rc = DEC_CWARPS * DEC_ILP;
     return rc < 1 ? 1 : rc;
 }
+// ... of the LM head, which is streamed for many sets: if a stage holds more than half a set of
+// DEC_CWARPS * DEC_ILP rows, half a set per stage, so that two stages give every warp DEC_ILP rows
+__device__ __forceinline__ int rows_per_chunk_lm(int K) {
+    const int rc = rows_per_chunk(K), half = DEC_CWARPS * DEC_ILP / 2;
+    return (rc > half && rc < 2 * half) ? half : rc;
+}
 
 // producer side: rows [r0, r1) of a matrix with row length K, chunk by chunk
-__device__ __forceinline__ bool produce_segment(Ring& R, const int8_t* Wq, const __half* Wd, int r0, int r1, int K,
+__device__ __forceinline__ bool produce_segment(Ring& R, const int8_t* Wq, const __half* Wd, int r0, int r1, int K, int RC,
                                                 Shared* S, int* status) {
     const int nb = K >> 5;
-    const int RC = rows_per_chunk(K);
     for (int r = r0; r < r1; r += RC) {
         const int n = (r1 - r < RC) ? (r1 - r) : RC;
         if (R.fill > 0) {
@@ -251,9 +270,10 @@ __device__ __forceinline__ void producer_drain(const Ring& R) {
     }
 }
 
-enum { EPI_V = 0, EPI_O = 1, EPI_GATE = 2, EPI_UP = 3, EPI_DOWN = 4, EPI_LOGITS = 5 };
+enum { EPI_V = 0, EPI_O = 1, EPI_DOWN = 2, EPI_LOGITS = 3 };
 
 struct EpiCtx {
+    Tracer tr;
     const lt_decode_desc* P;
     const lt_decode_layer* ly;
     Shared* S;
@@ -261,128 +281,283 @@ struct EpiCtx {
     unsigned tag;
     int pos, room;          // EPI_V: where the new cache row goes
     int nq, nk;
-    int svbuf;              // EPI_UP: which sv buffer
     float bestv;
     int besti;
 };
 
-// consumer side: fold rows [r0, r1) of a matrix with row length K against the quantised
-// activation in sXq / sXd.  A warp folds up to DEC_ILP rows together (rows warp, warp+15, ...
-// of the chunk): the block loop is outermost, so each row keeps its own ascending-block fma
-// chain and its own 5-level shuffle tree while the chains of different rows overlap.
-template <int EPI>
-__device__ __forceinline__ void consume_segment(Ring& R, const __half* Wd, int r0, int r1, int K, const int8_t* sXq,
-                                                const __half* sXd, EpiCtx& C, int* status) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nb = K >> 5;
-    const int RC = rows_per_chunk(K);
-    for (int r = r0; r < r1; r += RC) {
-        const int n = (r1 - r < RC) ? (r1 - r) : RC;
-        const bool ok = mbar_wait(&R.full[R.stage], R.fill & 1, C.S, status);
-        const unsigned char* base = R.base + (size_t)R.stage * DEC_STAGE_STRIDE;
-        const size_t doff = (size_t)(reinterpret_cast<uintptr_t>(Wd + (size_t)r * nb)) & 15;
-        const __half* wdbase = (const __half*)(base + (size_t)n * K + doff);
-        const int nv = (n - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // this warp's rows of the chunk (<= DEC_ILP)
-        if (ok && nv > 0) {
-            float acc[DEC_ILP];
+// The two 16-byte halves of lane L's 32-byte block are read in swapped order by the lanes whose
+// bit 2 is set: a quarter-warp's eight 16-byte reads then fall on all 32 banks (plain lane*32
+// addressing makes lanes L and L+4 collide).  The block dot is an integer sum: any order is exact.
+__device__ __forceinline__ int lane_swizzle() { return ((threadIdx.x >> 2) & 1) << 4; }
+
+__device__ __forceinline__ int4 lds128(unsigned addr) {
+    int4 v;
+    asm("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_half(unsigned addr) {
+    unsigned short h;
+    asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+    return __half2float(__ushort_as_half(h));
+}
+
+// rows a warp folds together: shared addresses of the quants and of the scales of each row
+template <int NR>
+struct RowSetN {
+    unsigned q[NR];
+    unsigned d[NR];
+};
+typedef RowSetN<DEC_ILP> RowSet;
+
+// Fold up to NR rows of shared memory against the quantised activation at shared addresses
+// xq / xd: lane L folds blocks L, L+32, ... in ascending order (the frozen chain), then the 5-level
+// shuffle tree; the chains of the rows overlap.  Returns in lane k (k < nv) the result of row k.
+// The first nv (warp-uniform) rows are valid.
+template <int NR>
+__device__ __forceinline__ float fold_rows(const RowSetN<NR>& rs, int nb, int nv, unsigned xq, unsigned xd) {
+    const int lane = threadIdx.x & 31;
+    const unsigned sw = (unsigned)lane_swizzle();
+    float acc[NR];
 #pragma unroll
-            for (int k = 0; k < DEC_ILP; k++) acc[k] = 0.0f;
-            for (int b = lane; b < nb; b += 32) {
-                const int4* xp = (const int4*)(sXq + b * 32);
-                const int4 x0 = xp[0], x1 = xp[1];
-                const float xd = __half2float(sXd[b]);
+    for (int k = 0; k < NR; k++) acc[k] = 0.0f;
+#pragma unroll (NR <= 4 ? 2 : 1)
+    for (int b = lane; b < nb; b += 32) {
+        const int4 x0 = lds128(xq + b * 32 + sw);
+        const int4 x1 = lds128(xq + b * 32 + (sw ^ 16u));
+        const float xs = lds_half(xd + b * 2);
 #pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) {
-                    if (k < nv) {       // warp-uniform
-                        const int i = warp + k * DEC_CWARPS;
-                        const int4* wp = (const int4*)(base + (size_t)i * K + b * 32);
-                        const int4 w0 = wp[0], w1 = wp[1];
-                        const float wd = __half2float(wdbase[(size_t)i * nb + b]);
-                        acc[k] = q8_accum(wd, xd, block_dot(w0, w1, x0, x1), acc[k]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) {
-#pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
-            }
-            float v = acc[0];       // lane k finishes row k
-#pragma unroll
-            for (int k = 1; k < DEC_ILP; k++) {
-                const float t = __shfl_sync(0xffffffffu, acc[k], 0);
-                if (lane == k) v = t;
-            }
-            if (lane < nv) {
-                const int row = r + warp + lane * DEC_CWARPS;
-                const lt_decode_desc& P = *C.P;
-                if (EPI == EPI_V) {
-                    // row of the v section: bias, hand-over to the attention CTAs, cache row
-                    const int vr = row - (C.nq + C.nk);     // index within the v section
-                    if (C.ly->qkv_bias != nullptr) v = __fadd_rn(v, __ldg(C.ly->qkv_bias + row));
-                    st_tagged((float2*)P.ws_qkv + vr, v, C.tag);
-                    if (C.room) C.ly->vcache[(size_t)C.pos * C.nk + vr] = v;
-                } else if (EPI == EPI_O) {
-                    v = __fadd_rn(v, C.resid[row]);
-                    st_tagged((float2*)P.ws_x1 + row, v, C.tag);
-                } else if (EPI == EPI_GATE) {
-                    C.S->gate[row - r0] = v;
-                } else if (EPI == EPI_UP) {
-                    C.S->sv[C.svbuf][row - r0] = silu_mul(C.S->gate[row - r0], v);
-                } else if (EPI == EPI_DOWN) {
-                    v = __fadd_rn(v, C.resid[row]);
-                    st_tagged((float2*)P.ws_x + row, v, C.tag);
-                } else {
-                    P.logits[row] = v;
-                    if (v > C.bestv || (v == C.bestv && row < C.besti)) { C.bestv = v; C.besti = row; }
-                }
+        for (int k = 0; k < NR; k++) {
+            if (k < nv) {       // warp-uniform
+                const int4 w0 = lds128(rs.q[k] + b * 32 + sw);
+                const int4 w1 = lds128(rs.q[k] + b * 32 + (sw ^ 16u));
+                const float wd = lds_half(rs.d[k] + b * 2);
+                acc[k] = q8_accum(wd, xs, block_dot(w0, w1, x0, x1), acc[k]);
             }
         }
-        __syncwarp();
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+#pragma unroll
+        for (int k = 0; k < NR; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
+    }
+    float v = acc[0];       // lane k takes row k
+#pragma unroll
+    for (int k = 1; k < NR; k++) {
+        const float t = __shfl_sync(0xffffffffu, acc[k], 0);
+        if (lane == k) v = t;
+    }
+    return v;
+}
+
+constexpr int DEC_MAXCH = 4;    // chunks of one segment that are folded together
+
+// consumer side of a segment = rows [r0, r1) of a matrix with row length K.  Up to DEC_MAXCH chunks
+// are taken together as one SET and their rows dealt to the warps (row j of the set to warp j % 15),
+// so that a short segment is one pass of all warps whatever its chunking; a warp folds up to DEC_ILP
+// rows together.  Work is split in two so that everything that does not depend on the activation
+// (waiting for the weight stages, every address, the epilogue's operand) is done BEFORE the hand-over
+// is awaited, and only the fold and the store come after it.
+struct SegPlan {
+    RowSet rs;
+    int r;          // first row of the set
+    int nset, nch, nv;
+    float add;      // epilogue operand of this lane's row (bias / residual)
+    bool ok;
+};
+
+__device__ __forceinline__ SegPlan seg_prepare(int epi, const Ring& R, const __half* Wd, int r0, int r, int r1, int K,
+                                               int RC, EpiCtx& C) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = K >> 5;
+    SegPlan sp;
+    // the set: chunks with nset rows from row r on, at most DEC_MAXCH chunks and DEC_CWARPS * DEC_ILP rows
+    int nset = r1 - r;
+    if (nset > DEC_MAXCH * RC) nset = DEC_MAXCH * RC;
+    if (nset > DEC_CWARPS * DEC_ILP) nset = (DEC_CWARPS * DEC_ILP / RC > 0 ? DEC_CWARPS * DEC_ILP / RC : 1) * RC;
+    if (nset > r1 - r) nset = r1 - r;
+    sp.r = r; sp.nset = nset;
+    sp.nch = (nset + RC - 1) / RC;
+    sp.nv = (nset - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // this warp's rows of the set (<= DEC_ILP)
+    sp.ok = true;
+    Ring R2 = R;
+    for (int c = 0; c < sp.nch; c++) {
+        sp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && sp.ok;
+        const int rc0 = r + c * RC;
+        const int n = (r + nset - rc0 < RC) ? (r + nset - rc0) : RC;
+        const unsigned cb = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
+        const unsigned cd = cb + (unsigned)(n * K) + (unsigned)(reinterpret_cast<uintptr_t>(Wd + (size_t)rc0 * nb) & 15);
+#pragma unroll
+        for (int k = 0; k < DEC_ILP; k++) {
+            const int i = warp + k * DEC_CWARPS - c * RC;       // row k of this warp, relative to chunk c
+            if (c == 0) { sp.rs.q[k] = cb; sp.rs.d[k] = cd; }   // (unused slots point at valid memory)
+            if (i >= 0 && i < n) {
+                sp.rs.q[k] = cb + (unsigned)(i * K);
+                sp.rs.d[k] = cd + (unsigned)(i * nb * 2);
+            }
+        }
+        R2.advance();
+    }
+    sp.add = 0.0f;
+    if (lane < sp.nv) {
+        const int row = r + warp + lane * DEC_CWARPS;
+        if (epi == EPI_V) { if (C.ly->qkv_bias != nullptr) sp.add = __ldg(C.ly->qkv_bias + row); }
+        else if (epi == EPI_O || epi == EPI_DOWN) sp.add = C.resid[row];
+    }
+    return sp;
+}
+
+__device__ __forceinline__ void seg_finish(int epi, const SegPlan& sp, Ring& R, int K, const int8_t* sXq, const __half* sXd,
+                                           EpiCtx& C) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const lt_decode_desc& P = *C.P;
+    float v = 0.0f;
+    if (sp.ok && sp.nv > 0) v = fold_rows<DEC_ILP>(sp.rs, K >> 5, sp.nv, smem_u32(sXq), smem_u32(sXd));
+    // the stages are no longer read: hand them back before the epilogue
+    __syncwarp();
+    for (int c = 0; c < sp.nch; c++) {
         if (lane == 0) mbar_arrive(&R.empty[R.stage]);
         R.advance();
     }
+    if (sp.ok && sp.nv > 0) {
+        const int row = sp.r + warp + lane * DEC_CWARPS;       // lanes < nv
+        if (epi == EPI_V) {
+            // row of the v section: bias, hand-over to the attention CTAs of its KV group, cache row
+            if (lane < sp.nv) {
+                const int vr = row - (C.nq + C.nk);     // index within the v section
+                if (C.ly->qkv_bias != nullptr) v = __fadd_rn(v, sp.add);
+                st_tagged((float2*)P.ws_qkv + vr, v, C.tag);
+                if (C.room) C.ly->vcache[(size_t)C.pos * C.nk + vr] = v;
+            }
+        } else if (epi == EPI_O || epi == EPI_DOWN) {
+            // residual add, then the lanes store the row's word to the copies of the buffer
+            v = __fadd_rn(v, sp.add);
+            float2* g = (float2*)(epi == EPI_O ? P.ws_x1 : P.ws_x);
+            for (int k = 0; k < sp.nv; k++) {
+                const float vk = __shfl_sync(0xffffffffu, v, k);
+                st_tagged_all(g, P.E, sp.r + warp + k * DEC_CWARPS, __float_as_uint(vk), C.tag, C.S->nrep);
+            }
+        } else {
+            if (lane < sp.nv) {
+                P.logits[row] = v;
+                if (v > C.bestv || (v == C.bestv && row < C.besti)) { C.bestv = v; C.besti = row; }
+            }
+        }
+    }
+}
+
+// one warp: quantise the 32-block whose lane values are `val` and publish it packed at block index b
+// of a vector of n elements, in every copy of the buffer (nw = n/4 + n/32 words per copy)
+__device__ __forceinline__ void publish_block_q8(float2* g, int n, int b, float val, unsigned tag, int nrep) {
+    const int nw = (n >> 2) + (n >> 5);
+    __half dh;
+    const unsigned q = (unsigned)quant_lane(val, &dh) & 0xffu;
+    unsigned w = q;
+    w |= __shfl_down_sync(0xffffffffu, q, 1) << 8;
+    w |= __shfl_down_sync(0xffffffffu, q, 2) << 16;
+    w |= __shfl_down_sync(0xffffffffu, q, 3) << 24;
+    for (int i = 0; i < 8; i++) {
+        const unsigned wi = __shfl_sync(0xffffffffu, w, 4 * i);
+        st_tagged_all(g, nw, b * 8 + i, wi, tag, nrep);
+    }
+    st_tagged_all(g, nw, (n >> 2) + b, (unsigned)__half_as_ushort(dh), tag, nrep);
+}
+
+// gate|up of up to two whole 32-row FFN blocks [b, b + nbk): the gate chunk and the up chunk of every
+// block are awaited together (before the activation is); a warp folds gate row i and up row i of two
+// rows of a block side by side (rows i = warp, warp+15; warps 0 and 1 then rows 30 and 31), forms
+// silu(gate)*up where both results land, and the blocks are then quantised and published by one warp each.
+struct FfnPlan {
+    unsigned cbase[4], cwd[4];      // shared addresses of the chunks: gate, up of block b, gate, up of block b+1
+    bool ok;
+};
+
+__device__ __forceinline__ FfnPlan ffn_prepare(const Ring& R, const __half* Wd, int F, int b, int nbk, int E, EpiCtx& C) {
+    const int nb = E >> 5;
+    FfnPlan fp;
+    fp.ok = true;
+    Ring R2 = R;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        fp.cbase[c] = 0; fp.cwd[c] = 0;
+        if (c < 2 * nbk) {
+            fp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && fp.ok;
+            const int row0 = ((c & 1) ? F : 0) + (b + (c >> 1)) * 32;      // gate chunk, then up chunk of a block
+            fp.cbase[c] = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
+            fp.cwd[c] = fp.cbase[c] + (unsigned)(32 * E) + (unsigned)(reinterpret_cast<uintptr_t>(Wd + (size_t)row0 * nb) & 15);
+            R2.advance();
+        }
+    }
+    return fp;
+}
+
+__device__ __forceinline__ void ffn_finish(const FfnPlan& fp, Ring& R, int F, int b, int nbk, bool more, int E,
+                                           const int8_t* sXq, const __half* sXd, EpiCtx& C) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = E >> 5;
+    const unsigned xq = smem_u32(sXq), xd = smem_u32(sXd);
+    const int items = (32 - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // rows of a block this warp folds: 3 for warps 0 and 1, else 2
+    for (int bi = 0; bi < nbk && fp.ok; bi++) {
+        const unsigned gq = bi ? fp.cbase[2] : fp.cbase[0], uq = bi ? fp.cbase[3] : fp.cbase[1];
+        const unsigned gd = bi ? fp.cwd[2] : fp.cwd[0], ud = bi ? fp.cwd[3] : fp.cwd[1];
+        RowSetN<6> rs;
+#pragma unroll
+        for (int k = 0; k < 6; k++) {
+            int i = warp + (k >> 1) * DEC_CWARPS;
+            if (i > 31) i = 31;
+            rs.q[k] = ((k & 1) ? uq : gq) + (unsigned)(i * E);
+            rs.d[k] = ((k & 1) ? ud : gd) + (unsigned)(i * nb * 2);
+        }
+        const float v = fold_rows<6>(rs, nb, 2 * items, xq, xd);     // lanes 2j, 2j+1: gate, up of row warp + 15 j
+        const float u = __shfl_down_sync(0xffffffffu, v, 1);
+        if (lane < 2 * items && (lane & 1) == 0) C.S->sv[bi][warp + (lane >> 1) * DEC_CWARPS] = silu_mul(v, u);
+    }
+    __syncwarp();
+    for (int c = 0; c < 2 * nbk; c++) {
+        if (lane == 0) mbar_arrive(&R.empty[R.stage]);
+        R.advance();
+    }
+    consumer_sync();
+    if (warp < nbk) publish_block_q8((float2*)C.P->ws_v, F, b + warp, C.S->sv[warp][lane], C.tag, C.S->nrep);
+    if (more) consumer_sync();      // sv is rewritten by the next group
 }
 
 // ---------------------------------------------------------------- activation prologue
-// 1/rms of the vector whose 256 declared lane partials are in sred: tree levels 128, 64, 32 in
-// registers (p[t] += p[t+128]; += p[t+64]; += p[t+32] for lane t), levels 16 .. 1 by shuffles.
-// Every warp evaluates it for itself (same operations in the same order: same bits).
-__device__ __forceinline__ float warp_inv_rms(const float* sred, int N, float eps) {
-    const int t = threadIdx.x & 31;
-    const float a = __fadd_rn(__fadd_rn(sred[t], sred[t + 128]), __fadd_rn(sred[t + 64], sred[t + 192]));
-    const float b = __fadd_rn(__fadd_rn(sred[t + 32], sred[t + 160]), __fadd_rn(sred[t + 96], sred[t + 224]));
-    float v = warp_tree_sum(__fadd_rn(a, b));
-    v = __shfl_sync(0xffffffffu, v, 0);
-    return rsqrtf(__fadd_rn(__fdiv_rn(v, (float)N), eps));
-}
-
-// quantise (x*inv)*w, N floats of shared memory, into sXq / sXd; the 15 consumer warps, two
-// blocks per warp together so that their dependent chains overlap
-__device__ __forceinline__ void quant_blocks(const float* sF, const float* sW, float inv, int N, int8_t* sXq, __half* sXd) {
+// quant(rmsnorm(x) * w) of the vector in sF whose 256 declared RMSNorm lane partials are in S->sred,
+// into sXq / sXd.  1/rms: tree levels 128, 64, 32 in registers (p[t] += p[t+128]; += p[t+64];
+// += p[t+32] for lane t), levels 16 .. 1 by shuffles; every warp evaluates it for itself (same
+// operations in the same order: same bits).  Then the 15 consumer warps quantise two blocks each at a
+// time so that their dependent chains overlap.
+__device__ __forceinline__ void norm_quant(const float* sF, const float* sW, int N, float eps, int8_t* sXq, __half* sXd,
+                                        const Shared* S) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* sred = S->sred;
+    const float a = __fadd_rn(__fadd_rn(sred[lane], sred[lane + 128]), __fadd_rn(sred[lane + 64], sred[lane + 192]));
+    const float b = __fadd_rn(__fadd_rn(sred[lane + 32], sred[lane + 160]), __fadd_rn(sred[lane + 96], sred[lane + 224]));
+    float ss = warp_tree_sum(__fadd_rn(a, b));
+    ss = __shfl_sync(0xffffffffu, ss, 0);
+    const float inv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)N), eps));
     const int nblk = N >> 5;
     for (int b0 = warp; b0 < nblk; b0 += 2 * DEC_CWARPS) {
-        float v[2], a[2];
+        float v[2], m[2];
 #pragma unroll
         for (int k = 0; k < 2; k++) {
-            const int b = b0 + k * DEC_CWARPS;
-            const int j = (b < nblk ? b : b0) * 32 + lane;
+            const int bb = b0 + k * DEC_CWARPS;
+            const int j = (bb < nblk ? bb : b0) * 32 + lane;
             const float x = __fmul_rn(__fmul_rn(sF[j], inv), sW[j]);
             v[k] = x;
             // amax over the 32 lanes: bit patterns of non-negative floats order like unsigned integers
-            a[k] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(x))));
+            m[k] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(x))));
         }
 #pragma unroll
         for (int k = 0; k < 2; k++) {
-            const int b = b0 + k * DEC_CWARPS;
-            if (b < nblk) {
-                const float d = (a[k] > 0.0f) ? __fdiv_rn(a[k], 127.0f) : 1.0f;
+            const int bb = b0 + k * DEC_CWARPS;
+            if (bb < nblk) {
+                const float d = (m[k] > 0.0f) ? __fdiv_rn(m[k], 127.0f) : 1.0f;
                 const __half dh = __float2half_rn(d);
                 int q = (int)rintf(__fdiv_rn(v[k], __half2float(dh)));
                 q = q < -127 ? -127 : (q > 127 ? 127 : q);
-                sXq[b * 32 + lane] = (int8_t)q;
-                if (lane == 0) sXd[b] = dh;
+                sXq[bb * 32 + lane] = (int8_t)q;
+                if (lane == 0) sXd[bb] = dh;
             }
         }
     }
@@ -392,15 +567,15 @@ __device__ __forceinline__ void quant_blocks(const float* sF, const float* sW, f
 // p_t = fold_{j = t, t+256, ...} fma(x_j, x_j, .) formed by the thread that fetched them.
 // from_smem: x is already in sF (first layer: embedding row), only the partials are formed.
 __device__ __forceinline__ void fetch_x(const float2* g, unsigned want, bool from_smem, float* sF, int E, Shared* S,
-                                        int* status, unsigned backoff_ns) {
+                                     int* status, unsigned pause_ns) {
     const int t = threadIdx.x;
     if (t < 256) {
         float p = 0.0f;
         if (from_smem) {
             for (int j = t; j < E; j += 256) p = __fmaf_rn(sF[j], sF[j], p);
         } else {
-            float2 v[DEC_XB];
-            poll_words<DEC_XB>(g, E, t, 256, want, v, S, status, backoff_ns);
+            float2 v[4];
+            poll_words(g + (size_t)(blockIdx.x % S->nrep) * E, E, t, 256, DEC_XB, want, v, S, status, pause_ns);
 #pragma unroll
             for (int k = 0; k < DEC_XB; k++) {
                 const int j = t + k * 256;
@@ -412,32 +587,17 @@ __device__ __forceinline__ void fetch_x(const float2* g, unsigned want, bool fro
 }
 
 // a packed quantised vector (n/4 words of 4 int8, then n/32 words of one fp16 scale) -> sXq / sXd
-template <int B>
-__device__ __forceinline__ void fetch_q8(const float2* g, unsigned want, int n, int8_t* sXq, __half* sXd, Shared* S,
-                                         int* status, unsigned backoff_ns) {
+__device__ __forceinline__ void fetch_q8(const float2* g, unsigned want, int n, int8_t* sXq, __half* sXd, Shared* S, int* status,
+                                      unsigned pause_ns) {
     const int nw = (n >> 2) + (n >> 5);
-    float2 v[B];
-    poll_words<B>(g, nw, threadIdx.x, DEC_CTHREADS, want, v, S, status, backoff_ns);
+    float2 v[4];
+    poll_words(g + (size_t)(blockIdx.x % S->nrep) * nw, nw, threadIdx.x, DEC_CTHREADS, 4, want, v, S, status, pause_ns);
 #pragma unroll
-    for (int k = 0; k < B; k++) {
+    for (int k = 0; k < 4; k++) {
         const int i = threadIdx.x + k * DEC_CTHREADS;
         if (i < (n >> 2)) ((unsigned*)sXq)[i] = __float_as_uint(v[k].x);
         else if (i < nw) sXd[i - (n >> 2)] = __ushort_as_half((unsigned short)(__float_as_uint(v[k].x) & 0xffffu));
     }
-}
-
-// one warp: quantise the 32-block whose lane values are `val` and publish it packed at block index b
-// of a vector of n elements
-__device__ __forceinline__ void publish_block_q8(float2* g, int n, int b, float val, unsigned tag) {
-    const int lane = threadIdx.x & 31;
-    __half dh;
-    const unsigned q = (unsigned)quant_lane(val, &dh) & 0xffu;
-    unsigned w = q;
-    w |= __shfl_down_sync(0xffffffffu, q, 1) << 8;
-    w |= __shfl_down_sync(0xffffffffu, q, 2) << 16;
-    w |= __shfl_down_sync(0xffffffffu, q, 3) << 24;
-    if ((lane & 3) == 0) st_tagged_u32(g + b * 8 + (lane >> 2), w, tag);
-    if (lane == 0) st_tagged_u32(g + (n >> 2) + b, (unsigned)__half_as_ushort(dh), tag);
 }
 
 struct Areas {
@@ -474,13 +634,17 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     const int vst = Lc < vcap ? Lc : vcap;   // cached V rows staged in shared memory
 
     // ---- before the layer input is awaited: everything that does not depend on it
-    float4 kr[HD4];                          // cached K row of position tid
+    // cached K rows in registers: position tid/2, the even thread holds the first half of the row,
+    // the odd thread the second half (the score's fma chain runs through the even thread, then the odd)
+    constexpr int HD8 = HD / 8;
+    constexpr int KPOS = DEC_CTHREADS / 2;   // positions held in registers
+    float4 kr[HD8];
 #pragma unroll
-    for (int i = 0; i < HD4; i++) kr[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (tid < Lc) {
-        const float4* kp = (const float4*)(ly->kcache + ((size_t)tid * nkv + hk) * HD);
+    for (int i = 0; i < HD8; i++) kr[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if ((tid >> 1) < Lc) {
+        const float4* kp = (const float4*)(ly->kcache + ((size_t)(tid >> 1) * nkv + hk) * HD) + (tid & 1) * HD8;
 #pragma unroll
-        for (int i = 0; i < HD4; i++) kr[i] = __ldcg(kp + i);
+        for (int i = 0; i < HD8; i++) kr[i] = __ldcg(kp + i);
     }
     for (int e = tid; e < vst * HD4; e += DEC_CTHREADS) {
         const int t = e / HD4, c = e - t * HD4;
@@ -492,51 +656,33 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     float rc = 1.0f, rs = 0.0f;              // rope angle of pair tid: the same for q and k
     if (tid < HALF) rope_trig(tid, HD, P.theta, pos, rc, rs);
 
+    // the head's resident q|k rows were requested a layer ago
+    const bool wok = mbar_wait(&S->wfull, (unsigned)il & 1u, S, P.status);
     // ---- layer input -> RMSNorm -> quantiser
     fetch_x((const float2*)P.ws_x, tag - 1u, il == 0, A.fa, E, S, P.status, backoff);
     consumer_sync();
     tr.stamp(11);
-    {
-        const float inv = warp_inv_rms(S->sred, E, P.eps);
-        quant_blocks(A.fa, A.w, inv, E, A.xq0, A.xd0);
-    }
+    norm_quant(A.fa, A.w, E, P.eps, A.xq0, A.xd0, S);
     consumer_sync();
+    tr.stamp(111);
     // ---- the head's q rows and its group's k rows (resident): rows warp, warp+15, ... four at a time
-    const bool wok = mbar_wait(&S->wfull, (unsigned)il & 1u, S, P.status);
     {
-        const unsigned char* wq = A.big;
-        const __half* wd = (const __half*)(A.big + (size_t)2 * HD * E);
+        const unsigned wq = smem_u32(A.big);
+        const unsigned wd = wq + (unsigned)(2 * HD * E);
         for (int i0 = warp; i0 < 2 * HD && wok; i0 += DEC_CWARPS * DEC_ILP) {
-            float acc[DEC_ILP];
+            const int left = (2 * HD - i0 + DEC_CWARPS - 1) / DEC_CWARPS;
+            const int nv = left < DEC_ILP ? left : DEC_ILP;
+            RowSet rs;
 #pragma unroll
-            for (int k = 0; k < DEC_ILP; k++) acc[k] = 0.0f;
-            for (int b = lane; b < nb; b += 32) {
-                const int4* xp = (const int4*)(A.xq0 + b * 32);
-                const int4 x0 = xp[0], x1 = xp[1];
-                const float xd = __half2float(A.xd0[b]);
-#pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) {
-                    const int i = i0 + k * DEC_CWARPS;
-                    if (i < 2 * HD) {       // warp-uniform
-                        const int4* wp = (const int4*)(wq + (size_t)i * E + b * 32);
-                        const int4 w0 = wp[0], w1 = wp[1];
-                        acc[k] = q8_accum(__half2float(wd[(size_t)i * nb + b]), xd, block_dot(w0, w1, x0, x1), acc[k]);
-                    }
-                }
+            for (int k = 0; k < DEC_ILP; k++) {
+                int i = i0 + k * DEC_CWARPS;
+                if (i >= 2 * HD) i = 2 * HD - 1;
+                rs.q[k] = wq + (unsigned)(i * E);
+                rs.d[k] = wd + (unsigned)(i * nb * 2);
             }
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) {
-#pragma unroll
-                for (int k = 0; k < DEC_ILP; k++) acc[k] = __fadd_rn(acc[k], __shfl_down_sync(0xffffffffu, acc[k], s));
-            }
-            float v = acc[0];
-#pragma unroll
-            for (int k = 1; k < DEC_ILP; k++) {
-                const float t = __shfl_sync(0xffffffffu, acc[k], 0);
-                if (lane == k) v = t;
-            }
+            float v = fold_rows<DEC_ILP>(rs, nb, nv, smem_u32(A.xq0), smem_u32(A.xd0));
             const int i = i0 + lane * DEC_CWARPS;
-            if (lane < DEC_ILP && i < 2 * HD) {
+            if (lane < nv) {
                 if (ly->qkv_bias != nullptr) v = __fadd_rn(v, S->bias[i]);
                 S->qk[i] = v;
             }
@@ -560,29 +706,34 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     }
     cp_async_wait_all();
     consumer_sync();
-    // ---- scores: thread t owns position t (cached row in registers, the new row in shared memory)
-    if (tid < L) {
+    // ---- scores: threads 2t, 2t+1 own position t (cached row in registers, the new row from shared memory)
+    {
+        const int t = tid >> 1, hf = tid & 1;
+        if (room && t == pos) {
+            const float4* k4 = (const float4*)A.kn + hf * HD8;
+#pragma unroll
+            for (int i = 0; i < HD8; i++) kr[i] = k4[i];
+        }
+        const float4* q4 = (const float4*)A.q + hf * HD8;
         float s = 0.0f;
-        const float4* q4 = (const float4*)A.q;
-        if (room && tid == pos) {
-            const float4* k4 = (const float4*)A.kn;
 #pragma unroll
-            for (int i = 0; i < HD4; i++) {
-                const float4 qq = q4[i], kk = k4[i];
-                s = __fmaf_rn(qq.x, kk.x, s); s = __fmaf_rn(qq.y, kk.y, s);
-                s = __fmaf_rn(qq.z, kk.z, s); s = __fmaf_rn(qq.w, kk.w, s);
+        for (int half = 0; half < 2; half++) {
+            if (hf == half) {
+#pragma unroll
+                for (int i = 0; i < HD8; i++) {
+                    const float4 qq = q4[i];
+                    s = __fmaf_rn(qq.x, kr[i].x, s); s = __fmaf_rn(qq.y, kr[i].y, s);
+                    s = __fmaf_rn(qq.z, kr[i].z, s); s = __fmaf_rn(qq.w, kr[i].w, s);
+                }
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < HD4; i++) {
-                const float4 qq = q4[i];
-                s = __fmaf_rn(qq.x, kr[i].x, s); s = __fmaf_rn(qq.y, kr[i].y, s);
-                s = __fmaf_rn(qq.z, kr[i].z, s); s = __fmaf_rn(qq.w, kr[i].w, s);
+            if (half == 0) {        // the odd thread continues the chain of its even neighbour
+                const float se = __shfl_sync(0xffffffffu, s, lane & ~1);
+                if (hf == 1) s = se;
             }
         }
-        A.sh[tid] = __fmul_rn(s, P.scale);
+        if (hf == 1 && t < L) A.sh[t] = __fmul_rn(s, P.scale);
     }
-    for (int t = tid + DEC_CTHREADS; t < L; t += DEC_CTHREADS) {     // contexts longer than the thread count
+    for (int t = tid + KPOS; t < L; t += DEC_CTHREADS) {     // contexts longer than the registers hold
         const float4* k4 = (room && t == pos) ? (const float4*)A.kn
                                               : (const float4*)(ly->kcache + ((size_t)t * nkv + hk) * HD);
         const float4* q4 = (const float4*)A.q;
@@ -600,6 +751,18 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     // ---- softmax in the declared 64-lane layout, V fold, quantiser: warps 0 and 1.  Positions
     // beyond L hold -1e30 / contribute exp() = +0 in the declared order: leaving them out gives
     // the same maximum and the same sums.
+    if (warp == 2) {
+        // the new v row of the group comes from the GEMV CTAs: fetched by an otherwise idle warp
+        // while warps 0 and 1 do the softmax
+        if (room) {
+            for (int j = lane; j < HD; j += 32) {
+                float2 vn[4];
+                poll_words((const float2*)P.ws_qkv, nk, hk * HD + j, 0, 1, tag, vn, S, P.status, backoff);
+                S->vn[j] = vn[0].x;
+            }
+        }
+        asm volatile("bar.sync 3, 96;" ::: "memory");
+    }
     if (tid < 64) {
         float m = -1e30f;
         for (int t = tid; t < L; t += 64) m = fmaxf(m, A.sh[t]);
@@ -620,10 +783,6 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
         Z = __shfl_sync(0xffffffffu, Z, 0);
         float out = 0.0f;
         if (tid < HD) {
-            // the new v row comes from a GEMV CTA; it was produced long before the softmax ended
-            float2 vn[1];
-            vn[0] = make_float2(0.0f, 0.0f);
-            if (room) poll_words<1>((const float2*)P.ws_qkv, nk, hk * HD + tid, 0, tag, vn, S, P.status, 0u);
             float acc = 0.0f;
 #pragma unroll 4
             for (int t = 0; t < vst; t++) acc = __fmaf_rn(A.sh[t], sV[(size_t)t * HD + tid], acc);
@@ -640,10 +799,13 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
                 }
                 for (; t < Lc; t++) acc = __fmaf_rn(A.sh[t], __ldcg(Vd + (size_t)t * stride), acc);
             }
-            if (room) acc = __fmaf_rn(A.sh[pos], vn[0].x, acc);
+            asm volatile("bar.sync 3, 96;" ::: "memory");       // warp 2 has the new v row
+            if (room) acc = __fmaf_rn(A.sh[pos], S->vn[tid], acc);
             out = __fdiv_rn(acc, Z);
+        } else {
+            asm volatile("bar.sync 3, 96;" ::: "memory");
         }
-        if (warp < (HD >> 5)) publish_block_q8((float2*)P.ws_att, nq, (h * HD >> 5) + warp, out, tag);
+        if (warp < (HD >> 5)) publish_block_q8((float2*)P.ws_att, nq, (h * HD >> 5) + warp, out, tag, S->nrep);
     }
     tr.stamp(14);
     consumer_sync();        // the shared-memory areas of this layer may be rewritten
@@ -670,6 +832,10 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
     A.sh = (float*)(smem + off); off += ((size_t)P.max_seq * 4 + 127) & ~(size_t)127;
     A.q = (float*)(smem + off); off += (size_t)HD * 4;
     A.kn = (float*)(smem + off); off += (size_t)HD * 4;
+    off = (off + 127) & ~(size_t)127;
+    // the layer descriptors, copied once: the producer thread walks them far ahead of the consumers and
+    // must not pay a memory round trip per pointer
+    lt_decode_layer* lys = (lt_decode_layer*)(smem + off);
     A.big = smem + fixed_bytes;
 
     const int tid = threadIdx.x;
@@ -686,8 +852,14 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         mbar_init(&S->wempty, DEC_CWARPS);
         mbar_init(&S->att_done, 1);
         S->abort_flag = 0;
+        S->nrep = (P.poll_looks >= 1 && P.poll_looks <= DEC_NREP) ? P.poll_looks : DEC_NREP;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    {
+        constexpr int LY_WORDS = (int)(sizeof(lt_decode_layer) / 8);
+        for (int i = tid; i < L * LY_WORDS; i += DEC_THREADS)
+            ((unsigned long long*)lys)[i] = __ldg((const unsigned long long*)P.layers + i);
     }
     __syncthreads();
 
@@ -713,7 +885,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             const unsigned qb = (unsigned)HD * E, db = (unsigned)HD * nbE * 2;
             int armed = -1;         // last layer whose resident rows were requested
             for (int il = 0; il < L && ok; il++) {
-                const lt_decode_layer* ly = P.layers + il;
+                const lt_decode_layer* ly = lys + il;
                 if (il > 0) ok = mbar_wait(&S->wempty, (unsigned)(il - 1) & 1u, S, P.status);
                 if (!ok) break;
                 armed = il;
@@ -732,17 +904,17 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             }
         } else {
             for (int il = 0; il < L && ok; il++) {
-                const lt_decode_layer* ly = P.layers + il;      // read from global memory: the producer runs ahead
-                ok = produce_segment(R, ly->qkv_q, (const __half*)ly->qkv_d, nq + nk + v0, nq + nk + v1, E, S, P.status);
-                if (ok) ok = produce_segment(R, ly->o_q, (const __half*)ly->o_d, e0, e1, nq, S, P.status);
+                const lt_decode_layer* ly = lys + il;
+                ok = produce_segment(R, ly->qkv_q, (const __half*)ly->qkv_d, nq + nk + v0, nq + nk + v1, E, rows_per_chunk(E), S, P.status);
+                if (ok) ok = produce_segment(R, ly->o_q, (const __half*)ly->o_d, e0, e1, nq, rows_per_chunk(nq), S, P.status);
                 for (int b = b0; b < b1 && ok; b++) {
-                    ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, b * 32, b * 32 + 32, E, S, P.status);
-                    if (ok) ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, F + b * 32, F + b * 32 + 32, E, S, P.status);
+                    ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, b * 32, b * 32 + 32, E, rows_per_chunk(E), S, P.status);
+                    if (ok) ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, F + b * 32, F + b * 32 + 32, E, rows_per_chunk(E), S, P.status);
                 }
-                if (ok) ok = produce_segment(R, ly->down_q, (const __half*)ly->down_d, e0, e1, F, S, P.status);
+                if (ok) ok = produce_segment(R, ly->down_q, (const __half*)ly->down_d, e0, e1, F, rows_per_chunk(F), S, P.status);
             }
         }
-        if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, S, P.status);
+        if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status);
         if (!ok || S->abort_flag) producer_drain(R);
         return;
     }
@@ -754,9 +926,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
     const unsigned backoff = (unsigned)P.poll_ns;
     // tags of this step: token counter * (L+2) + layer + 1 (never 0 = "never written"); the argmax partials use tag0 + L
     const unsigned tag0 = __ldcg(P.epoch) * (unsigned)(L + 2) + 1u;
-    constexpr int LY_WORDS = (int)(sizeof(lt_decode_layer) / 8);
-    if (tid < LY_WORDS) ((unsigned long long*)&S->ly[0])[tid] = ((const unsigned long long*)P.layers)[tid];
-    for (int l = tid; l < L; l += DEC_CTHREADS) S->lens[l] = __ldcg(P.layers[l].len);
+    for (int l = tid; l < L; l += DEC_CTHREADS) S->lens[l] = __ldcg(lys[l].len);
     // x of layer 0: gathered from the Q8_0 table by the device token, or preloaded by the host
     if (P.tok != nullptr) {
         int t = __ldcg(P.tok);
@@ -771,82 +941,98 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
     }
     consumer_sync();
 
-    EpiCtx C;
-    C.P = &P; C.S = S; C.nq = nq; C.nk = nk; C.bestv = -3.4e38f; C.besti = 2147483647; C.svbuf = 0;
-    C.resid = A.fa; C.tag = 0; C.pos = 0; C.room = 0; C.ly = &S->ly[0];
-
-    for (int il = 0; il < L; il++) {
-        const lt_decode_layer* ly = &S->ly[il & 1];
-        // the next layer's descriptor (visible after this layer's barriers)
-        if (il + 1 < L && tid < LY_WORDS)
-            ((unsigned long long*)&S->ly[(il + 1) & 1])[tid] = ((const unsigned long long*)(P.layers + il + 1))[tid];
-        const unsigned tag = tag0 + (unsigned)il;
-        if (att) {
-            attention_layer<HD>(P, ly, il, tag0, A, vcap, S, tr);
-            continue;
-        }
-        C.ly = ly; C.tag = tag;
-        // ---- (1) layer input -> RMSNorm -> quantiser -> this CTA's v rows
-        for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(ly->attn_norm + j);
-        fetch_x((const float2*)P.ws_x, tag - 1u, il == 0, A.fa, E, S, P.status, backoff);
-        consumer_sync();
-        tr.stamp(21);
-        {
-            const float inv = warp_inv_rms(S->sred, E, P.eps);
-            quant_blocks(A.fa, A.w, inv, E, A.xq0, A.xd0);
-        }
-        consumer_sync();
-        {
-            int pos = S->lens[il];
-            C.room = (pos >= 0 && pos < P.max_seq);
-            C.pos = pos;
-        }
-        consume_segment<EPI_V>(R, (const __half*)ly->qkv_d, nq + nk + v0, nq + nk + v1, E, A.xq0, A.xd0, C, P.status);
-        // ---- (2) quantised attention output -> o_proj + x -> x1
-        for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(ly->ffn_norm + j);   // for (3); all reads of A.w in (1) are past a barrier
-        fetch_q8<DEC_AB>((const float2*)P.ws_att, tag, nq, A.xq1, A.xd1, S, P.status, backoff);
-        consumer_sync();
-        tr.stamp(22);
-        C.resid = A.fa;
-        consume_segment<EPI_O>(R, (const __half*)ly->o_d, e0, e1, nq, A.xq1, A.xd1, C, P.status);
-        // ---- (3) x1 -> RMSNorm -> quantiser -> gate|up blocks -> quantised silu(gate)*up
-        fetch_x((const float2*)P.ws_x1, tag, false, A.fb, E, S, P.status, backoff);
-        consumer_sync();
-        tr.stamp(23);
-        {
-            const float inv = warp_inv_rms(S->sred, E, P.eps);
-            quant_blocks(A.fb, A.w, inv, E, A.xq0, A.xd0);
-        }
-        consumer_sync();
-        for (int b = b0; b < b1; b++) {
-            consume_segment<EPI_GATE>(R, (const __half*)ly->gu_d, b * 32, b * 32 + 32, E, A.xq0, A.xd0, C, P.status);
-            consume_segment<EPI_UP>(R, (const __half*)ly->gu_d, F + b * 32, F + b * 32 + 32, E, A.xq0, A.xd0, C, P.status);
-            consumer_sync();
-            if (warp == 0) publish_block_q8((float2*)P.ws_v, F, b, S->sv[C.svbuf][lane], tag);
-            C.svbuf ^= 1;
-        }
-        // ---- (4) quantised FFN activation -> down + x1 -> x of the next layer
-        fetch_q8<DEC_VB>((const float2*)P.ws_v, tag, F, A.xq1, A.xd1, S, P.status, backoff);
-        consumer_sync();
-        tr.stamp(24);
-        C.resid = A.fb;
-        consume_segment<EPI_DOWN>(R, (const __half*)ly->down_d, e0, e1, F, A.xq1, A.xd1, C, P.status);
-    }
+    // ---- attention CTAs: their own loop over the layers
     if (att) {
+        for (int il = 0; il < L; il++) attention_layer<HD>(P, lys + il, il, tag0, A, vcap, S, tr);
         if (tid == 0) mbar_arrive(&S->att_done);        // every warp is past the last layer's final barrier
+        for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(P.out_norm + j);
+    } else {
+        for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(lys[0].attn_norm + j);
     }
-    // ------------------------------------------------------------ final norm, LM head, argmax
-    for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(P.out_norm + j);
-    fetch_x((const float2*)P.ws_x, tag0 + (unsigned)L - 1u, false, A.fa, E, S, P.status, backoff);
-    consumer_sync();
-    tr.stamp(31);
-    {
-        const float inv = warp_inv_rms(S->sred, E, P.eps);
-        quant_blocks(A.fa, A.w, inv, E, A.xq0, A.xd0);
+
+    // ---- weight phases, one copy of the code: four per layer for the GEMV CTAs, then the LM head for
+    // every CTA (phase 0 of a layer "L").  Phase p of layer il:
+    //   0  x  -> RMSNorm -> quantiser -> this CTA's v rows             (x of layer il: tag of layer il - 1)
+    //   1  quantised attention output -> o_proj + x -> x1
+    //   2  x1 -> RMSNorm -> quantiser -> gate|up blocks -> quantised silu(gate)*up
+    //   3  quantised FFN activation -> down + x1 -> x of the next layer
+    EpiCtx C;
+    C.tr = tr; C.P = &P; C.S = S; C.nq = nq; C.nk = nk; C.bestv = -3.4e38f; C.besti = 2147483647;
+    C.resid = A.fa; C.tag = 0; C.pos = 0; C.room = 0; C.ly = lys;
+    for (int idx = att ? 4 * L : 0; idx <= 4 * L; idx++) {
+        const int il = idx >> 2, ph = idx & 3;
+        const bool lm = (il == L);
+        const lt_decode_layer* ly = lys + (lm ? L - 1 : il);
+        const unsigned tag = tag0 + (unsigned)il;
+        C.ly = ly; C.tag = tag;
+        // ---- before the hand-over is awaited: the weight stages of the phase, every address, the
+        // epilogue's operands, the norm weight of the next phase (into registers)
+        int epi = EPI_LOGITS, r0 = l0, r1 = l1, K = E;
+        const __half* Wd = (const __half*)P.lm_d;
+        if (!lm) {
+            if (ph == 0) {
+                const int pos = S->lens[il];
+                C.room = (pos >= 0 && pos < P.max_seq);
+                C.pos = pos;
+                epi = EPI_V; Wd = (const __half*)ly->qkv_d; r0 = nq + nk + v0; r1 = nq + nk + v1;
+            } else if (ph == 1) {
+                epi = EPI_O; Wd = (const __half*)ly->o_d; r0 = e0; r1 = e1; K = nq; C.resid = A.fa;
+            } else if (ph == 3) {
+                epi = EPI_DOWN; Wd = (const __half*)ly->down_d; r0 = e0; r1 = e1; K = F; C.resid = A.fb;
+            }
+        }
+        SegPlan sp;
+        FfnPlan fp;
+        if (ph == 2) fp = ffn_prepare(R, (const __half*)ly->gu_d, F, b0, b1 - b0 < 2 ? b1 - b0 : 2, E, C);
+        const int RC = lm ? rows_per_chunk_lm(K) : rows_per_chunk(K);
+        if (ph != 2) sp = seg_prepare(epi, R, Wd, r0, r0, r1, K, RC, C);
+        float nwr[DEC_XB / 2];
+        if (ph & 1) {
+            const float* nw = ph == 1 ? ly->ffn_norm : (il + 1 < L ? lys[il + 1].attn_norm : P.out_norm);
+#pragma unroll
+            for (int k = 0; k < DEC_XB / 2; k++) {
+                const int j = tid + k * DEC_CTHREADS;
+                nwr[k] = j < E ? __ldg(nw + j) : 0.0f;
+            }
+        }
+        C.tr.stamp(20);
+        // ---- the hand-over, then what depends on it
+        if ((ph & 1) == 0) {
+            float* sF = ph == 0 ? A.fa : A.fb;
+            fetch_x((const float2*)(ph == 0 ? P.ws_x : P.ws_x1), ph == 0 ? tag - 1u : tag, idx == 0, sF, E, S, P.status, backoff);
+            consumer_sync();
+            C.tr.stamp(21 + ph);
+            norm_quant(sF, A.w, E, P.eps, A.xq0, A.xd0, S);
+            consumer_sync();
+        } else {
+            fetch_q8((const float2*)(ph == 1 ? P.ws_att : P.ws_v), tag, ph == 1 ? nq : F, A.xq1, A.xd1, S, P.status, backoff);
+            // the norm weight of the next phase; every read of A.w in the previous phase is past a barrier
+#pragma unroll
+            for (int k = 0; k < DEC_XB / 2; k++) {
+                const int j = tid + k * DEC_CTHREADS;
+                if (j < E) A.w[j] = nwr[k];
+            }
+            consumer_sync();
+            C.tr.stamp(21 + ph);
+        }
+        const int8_t* sXq = (ph & 1) ? A.xq1 : A.xq0;
+        const __half* sXd = (ph & 1) ? A.xd1 : A.xd0;
+        if (ph == 2) {
+            for (int b = b0; b < b1; b += 2) {
+                if (b > b0) fp = ffn_prepare(R, (const __half*)ly->gu_d, F, b, b1 - b < 2 ? b1 - b : 2, E, C);
+                ffn_finish(fp, R, F, b, b1 - b < 2 ? b1 - b : 2, b + 2 < b1, E, sXq, sXd, C);
+            }
+        } else {
+            for (;;) {
+                seg_finish(epi, sp, R, K, sXq, sXd, C);
+                const int r = sp.r + sp.nset;
+                if (r >= r1) break;
+                sp = seg_prepare(epi, R, Wd, r0, r, r1, K, RC, C);
+            }
+        }
+        C.tr.stamp(25 + ph);
     }
-    consumer_sync();
-    consume_segment<EPI_LOGITS>(R, (const __half*)P.lm_d, l0, l1, E, A.xq0, A.xd0, C, P.status);
-    tr.stamp(32);
+    C.tr.stamp(32);
     float bestv = C.bestv;
     int besti = C.besti;
 #pragma unroll
@@ -874,8 +1060,8 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         float bv = -3.4e38f;
         int bi = 2147483647;
         for (int c = lane; c < G; c += 32) {
-            float2 w[2];
-            poll_words<2>((const float2*)P.ws_part, 2 * G, 2 * c, 1, ptag, w, S, P.status, backoff);
+            float2 w[4];
+            poll_words((const float2*)P.ws_part, 2 * G, 2 * c, 1, 2, ptag, w, S, P.status, backoff);
             const float v = w[0].x;
             const int i = (int)__float_as_uint(w[1].x);
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
@@ -889,7 +1075,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         // every CTA has delivered its result, so every CTA has read the token, the lengths and the
         // token counter of this step: they may advance now
         for (int l = lane; l < L; l += 32) {
-            int* lp = P.layers[l].len;
+            int* lp = lys[l].len;
             const int p = __ldcg(lp);
             if (p >= 0 && p < P.max_seq) *lp = p + 1;
         }
@@ -904,7 +1090,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             *P.epoch = *P.epoch + 1u;
         }
     }
-    tr.stamp(99);
+    C.tr.stamp(99);
 }
 
 struct DecodeGeometry {
@@ -925,7 +1111,7 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
     size_t fixed = up128(sizeof(Shared)) + up128(E) + up128((size_t)(E >> 5) * 2) + up128(kmax1) +
                    up128((size_t)(kmax1 >> 5) * 2) + 3 * up128((size_t)E * 4) + up128((size_t)d->max_seq * 4) +
                    (size_t)2 * hd * 4;
-    fixed = up128(fixed);
+    fixed = up128(fixed) + up128((size_t)d->n_layers * sizeof(lt_decode_layer));
     const size_t avail = (size_t)smem_max - 256;
     // attention CTA: the head's q rows and its group's k rows (quants, then scales), then staged V rows
     const size_t wreg = (size_t)2 * hd * (E + (E >> 5) * 2);
@@ -940,6 +1126,10 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
     int nst = (int)((avail - fixed) / DEC_STAGE_STRIDE);
     if (nst > DEC_MAX_STAGES) nst = DEC_MAX_STAGES;
     g->nstages = nst;
+    if (nst < DEC_MAXCH) {
+        set_error("lt_decode_step: shared memory leaves only %d ring stages (needs %d)", nst, DEC_MAXCH);
+        return LT_ERR_UNSUPPORTED;
+    }
     // the LM-head ring of an attention CTA lives in its big area once the layers are done
     const size_t big_att = wreg + vrows * (size_t)hd * 4;
     int nsa = (int)(big_att / DEC_STAGE_STRIDE);
@@ -971,16 +1161,19 @@ static int decode_check(const lt_decode_desc* d, DecodeGeometry* g) {
     LT_REQUIRE(d->n_layers > 0 && d->n_layers <= DEC_MAX_LAYERS && d->E > 0 && d->F > 0 && d->V > 0 && d->max_seq > 0,
                "lt_decode_step: bad dimensions");
     LT_REQUIRE(d->poll_ns >= 0 && d->poll_ns <= 100000, "lt_decode_step: poll_ns=%d out of range", d->poll_ns);
+    LT_REQUIRE(d->poll_looks >= 0 && d->poll_looks <= DEC_NREP, "lt_decode_step: %d workspace copies out of range (0..%d)", d->poll_looks, DEC_NREP);
     const int nq = d->nh * d->hd, nk = d->nkv * d->hd;
     if (!(d->hd == 32 || d->hd == 64)) {
         set_error("lt_decode_step: hd=%d (this kernel keeps a cached K row in registers: hd 32 or 64)", d->hd);
         return LT_ERR_UNSUPPORTED;
     }
     const int fmax = DEC_CTHREADS * DEC_VB * 32 / 9 / 32 * 32, qmax = DEC_CTHREADS * DEC_AB * 32 / 9 / 32 * 32;
-    if (!(d->E % 32 == 0 && d->F % 32 == 0 && d->E <= 256 * DEC_XB && d->F <= fmax && nq <= qmax &&
+    // a 32-row block of gate|up must fit one ring stage
+    const int emax = DEC_STAGE_BYTES / 34 / 32 * 32 < 256 * DEC_XB ? DEC_STAGE_BYTES / 34 / 32 * 32 : 256 * DEC_XB;
+    if (!(d->E % 32 == 0 && d->F % 32 == 0 && d->E <= emax && d->F <= fmax && nq <= qmax &&
           d->F + d->F / 16 <= DEC_STAGE_BYTES)) {
         set_error("lt_decode_step: this kernel handles E <= %d, F <= %d, nh*hd <= %d (multiples of 32); got E=%d F=%d nh*hd=%d",
-                  256 * DEC_XB, fmax, qmax, d->E, d->F, nq);
+                  emax, fmax, qmax, d->E, d->F, nq);
         return LT_ERR_UNSUPPORTED;
     }
     LT_REQUIRE(d->nkv > 0 && d->nh % d->nkv == 0, "lt_decode_step: nh must be a multiple of nkv");
@@ -1004,8 +1197,8 @@ static int decode_check(const lt_decode_desc* d, DecodeGeometry* g) {
     LT_REQUIRE(aligned16(d->lm_q), "lt_decode_step: the LM-head matrix must be 16-byte aligned");
     int rc = decode_geometry(d, g);
     if (rc != LT_OK) return rc;
-    if (d->nh + 1 > g->ctas) {
-        set_error("lt_decode_step: %d query heads need more CTAs than the %d SMs give", d->nh, g->ctas);
+    if (d->nh + 1 > g->ctas || nk > 64 * (g->ctas - d->nh)) {
+        set_error("lt_decode_step: %d query heads / %d v rows are too many for %d SMs", d->nh, nk, g->ctas);
         return LT_ERR_UNSUPPORTED;
     }
     return LT_OK;
@@ -1036,6 +1229,8 @@ extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
     count_launches(1);
     return LT_OK;
 }
+
+extern "C" int lt_decode_ws_replicas(void) { return DEC_NREP; }
 
 extern "C" int lt_decode_num_ctas(void) {
     int dev = 0, sms = 0;

@@ -711,6 +711,7 @@ def _compute_folded_logits(w, cfg, E):
 _FUSED_STEP = "persistent"
 # pause (ns) between two looks at hand-over words that have not arrived yet, in the one-kernel step
 _POLL_NS = 0
+_POLL_LOOKS = 1
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -730,7 +731,7 @@ class _DecDesc(ctypes.Structure):
                [(n, ctypes.c_void_p) for n in (
                    "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "ws_x", "ws_x1", "ws_qkv", "ws_att",
                    "ws_v", "logits", "tok", "out_tok", "history", "step", "sync", "epoch", "part_val", "part_idx",
-                   "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("reserved_", ctypes.c_int)]
+                   "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("poll_looks", ctypes.c_int)]
 
 
 class FusedDecodeStep:
@@ -773,7 +774,8 @@ class FusedDecodeStep:
         nct = max(_lib.lib().lt_decode_num_ctas(), _lib.lib().lt_decode_pdl_num_parts())
         f32 = dict(dtype=torch.float32, device="cuda")
         # tagged workspaces: {value, tag} pairs, zero tags = "never written"
-        self.ws = [torch.zeros(2 * n, **f32) for n in (E, E, nq + 2 * nk, nq, F)]
+        rep = _lib.lib().lt_decode_ws_replicas()
+        self.ws = [torch.zeros(2 * n, **f32) for n in (rep * E, rep * E, nq + 2 * nk, rep * nq, rep * F)]
         self.ws_part = torch.zeros(4 * nct, **f32)
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
         self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -792,7 +794,7 @@ class FusedDecodeStep:
                              None if history is None else int(history), None if step is None else int(step),
                              self.sync.data_ptr(), self.epoch.data_ptr(), self.part_val.data_ptr(),
                              self.part_idx.data_ptr(), None, None, ctypes.addressof(self._layers_host),
-                             self.ws_part.data_ptr(), int(_POLL_NS), 0)
+                             self.ws_part.data_ptr(), int(_POLL_NS), int(_POLL_LOOKS))
         self.mode = "persistent" if _FUSED_STEP is True else _FUSED_STEP
         if self.mode == "persistent" and not _lib.lib().lt_decode_step_supported(ctypes.byref(self.desc)):
             self.mode = "pdl"       # the one-kernel step keeps 2*hd rows of q|k|v resident per SM: small models only

@@ -184,90 +184,89 @@ def run_gemm(args):
                       "device_status": sorted(_lib.device_status()), "peak_source": src}))
 
 
-def run_tp_decode(args):
-    """Llama-3-8B-architecture (or --arch) random-init Q8_0 decode, tensor-parallel over the ranks this
-    program was launched with (torch.distributed.run; a plain launch is world 1).  KV caches pre-filled
-    to --ctx positions, --steps greedy steps from a captured graph; device time is the max over ranks."""
-    import datetime
-    import torch.distributed as dist
-    from . import tp
-    hbm, _tf, src = peaks()
-    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local),
-                                timeout=datetime.timedelta(seconds=120))
-    a = synth.ARCHS[args.arch]
+def tp_arch_cfg(arch, layers=0):
+    a = synth.ARCHS[arch]
     cfg = dict(n_layers=a["n_layers"], n_head=a["n_head"], n_head_kv=a["n_head_kv"], n_embd=a["n_embd"],
                rope_theta=a["rope_theta"], norm_eps=a["norm_eps"], hd=a["hd"], n_ffn=a["n_ffn"], vocab=a["vocab"],
                tied=a["tied"])
-    if args.layers:
-        cfg["n_layers"] = args.layers
+    if layers:
+        cfg["n_layers"] = layers
+    return cfg
+
+
+def tp_decode_case(cfg, arch, rank, world, B, ctx, steps, warmup, comm="p2p", attn_split=0, chained=False,
+                   fused_allreduce=True, check_world1=False, exact_split=True):
+    """One tensor-parallel decode measurement: B sequences, KV caches pre-filled to `ctx` positions,
+    `steps` greedy steps from a captured graph, CUDA events, max over ranks.  Every rank of the
+    (already initialised) process group must call it; every rank gets the result dict."""
+    import torch.distributed as dist
+    from . import tp
+    hbm, _tf, src = peaks()
     E, F, V, L = cfg["n_embd"], cfg["n_ffn"], cfg["vocab"], cfg["n_layers"]
     nq, nk = cfg["n_head"] * cfg["hd"], cfg["n_head_kv"] * cfg["hd"]
     wbytes = (L * ((nq + 2 * nk) * E + E * nq + 2 * F * E + E * F) + V * E) // 32 * 34
-    for B in args.batch:
-        max_seq = args.ctx + args.steps + 8
-        dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=args.comm,
-                            attn_split=args.attn_split, chained=bool(args.chained),
-                            fused_allreduce=bool(args.fused_allreduce))
-        dec.fill_cache(args.ctx, seed=1)
-        start = np.random.default_rng(0).integers(0, V, size=B)
-        dec.set_tokens(start)
-        dec.capture()                               # one warm-up step inside
-        warm = [dec.tok.clone()]
-        for _ in range(max(0, args.warmup - 1)):
-            dec.graph.replay()
-            warm.append(dec.tok.clone())
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        toks = []
-        for _ in range(args.steps):
-            dec.graph.replay()
-            toks.append(dec.tok.clone())
-        e1.record(); torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        toks = torch.stack(toks).cpu().numpy()
-        t = torch.tensor([ms], device="cuda")
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        # the all-reduces of one step alone, back to back (2 per layer, [B, E] fp32)
-        ar_ms = 0.0
-        if world > 1:
-            buf = torch.zeros((B, E), device="cuda"); buf2 = torch.zeros((B, E), device="cuda")
-            side = torch.cuda.Stream()
+    max_seq = ctx + steps + warmup + 8
+    dec = tp.TPDecoder(cfg, rank=rank, world=world, batch=B, max_seq=max_seq, seed=0, comm=comm,
+                       attn_split=attn_split, chained=bool(chained), fused_allreduce=bool(fused_allreduce),
+                       exact_split=bool(exact_split))
+    dec.fill_cache(ctx, seed=1)
+    start = np.random.default_rng(0).integers(0, V, size=B)
+    dec.set_tokens(start)
+    dec.capture()                               # one warm-up step inside
+    warm = [dec.tok.clone()]
+    for _ in range(max(0, warmup - 1)):
+        dec.graph.replay()
+        warm.append(dec.tok.clone())
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    toks = []
+    for _ in range(steps):
+        dec.graph.replay()
+        toks.append(dec.tok.clone())
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    toks = torch.stack(toks).cpu().numpy()
+    t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    # the all-reduces of one step alone, back to back (2 per layer, [B, E] fp32)
+    ar_ms = 0.0
+    if world > 1:
+        buf = torch.zeros((B, E), device="cuda"); buf2 = torch.zeros((B, E), device="cuda")
+        side = torch.cuda.Stream()
 
-            def one():
-                if dec.comm is not None:
-                    dec.comm.allreduce_add(buf, None, buf2, B * E)
-                else:
-                    dist.all_reduce(buf)
-            with torch.cuda.stream(side):
+        def one():
+            if dec.comm is not None:
+                dec.comm.allreduce_add(buf, None, buf2, B * E)
+            else:
+                dist.all_reduce(buf)
+        with torch.cuda.stream(side):
+            one()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(2 * L):
                 one()
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for _ in range(2 * L):
-                    one()
-            g.replay(); torch.cuda.synchronize()
-            dist.barrier()
-            ar_ms = _event_ms(lambda i: g.replay(), 10)
-            t = torch.tensor([ar_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ar_ms = float(t.item())
-        status = sorted(_lib.device_status())
-        match = None
-        if args.check_world1 and world > 1 and rank == 0:
-            # world 1 on this GPU, teacher-forced with the sharded run's tokens: does it choose the same
-            # next token from the same history, and if not, how far apart are the two candidates' logits
-            launches = dec.launches_per_step
-            del dec
-            torch.cuda.empty_cache()
-            ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0, attn_split=args.attn_split)
-            ref.fill_cache(args.ctx, seed=1)
+        g.replay(); torch.cuda.synchronize()
+        dist.barrier()
+        ar_ms = _event_ms(lambda i: g.replay(), 10)
+        t = torch.tensor([ar_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ar_ms = float(t.item())
+    status = sorted(_lib.device_status())
+    launches = dec.launches_per_step
+    match = None
+    if check_world1 and world > 1:
+        # world 1 on rank 0's GPU, teacher-forced with the sharded run's tokens: does it choose the same
+        # next token from the same history, and how far apart are its logits from the sharded run's choice
+        dec.close()
+        del dec
+        torch.cuda.empty_cache()
+        if rank == 0:
+            ref = tp.TPDecoder(cfg, rank=0, world=1, batch=B, max_seq=max_seq, seed=0, attn_split=attn_split)
+            ref.fill_cache(ctx, seed=1)
             ref.set_tokens(start)
             warm_h = torch.stack(warm).cpu().numpy()
             allt = np.concatenate([warm_h, toks], axis=0)      # every token the sharded run produced, warm-up included
@@ -284,31 +283,51 @@ def run_tp_decode(args):
                 ref.set_tokens(allt[sidx])
             match = {"same_next_token_given_same_history": agree / (allt.shape[0] * B),
                      "largest_logit_gap_where_different": worst}
+            ref.close()
             del ref
-        else:
-            launches = dec.launches_per_step
+        dist.barrier()
+    else:
+        dec.close()
+        del dec
+    torch.cuda.empty_cache()
+    step_ms = ms / steps
+    kv_bytes = B * L * 2 * (ctx + steps // 2) * nk * 4
+    step_bytes = wbytes + kv_bytes
+    return {
+        "metric": "decode tok/s (Q8_0, tensor-parallel)", "value": B * steps / (ms * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "ms_per_step": step_ms, "steps": steps, "warmup": warmup,
+        "config": {"workload": f"{arch} Q8_0 decode, batch {B}, context {ctx}, TP={world}",
+                   "layers": L, "launches_per_step": launches, "comm": comm if world > 1 else None,
+                   "chained_launches": bool(chained),
+                   "allreduce_in_gemv": bool(fused_allreduce) and world > 1 and comm == "p2p" and B == 1,
+                   "exact_down_split": bool(exact_split) and world > 1,
+                   "attention_order": f"attn_decode_split, S={attn_split}" if attn_split else "one-pass (production)"},
+        "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
+                     "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
+                     "frac": step_bytes / (step_ms * 1e-3) / 1e9 / (hbm * world), "peak_source": src},
+        "allreduce_ms_per_step_alone": ar_ms, "allreduce_share": ar_ms / step_ms if step_ms else None,
+        "token_match_vs_world1": match, "first_tokens": toks[:4, 0].tolist(),
+        "device_status": status, "data": "synthetic"}
+
+
+def run_tp_decode(args):
+    """Llama-3-8B-architecture (or --arch) random-init Q8_0 decode, tensor-parallel over the ranks this
+    program was launched with (torch.distributed.run; a plain launch is world 1)."""
+    import datetime
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=120))
+    cfg = tp_arch_cfg(args.arch, args.layers)
+    for B in args.batch:
+        out = tp_decode_case(cfg, args.arch, rank, world, B, args.ctx, args.steps, args.warmup, comm=args.comm,
+                             attn_split=args.attn_split, chained=args.chained, fused_allreduce=args.fused_allreduce,
+                             check_world1=args.check_world1, exact_split=args.exact_split)
         if rank == 0:
-            step_ms = ms / args.steps
-            kv_bytes = B * L * 2 * (args.ctx + args.steps // 2) * nk * 4
-            step_bytes = wbytes + kv_bytes
-            print(json.dumps({
-                "metric": "decode tok/s (Q8_0, tensor-parallel)", "value": B * args.steps / (ms * 1e-3), "unit": "tok/s",
-                "n_gpus": world, "ms_per_step": step_ms, "steps": args.steps, "warmup": args.warmup,
-                "config": {"workload": f"{args.arch} Q8_0 decode, batch {B}, context {args.ctx}, TP={world}",
-                           "layers": L, "launches_per_step": launches, "comm": args.comm if world > 1 else None, "chained_launches": bool(args.chained),
-                           "allreduce_in_gemv": bool(args.fused_allreduce) and world > 1 and args.comm == "p2p" and B == 1,
-                           "attention_order": f"attn_decode_split, S={args.attn_split}" if args.attn_split else "one-pass (production)"},
-                "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
-                             "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",
-                             "frac": step_bytes / (step_ms * 1e-3) / 1e9 / (hbm * world), "peak_source": src},
-                "allreduce_ms_per_step_alone": ar_ms, "allreduce_share": ar_ms / step_ms if step_ms else None,
-                "token_match_vs_world1": match, "first_tokens": toks[:4, 0].tolist(),
-                "device_status": status, "data": "synthetic"}), flush=True)
-        try:
-            del dec
-        except NameError:
-            pass
-        torch.cuda.empty_cache()
+            print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -349,6 +368,9 @@ def main(argv=None):
                    help="1: one-sequence operators as chained launches (lt_set_chained_launch; measured slower inside "
                         "a captured graph); 0: ordinary launches")
     t.add_argument("--check-world1", action="store_true", help="rank 0 re-runs at world 1 and compares the tokens")
+    t.add_argument("--exact-split", type=int, default=1,
+                   help="1: down is split by dealing Q8_0 blocks round-robin (lane-exact partial folds, tree-ordered "
+                        "sum: the bits of one GPU); 0: contiguous K ranges")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("llamatov_b200.measure needs a CUDA device (there is no CPU path)")
