@@ -10,10 +10,18 @@ quantised to Q8_0 (llamatov_b200.synth); the prompt is 32 uniform random token i
 Printed JSON line (rank 0):
   value        tok/s with everything resident in HBM: K replays of the captured step with the
                token loop on the device (embedding gather and argmax inside the graph), CUDA
-               events on the replay stream, max over ranks.
+               events on the replay stream, max over ranks; the MEDIAN of --repeats timed regions
+               of K steps each (the reference's own protocol is the median of 6 runs of 100
+               replays, bpd/kernelgen/referee/rms_quant_prod_ab.py:22-47), min and max beside it.
   e2e          tok/s through the reference-facing call GraphRunner.replay_token(tok): per
-               token the host looks up the embedding row, copies it to the device (E*4 bytes),
-               launches the graph, synchronises and reads the chosen token back (4 bytes).
+               token the host copies the step's input to the device from page-locked memory
+               (the token id, 4 bytes, when the embedding table is a Q8_0 table and the step
+               gathers the row itself; else the fp32 row, E*4 bytes), launches the graph,
+               synchronises and reads the chosen token back (4 bytes).  Median of the repeats.
+  tp           the tensor-parallel path (BASELINE config 4): Llama-3-8B-architecture decode, 4096
+               positions of context, TP = number of ranks, batch 1 and batch 32 (one object per
+               batch: tok/s, ms per step, fraction of ranks x HBM peak, all-reduce share, token
+               match and largest logit gap against the same tokens at TP = 1).
   roofline     the decode step as a whole: algorithmic bytes of one token (34 bytes per 32 weights of
                every matrix + the fp32 KV rows read once per KV head) divided by the device time per
                token (CUDA events on the replay stream), against the measured HBM copy bandwidth;
@@ -47,8 +55,8 @@ METRIC = "decode tok/s (0.5B Q8_0, bs1)"
 UNIT = "tok/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE token's launches, from an ncu capture of
-# this very command (profiles/decode_step_qwen05b.md), keyed by step mode; None where not captured.
-NCU_TRAFFIC = {"pdl": 530232064}
+# this very command, keyed by step mode; None where not captured.
+NCU_TRAFFIC = {"pdl": 530232064, "persistent": None}
 
 
 def _peaks():
@@ -156,7 +164,6 @@ def run_reference(args, rank):
         o.set_threads(os.cpu_count() or 1)
     eng = o.OracleEngine(synth.oracle_model(model), max_seq=256)
     nxt = prompt[0]
-    per_step = max(1, min(4, args.steps))       # tokens per "step" sample: bounded CPU work
     for _ in range(args.warmup):
         _, nxt = eng.step(nxt)
     t0 = time.perf_counter()
@@ -272,13 +279,37 @@ def run_config0(args):
     print(json.dumps(out))
 
 
+def run_tp_leg(rank, world, steps):
+    """BASELINE config 4 on the ranks of this run: Llama-3-8B-architecture random-init Q8_0 decode, TP = world,
+    KV caches pre-filled to 4096 positions, batch 1 (attention in the declared split order, S = 16) and batch 32
+    (one-pass order), `steps` greedy steps from a captured graph.  With world > 1 rank 0 then re-runs the same
+    tokens at TP = 1 and reports how often it chooses the same next token and the largest logit gap."""
+    from llamatov_b200 import measure
+    cfg = measure.tp_arch_cfg("llama-3-8b")
+    out = {"world": world, "arch": "llama-3-8b", "context": 4096, "steps": steps}
+    for B, split in ((1, 16), (32, 0)):
+        r = measure.tp_decode_case(cfg, "llama-3-8b", rank, world, B, 4096, steps, 3, comm="p2p", attn_split=split,
+                                   check_world1=world > 1, exact_split=True)
+        m = r["token_match_vs_world1"] or {}
+        out[f"batch{B}"] = {"tok_s": r["value"], "ms_per_step": r["ms_per_step"], "frac_of_ranks_x_hbm_peak": r["roofline"]["frac"],
+                            "allreduce_share": r["allreduce_share"], "launches_per_step": r["config"]["launches_per_step"],
+                            "token_match_vs_world1": m.get("same_next_token_given_same_history"),
+                            "max_abs_logit_vs_world1": m.get("largest_logit_gap_where_different"),
+                            "exact_down_split": r["config"]["exact_down_split"], "attention_order": r["config"]["attention_order"],
+                            "device_status": r["device_status"]}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel leg (the `tp` object)")
+    ap.add_argument("--tp-steps", type=int, default=32)
     ap.add_argument("--config0", action="store_true", help="the single-GEMV case (BASELINE config 0) instead of decode")
     ap.add_argument("--step-mode", default=None, choices=["pdl", "persistent", "per-op"],
                     help="how the captured decode step is built (default: the engine's default)")
@@ -300,7 +331,8 @@ def main():
     from llamatov_b200 import _lib, dev_residency as dr, synth
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
 
     model = synth.make_model(ARCH, seed=0)
     mc = model["cfg"]
@@ -340,37 +372,46 @@ def main():
     if K + W > max_new:
         raise SystemExit(f"steps+warmup = {K + W} exceeds the KV capacity left after the prompt ({max_new})")
 
+    R = max(1, args.repeats)
     # ---- e2e: the reference-facing call, host buffers, copies inside the timed region
-    reset_cache()
-    tok = first
-    for _ in range(W):
-        tok = gr.replay_token(tok)
-    barrier()
     sampler = ClockSampler(local); sampler.start()
-    t0 = time.perf_counter()
-    e2e_tokens = []
-    for _ in range(K):
-        tok = gr.replay_token(tok)
-        e2e_tokens.append(tok)
-    barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0)
+    e2e_runs, e2e_tokens = [], []
+    for r in range(R):
+        reset_cache()
+        tok = first
+        for _ in range(W):
+            tok = gr.replay_token(tok)
+        barrier()
+        t0 = time.perf_counter()
+        e2e_tokens = []
+        for _ in range(K):
+            tok = gr.replay_token(tok)
+            e2e_tokens.append(tok)
+        barrier()
+        e2e_runs.append(max_over_ranks((time.perf_counter() - t0) * 1000.0))
+    e2e_ms = float(np.median(e2e_runs))
     e2e_launches = (gr.launches_per_token + 2) * K
 
     # ---- value: device-resident token loop, CUDA events on the replay stream
     reset_cache()
     gr.capture_device_loop(first)
-    gr.replay_device(W)
-    barrier()
-    ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(gr.stream):
-        ev0.record()
-    gr.replay_device(K)
-    with torch.cuda.stream(gr.stream):
-        ev1.record()
-    barrier()
-    dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    dev_runs, dev_tokens = [], []
+    for r in range(R):
+        reset_cache()
+        gr.reset_device_loop(first)
+        gr.replay_device(W)
+        barrier()
+        ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(gr.stream):
+            ev0.record()
+        gr.replay_device(K)
+        with torch.cuda.stream(gr.stream):
+            ev1.record()
+        barrier()
+        dev_runs.append(max_over_ranks(ev0.elapsed_time(ev1)))
+        dev_tokens = gr.device_tokens()[W:W + K]
+    dev_ms = float(np.median(dev_runs))
     clocks = sampler.stop()
-    dev_tokens = gr.device_tokens()[W:W + K]
     status = _lib.device_status()
     tokens_match = (dev_tokens == e2e_tokens)
 
@@ -385,6 +426,7 @@ def main():
     step_bytes = weight_bytes + kv_bytes
     peak, peak_src = _peaks()
     achieved = step_bytes / (dev_ms / K * 1e-3) / 1e9
+    step_mode = getattr(gr, "_step_dev", None).mode if getattr(gr, "_step_dev", None) is not None else "per-op"
     # the one launch of the chain that is bandwidth-bound by itself: the LM-head GEMV, timed alone
     # (its 145 MB exceed L2, so every launch streams from HBM)
     dWq, dWd, N_, K_ = dr._weights(dr._lm_head(w))
@@ -406,10 +448,13 @@ def main():
     lm_us = 1000.0 * e0.elapsed_time(e1) / 20
     lm_gbs = gemv_bytes(N_, K_) / (lm_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC.get(dr._FUSED_STEP if dr._FUSED_STEP else "per-op"),
+                "traffic": NCU_TRAFFIC.get(step_mode),
                 "kernel": "decode step = %d launches per token (%s)" % (
                     gr.launches_per_step, "k_fused_gemv, k_fused_gateup, k_fused_attn, k_fused_lmhead, k_fused_argmax"
-                    if dr._FUSED_STEP == "pdl" else ("k_decode_step" if dr._FUSED_STEP else "per-op kernels")),
+                    if step_mode == "pdl" else ("lt::k_decode_step, one cooperative launch" if step_mode == "persistent"
+                                                else "per-op kernels")),
+                "traffic_source": "ncu capture of this command (dram__bytes_read.sum + dram__bytes_write.sum of one "
+                                  "token's launches), not measured in this run" if NCU_TRAFFIC.get(step_mode) else None,
                 "algorithmic_bytes_per_launch": step_bytes / max(1, gr.launches_per_step),
                 "algorithmic_bytes_per_token": step_bytes,
                 "us_per_token": 1000.0 * dev_ms / K,
@@ -420,24 +465,56 @@ def main():
     value = world * K / (dev_ms * 1e-3)
     e2e_val = world * K / (e2e_ms * 1e-3)
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+           "repeats": R, "value_min": world * K / (max(dev_runs) * 1e-3), "value_max": world * K / (min(dev_runs) * 1e-3),
            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
            "dtype": "int8*int8->int32, fp32 accumulate", "data": "synthetic",
            "config": {"workload": f"{ARCH} Q8_0 decode, batch 1, {PROMPT_LEN}-token prompt, {K} greedy steps",
                       "parallelism": "replicas only" if world > 1 else "1 GPU",
                       "l2": "inputs larger than L2 (525 MB of weights streamed per token vs 126 MB L2)",
-                      "step_mode": dr._FUSED_STEP if dr._FUSED_STEP else "per-op",
+                      "step_mode": step_mode, "timing": f"median of {R} timed regions of {K} steps",
                       "tokens_device_loop_equal_host_loop": tokens_match, "device_status": sorted(status)},
-           "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": E * 4, "d2h_bytes_per_step": 4,
-                   "ms_per_step": e2e_ms / K},
+           "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": gr.input_bytes_per_replay(), "d2h_bytes_per_step": 4,
+                   "ms_per_step": e2e_ms / K, "value_min": world * K / (max(e2e_runs) * 1e-3),
+                   "value_max": world * K / (min(e2e_runs) * 1e-3)},
            "gpu_launches": int(gr.launches_per_step * K),
            "gpu_launches_e2e": int(e2e_launches),
            "clocks": clocks, "roofline": roofline}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_decode_baseline(model, prompt)
-    if rank == 0:
-        print(json.dumps(out))
+    # ---- the tensor-parallel leg.  A failure or a stall here must not cost the line above: a watchdog prints
+    # the line without the leg's numbers and ends the process.
+    printed = threading.Event()
+
+    def emit(tp_obj):
+        if printed.is_set():
+            return
+        printed.set()
+        out["tp"] = tp_obj
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+
+    if args.no_tp:
+        emit(None)
+    else:
+        def give_up():
+            emit({"error": "the tensor-parallel leg did not finish within its time limit"})
+            sys.stdout.flush()
+            os._exit(0)
+        dog = threading.Timer(420.0, give_up); dog.daemon = True; dog.start()
+        try:
+            # free the 0.5B engine first: the leg builds an 8B model
+            del gr, kv, w, model
+            dr.reset_engine_state()
+            torch.cuda.empty_cache()
+            tp_obj = run_tp_leg(rank, world, args.tp_steps)
+        except Exception as e:      # noqa: BLE001 -- the headline must survive anything the leg does
+            tp_obj = {"error": f"{type(e).__name__}: {e}"[:400]}
+        dog.cancel()
+        emit(tp_obj)
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        # no interpreter teardown: a process group being destroyed can wait on a peer that has already gone
+        os._exit(0)
 
 
 if __name__ == "__main__":

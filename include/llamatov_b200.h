@@ -361,16 +361,35 @@ typedef struct lt_comm {
 } lt_comm;
 int lt_comm_alloc(int world, int max_n, lt_comm* comm, unsigned char* handle);
 int lt_comm_connect(lt_comm* comm, int rank, const unsigned char* all_handles);
+/* lt_comm_free unmaps the peers' buffers and frees this rank's: no kernel of ANY rank that uses the comm may
+ * still be running -- synchronise the device, then pass a host barrier over all ranks, then call it. */
 int lt_comm_free(lt_comm* comm);
 int lt_allreduce_add(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
                      void* stream);
+/* The same exchange with the partials summed pairwise, p[t] + p[t + s] for s = world/2 .. 1 (world a power of
+ * two): the order in which the GEMV contract's lane tree (bpd/kernelgen/emitters/q8_0_from_facts.pl:476) joins
+ * lanes t and t + s.  With lt_q8_gemv_lanes partials this gives the bits of the one-GPU GEMV. */
+int lt_allreduce_add_tree(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
+                          void* stream);
+
+/* Partial GEMV of a tensor-parallel row split that keeps the one-GPU bits.  The `group` ranks deal the Q8_0
+ * blocks of every row round-robin (rank r holds blocks b = r mod group, i.e. the blocks of the contract's
+ * lanes L = r mod group, q8_0_from_facts.pl:476); Wq / Wd are this rank's blocks, K its share of the row
+ * length.  Lane chains in ascending block order and the tree levels that stay inside a rank; Y[t*M + n] is
+ * the rank's partial.  Summing the ranks' partials in lt_allreduce_add_tree's order gives lt_q8_gemv's result
+ * on the whole matrix bit for bit.  group 1, 2, 4 or 8 (group 1 = lt_q8_gemv). */
+int lt_q8_gemv_lanes(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, float* Y, int M,
+                     int K, int T, int group, void* stream);
 
 /* The tensor-parallel row-split projection (o_proj, down) of one sequence with the all-reduce inside the
  * GEMV: this rank folds its K-slice of every row (lt_q8_gemv arithmetic), a warp stores each finished partial
  * into every rank's staging memory at once and, when its rows are out, takes the partials of all ranks from
  * its own staging memory: Y[n] = Resid[n] + ((part_0[n] + part_1[n]) + ...) in rank order, the same bits as
  * lt_q8_gemv followed by lt_allreduce_add.  Same call sequence and the same M, K on every rank; M <= max_n of
- * the comm; Y may alias Resid.  Bounded waits (LT_STATUS_WAIT_TIMEOUT). */
+ * the comm; Y may alias Resid.  Bounded waits (LT_STATUS_WAIT_TIMEOUT); a row's exchange is counted even
+ * when its wait gave up, so the ranks stay in step.  Warps of different ranks wait for each other, so the
+ * kernel is launched cooperatively (at most one resident wave): one process per GPU, nothing else may hold
+ * the GPU's SMs for good while it runs. */
 int lt_q8_gemv_allreduce(const lt_comm* comm, const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq,
                          const uint16_t* Xd, const float* Resid, float* Y, int M, int K, void* stream);
 

@@ -55,6 +55,8 @@ SIGNATURES = {
     "lt_comm_connect": [_vp, _i, _vp],
     "lt_comm_free": [_vp],
     "lt_allreduce_add": [_vp, _vp, _vp, _vp, _i, _vp],
+    "lt_allreduce_add_tree": [_vp, _vp, _vp, _vp, _i, _vp],
+    "lt_q8_gemv_lanes": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],
     "lt_decode_step": [_vp, _vp],

@@ -14,6 +14,10 @@ namespace lt {
 constexpr int COMM_THREADS = 256;
 constexpr int COMM_CHUNK = COMM_THREADS * 4;        // floats per CTA
 
+// TREE: the partials are summed pairwise, p[t] + p[t + s] for s = world/2 .. 1 (world a power of two): the last
+// levels of the GEMV contract's lane tree when the ranks hold lane subsets (lt_q8_gemv_lanes); otherwise in
+// rank order.
+template <bool TREE>
 __global__ void __launch_bounds__(COMM_THREADS)
 k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __restrict__ resid,
                 float* __restrict__ out, int n, int* status) {
@@ -39,24 +43,48 @@ k_allreduce_add(const CommDev C, const float* __restrict__ part, const float* __
             }
         }
         float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float p[TREE ? LT_COMM_MAX_RANKS : 1][4];
         bool ok = true;
         const long long t0 = clock64();
-        for (int r = 0; r < C.world && ok; r++) {
-            const float2* src = C.stage[C.rank] + comm_slot(C, U, number, r, i);
 #pragma unroll
-            for (int e = 0; e < 4; e += 2) {      // two words per 16-byte load, both tags checked
-                float4 w = ld_volatile_f4(src + e);
-                while (__float_as_uint(w.y) != number || __float_as_uint(w.w) != number) {
-                    if (clock64() - t0 > COMM_WAIT_LIMIT) {
-                        atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
-                        ok = false;
-                        break;
+        for (int r = 0; r < LT_COMM_MAX_RANKS; r++) {
+            if (r < C.world && ok) {
+                const float2* src = C.stage[C.rank] + comm_slot(C, U, number, r, i);
+#pragma unroll
+                for (int e = 0; e < 4; e += 2) {      // two words per 16-byte load, both tags checked
+                    float4 w = ld_volatile_f4(src + e);
+                    while (__float_as_uint(w.y) != number || __float_as_uint(w.w) != number) {
+                        if (clock64() - t0 > COMM_WAIT_LIMIT) {
+                            atomicOr(status, (int)LT_STATUS_WAIT_TIMEOUT);
+                            ok = false;
+                            break;
+                        }
+                        w = ld_volatile_f4(src + e);
                     }
-                    w = ld_volatile_f4(src + e);
+                    if (TREE) {
+                        p[TREE ? r : 0][e] = w.x; p[TREE ? r : 0][e + 1] = w.z;
+                    } else {
+                        a[e] = r == 0 ? w.x : __fadd_rn(a[e], w.x);
+                        a[e + 1] = r == 0 ? w.z : __fadd_rn(a[e + 1], w.z);
+                    }
                 }
-                a[e] = r == 0 ? w.x : __fadd_rn(a[e], w.x);
-                a[e + 1] = r == 0 ? w.z : __fadd_rn(a[e + 1], w.z);
+            } else if (TREE) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) p[TREE ? r : 0][e] = 0.0f;
             }
+        }
+        if (TREE) {
+#pragma unroll
+            for (int s = LT_COMM_MAX_RANKS / 2; s > 0; s >>= 1) {
+                if (s < C.world) {
+#pragma unroll
+                    for (int t = 0; t < s; t++)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) p[TREE ? t : 0][e] = __fadd_rn(p[TREE ? t : 0][e], p[TREE ? t + s : 0][e]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) a[e] = p[0][e];
         }
         if (ok) {
             float4 y = make_float4(a[0], a[1], a[2], a[3]);
@@ -138,7 +166,23 @@ extern "C" int lt_allreduce_add(const lt_comm* comm, const float* part, const fl
     LT_REQUIRE(st != nullptr, "lt_allreduce_add: status word unavailable");
     const CommDev C = comm_dev(comm);
     const int ctas = (n + COMM_CHUNK - 1) / COMM_CHUNK;
-    const cudaError_t e = launch_chained(k_allreduce_add, dim3(ctas), dim3(COMM_THREADS), 0, (cudaStream_t)stream, C, part,
-                                         resid, out, n, st);
+    const cudaError_t e = launch_chained(k_allreduce_add<false>, dim3(ctas), dim3(COMM_THREADS), 0, (cudaStream_t)stream, C,
+                                         part, resid, out, n, st);
     return check_launch("lt_allreduce_add", 1, e);
+}
+
+extern "C" int lt_allreduce_add_tree(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
+                                     void* stream) {
+    LT_REQUIRE(comm && part && out, "lt_allreduce_add_tree: null pointer");
+    LT_REQUIRE((comm->world & (comm->world - 1)) == 0, "lt_allreduce_add_tree: world=%d must be a power of two", comm->world);
+    LT_REQUIRE(n > 0 && n % 4 == 0 && n <= comm->max_n, "lt_allreduce_add_tree: n=%d must be a multiple of 4, at most %d", n, comm->max_n);
+    LT_REQUIRE(aligned16(part) && aligned16(out) && (resid == nullptr || aligned16(resid)),
+               "lt_allreduce_add_tree: vectors must be 16-byte aligned");
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_allreduce_add_tree: status word unavailable");
+    const CommDev C = comm_dev(comm);
+    const int ctas = (n + COMM_CHUNK - 1) / COMM_CHUNK;
+    const cudaError_t e = launch_chained(k_allreduce_add<true>, dim3(ctas), dim3(COMM_THREADS), 0, (cudaStream_t)stream, C,
+                                         part, resid, out, n, st);
+    return check_launch("lt_allreduce_add_tree", 1, e);
 }

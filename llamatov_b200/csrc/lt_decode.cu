@@ -120,7 +120,9 @@ struct Shared {
     float sv[2][32];                        // silu(gate)*up of the FFN blocks being folded
     float bias[256];                        // attention CTA: bias of its q rows, then of its k rows
     float qk[256];                          // attention CTA: q rows then k rows before rope
-    float vbias[64];                        // GEMV CTA: bias of its v rows
+    // plans of the recurring sets, remembered per warp relative to the stage bases: [kind][warp][qrel 4 | drel 4 |
+    // chunk of row k (4 x 8 bits) | nset | nch | nv]; kinds: v rows, o_proj, down, a full LM-head set
+    unsigned memo[4][DEC_CWARPS][12];
     float vn[128];                          // attention CTA: the new v row of its group
     int lens[DEC_MAX_LAYERS];               // cache lengths at kernel entry
     float best_v[DEC_CWARPS];
@@ -320,7 +322,7 @@ __device__ __forceinline__ float fold_rows(const RowSetN<NR>& rs, int nb, int nv
     float acc[NR];
 #pragma unroll
     for (int k = 0; k < NR; k++) acc[k] = 0.0f;
-#pragma unroll (NR <= 4 ? 2 : 1)
+#pragma unroll (NR == 1 ? 4 : (NR <= 4 ? 2 : 1))
     for (int b = lane; b < nb; b += 32) {
         const int4 x0 = lds128(xq + b * 32 + sw);
         const int4 x1 = lds128(xq + b * 32 + (sw ^ 16u));
@@ -365,37 +367,90 @@ struct SegPlan {
     bool ok;
 };
 
+// memo: the plan of this set relative to its stages' base addresses does not change from layer to layer (same
+// rows, same chunking; the launcher checks that a matrix kind's scale arrays are aligned alike in every layer):
+// memo_mode 1 = compute it and remember it, 2 = take it from the memo (a fraction of the arithmetic), 0 = neither.
 __device__ __forceinline__ SegPlan seg_prepare(int epi, const Ring& R, const __half* Wd, int r0, int r, int r1, int K,
-                                               int RC, EpiCtx& C) {
+                                               int RC, EpiCtx& C, unsigned* memo, int memo_mode) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = K >> 5;
     SegPlan sp;
-    // the set: chunks with nset rows from row r on, at most DEC_MAXCH chunks and DEC_CWARPS * DEC_ILP rows
-    int nset = r1 - r;
-    if (nset > DEC_MAXCH * RC) nset = DEC_MAXCH * RC;
-    if (nset > DEC_CWARPS * DEC_ILP) nset = (DEC_CWARPS * DEC_ILP / RC > 0 ? DEC_CWARPS * DEC_ILP / RC : 1) * RC;
-    if (nset > r1 - r) nset = r1 - r;
-    sp.r = r; sp.nset = nset;
-    sp.nch = (nset + RC - 1) / RC;
-    sp.nv = (nset - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // this warp's rows of the set (<= DEC_ILP)
+    sp.r = r;
     sp.ok = true;
-    Ring R2 = R;
-    for (int c = 0; c < sp.nch; c++) {
-        sp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && sp.ok;
-        const int rc0 = r + c * RC;
-        const int n = (r + nset - rc0 < RC) ? (r + nset - rc0) : RC;
-        const unsigned cb = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
-        const unsigned cd = cb + (unsigned)(n * K) + (unsigned)(reinterpret_cast<uintptr_t>(Wd + (size_t)rc0 * nb) & 15);
+    unsigned cb[DEC_MAXCH];
+    if (memo_mode == 2) {
+        sp.nset = (int)memo[9]; sp.nch = (int)memo[10]; sp.nv = (int)memo[11];
+        Ring R2 = R;
 #pragma unroll
-        for (int k = 0; k < DEC_ILP; k++) {
-            const int i = warp + k * DEC_CWARPS - c * RC;       // row k of this warp, relative to chunk c
-            if (c == 0) { sp.rs.q[k] = cb; sp.rs.d[k] = cd; }   // (unused slots point at valid memory)
-            if (i >= 0 && i < n) {
-                sp.rs.q[k] = cb + (unsigned)(i * K);
-                sp.rs.d[k] = cd + (unsigned)(i * nb * 2);
+        for (int c = 0; c < DEC_MAXCH; c++) {
+            cb[c] = 0;
+            if (c < sp.nch) {
+                sp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && sp.ok;
+                cb[c] = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
+                R2.advance();
             }
         }
-        R2.advance();
+        const unsigned ck = memo[8];
+#pragma unroll
+        for (int k = 0; k < DEC_ILP; k++) {
+            const unsigned c = (ck >> (8 * k)) & 0xffu;
+            unsigned base = cb[0];
+#pragma unroll
+            for (int cc = 1; cc < DEC_MAXCH; cc++)
+                if (c == (unsigned)cc) base = cb[cc];
+            sp.rs.q[k] = base + memo[k];
+            sp.rs.d[k] = base + memo[4 + k];
+        }
+    } else {
+        // the set: chunks with nset rows from row r on, at most DEC_MAXCH chunks and DEC_CWARPS * DEC_ILP rows
+        int nset = r1 - r;
+        if (nset > DEC_MAXCH * RC) nset = DEC_MAXCH * RC;
+        if (nset > DEC_CWARPS * DEC_ILP) nset = (DEC_CWARPS * DEC_ILP / RC > 0 ? DEC_CWARPS * DEC_ILP / RC : 1) * RC;
+        if (nset > r1 - r) nset = r1 - r;
+        sp.nset = nset;
+        sp.nch = (nset + RC - 1) / RC;
+        sp.nv = (nset - warp + DEC_CWARPS - 1) / DEC_CWARPS;     // this warp's rows of the set (<= DEC_ILP)
+        unsigned qrel[DEC_ILP], drel[DEC_ILP], ck = 0;
+#pragma unroll
+        for (int k = 0; k < DEC_ILP; k++) { qrel[k] = 0; drel[k] = 0; }
+        Ring R2 = R;
+#pragma unroll
+        for (int c = 0; c < DEC_MAXCH; c++) {
+            cb[c] = 0;
+            if (c < sp.nch) {
+                sp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && sp.ok;
+                const int rc0 = r + c * RC;
+                const int n = (r + nset - rc0 < RC) ? (r + nset - rc0) : RC;
+                cb[c] = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
+                const unsigned cdrel = (unsigned)(n * K) + (unsigned)(reinterpret_cast<uintptr_t>(Wd + (size_t)rc0 * nb) & 15);
+#pragma unroll
+                for (int k = 0; k < DEC_ILP; k++) {
+                    const int i = warp + k * DEC_CWARPS - c * RC;       // row k of this warp, relative to chunk c
+                    if (c == 0) drel[k] = cdrel;                        // (unused slots point at valid memory)
+                    if (i >= 0 && i < n) {
+                        qrel[k] = (unsigned)(i * K);
+                        drel[k] = cdrel + (unsigned)(i * nb * 2);
+                        ck |= (unsigned)c << (8 * k);
+                    }
+                }
+                R2.advance();
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < DEC_ILP; k++) {
+            const unsigned c = (ck >> (8 * k)) & 0xffu;
+            unsigned base = cb[0];
+#pragma unroll
+            for (int cc = 1; cc < DEC_MAXCH; cc++)
+                if (c == (unsigned)cc) base = cb[cc];
+            sp.rs.q[k] = base + qrel[k];
+            sp.rs.d[k] = base + drel[k];
+        }
+        if (memo_mode == 1 && lane == 0) {
+#pragma unroll
+            for (int k = 0; k < DEC_ILP; k++) { memo[k] = qrel[k]; memo[4 + k] = drel[k]; }
+            memo[8] = ck; memo[9] = (unsigned)sp.nset; memo[10] = (unsigned)sp.nch; memo[11] = (unsigned)sp.nv;
+        }
     }
     sp.add = 0.0f;
     if (lane < sp.nv) {
@@ -411,7 +466,14 @@ __device__ __forceinline__ void seg_finish(int epi, const SegPlan& sp, Ring& R, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const lt_decode_desc& P = *C.P;
     float v = 0.0f;
-    if (sp.ok && sp.nv > 0) v = fold_rows<DEC_ILP>(sp.rs, K >> 5, sp.nv, smem_u32(sXq), smem_u32(sXd));
+    if (sp.ok && sp.nv == 1) {
+        // one long row per warp (down): its rounds' loads and block dots all in flight, only the fma chain is serial
+        RowSetN<1> r1;
+        r1.q[0] = sp.rs.q[0]; r1.d[0] = sp.rs.d[0];
+        v = fold_rows<1>(r1, K >> 5, 1, smem_u32(sXq), smem_u32(sXd));
+    } else if (sp.ok && sp.nv > 0) {
+        v = fold_rows<DEC_ILP>(sp.rs, K >> 5, sp.nv, smem_u32(sXq), smem_u32(sXd));
+    }
     // the stages are no longer read: hand them back before the epilogue
     __syncwarp();
     for (int c = 0; c < sp.nch; c++) {
@@ -669,18 +731,19 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     {
         const unsigned wq = smem_u32(A.big);
         const unsigned wd = wq + (unsigned)(2 * HD * E);
-        for (int i0 = warp; i0 < 2 * HD && wok; i0 += DEC_CWARPS * DEC_ILP) {
+        constexpr int AILP = 5;     // 2*hd = 128 rows over 15 warps: two passes of up to 5 rows
+        for (int i0 = warp; i0 < 2 * HD && wok; i0 += DEC_CWARPS * AILP) {
             const int left = (2 * HD - i0 + DEC_CWARPS - 1) / DEC_CWARPS;
-            const int nv = left < DEC_ILP ? left : DEC_ILP;
-            RowSet rs;
+            const int nv = left < AILP ? left : AILP;
+            RowSetN<AILP> rs;
 #pragma unroll
-            for (int k = 0; k < DEC_ILP; k++) {
+            for (int k = 0; k < AILP; k++) {
                 int i = i0 + k * DEC_CWARPS;
                 if (i >= 2 * HD) i = 2 * HD - 1;
                 rs.q[k] = wq + (unsigned)(i * E);
                 rs.d[k] = wd + (unsigned)(i * nb * 2);
             }
-            float v = fold_rows<DEC_ILP>(rs, nb, nv, smem_u32(A.xq0), smem_u32(A.xd0));
+            float v = fold_rows<AILP>(rs, nb, nv, smem_u32(A.xq0), smem_u32(A.xd0));
             const int i = i0 + lane * DEC_CWARPS;
             if (lane < nv) {
                 if (ly->qkv_bias != nullptr) v = __fadd_rn(v, S->bias[i]);
@@ -985,7 +1048,13 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         FfnPlan fp;
         if (ph == 2) fp = ffn_prepare(R, (const __half*)ly->gu_d, F, b0, b1 - b0 < 2 ? b1 - b0 : 2, E, C);
         const int RC = lm ? rows_per_chunk_lm(K) : rows_per_chunk(K);
-        if (ph != 2) sp = seg_prepare(epi, R, Wd, r0, r0, r1, K, RC, C);
+        // recurring sets take their plan from the memo: the layer phases from the second layer on, the
+        // full sets of the LM head from its second set on
+        const int kind = lm ? 3 : (ph == 0 ? 0 : (ph == 1 ? 1 : 2));
+        const int full_lm = DEC_CWARPS * DEC_ILP;
+        if (ph != 2) sp = seg_prepare(epi, R, Wd, r0, r0, r1, K, RC, C, S->memo[kind][warp],
+                                      lm ? (r1 - r0 >= full_lm && 2 * RC == full_lm && (RC * (K >> 5) * 2) % 16 == 0 ? 1 : 0)
+                                         : (il == 0 ? 1 : 2));
         float nwr[DEC_XB / 2];
         if (ph & 1) {
             const float* nw = ph == 1 ? ly->ffn_norm : (il + 1 < L ? lys[il + 1].attn_norm : P.out_norm);
@@ -1027,7 +1096,9 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
                 seg_finish(epi, sp, R, K, sXq, sXd, C);
                 const int r = sp.r + sp.nset;
                 if (r >= r1) break;
-                sp = seg_prepare(epi, R, Wd, r0, r, r1, K, RC, C);
+                sp = seg_prepare(epi, R, Wd, r0, r, r1, K, RC, C, S->memo[kind][warp],
+                                 (lm && r1 - r >= full_lm && 2 * RC == full_lm && r1 - r0 >= full_lm &&
+                                  (RC * (K >> 5) * 2) % 16 == 0) ? 2 : 0);
             }
         }
         C.tr.stamp(25 + ph);
@@ -1195,6 +1266,13 @@ static int decode_check(const lt_decode_desc* d, DecodeGeometry* g) {
                    "lt_decode_step: weights and caches of layer %d must be 16-byte aligned", il);
     }
     LT_REQUIRE(aligned16(d->lm_q), "lt_decode_step: the LM-head matrix must be 16-byte aligned");
+    for (int il = 1; il < d->n_layers; il++) {
+        const lt_decode_layer *a = d->h_layers, *b = d->h_layers + il;
+        // (the kernel remembers where a warp's rows lie in a ring stage from the first layer on)
+        LT_REQUIRE(((uintptr_t)a->qkv_d & 15) == ((uintptr_t)b->qkv_d & 15) && ((uintptr_t)a->o_d & 15) == ((uintptr_t)b->o_d & 15) &&
+                       ((uintptr_t)a->down_d & 15) == ((uintptr_t)b->down_d & 15) && (a->qkv_bias == nullptr) == (b->qkv_bias == nullptr),
+                   "lt_decode_step: the scale arrays of layer %d are aligned differently from layer 0's", il);
+    }
     int rc = decode_geometry(d, g);
     if (rc != LT_OK) return rc;
     if (d->nh + 1 > g->ctas || nk > 64 * (g->ctas - d->nh)) {

@@ -263,8 +263,10 @@ k_q8_gemv1(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const v
                 if (ok) {
                     if (Resid != nullptr) a = __fadd_rn(Resid[row], a);
                     Y[row] = a;
-                    const_cast<unsigned*>(rowctr)[row] = num;
                 }
+                // the exchange is counted whether or not it completed: every rank pushed this row with this
+                // number, so the ranks' numbers must stay in step after a wait that gave up
+                const_cast<unsigned*>(rowctr)[row] = num;
             }
         }
     }
@@ -320,6 +322,78 @@ static int gemv_grid(long row_groups) {
     long cap = (long)sms * 8;  // up to 8 resident CTAs of 256 threads per SM
     return (int)(ctas > cap ? cap : ctas);
 }
+
+// Lane-subset GEMV for a tensor-parallel row split that keeps the bits of one GPU.  A group of g ranks
+// deals the Q8_0 blocks of a row round-robin: rank r holds blocks b = r (mod g), i.e. exactly the blocks of
+// the contract's lanes L = r (mod g).  In the rank's local matrix (blocks j = (b - r) / g) the chain of
+// lane L = r + g*m is blocks j = m, m + 32/g, m + 2*32/g, ...: the contract with LN = 32/g lanes.  The tree
+// levels s >= g pair lanes of one rank (local levels s/g = LN/2 .. 1); the levels s < g pair ranks and are
+// done by whoever sums the partials, in the order p[t] + p[t + s] for s = g/2 .. 1.  A warp folds G rows at
+// once (LN lanes per row).  Y[t*M + n] = the rank's partial of (row n, column t).
+template <int G>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_q8_gemv_lanes(const int8_t* __restrict__ Wq, const __half* __restrict__ Wd, const int8_t* __restrict__ Xq,
+                const __half* __restrict__ Xd, float* __restrict__ Y, int M, int K, int T) {
+    constexpr int LN = 32 / G;
+    const int nb = K >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LN, m = lane % LN;
+    const long warps_total = (long)gridDim.x * GEMV_WARPS;
+    chain_release();
+    chain_wait();
+    for (long rg = (long)blockIdx.x * GEMV_WARPS + warp; rg * G < M; rg += warps_total) {
+        const long row = rg * G + sub;
+        const bool live = row < M;
+        for (int t = 0; t < T; t++) {
+            float acc = 0.0f;
+            if (live) {
+                const int8_t* wrow = Wq + row * K;
+                const __half* drow = Wd + row * nb;
+                const int8_t* xrow = Xq + (long)t * K;
+                const __half* xdrow = Xd + (long)t * nb;
+                int j = m;
+                for (; j + 3 * LN < nb; j += 4 * LN) {       // four blocks of the chain in flight
+                    int4 w0[4], w1[4];
+                    unsigned short wd[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int8_t* p = wrow + (long)(j + u * LN) * 32;
+                        w0[u] = ld_stream_v4(p); w1[u] = ld_stream_v4(p + 16);
+                        wd[u] = ld_stream_u16(drow + j + u * LN);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int4* xp = (const int4*)(xrow + (long)(j + u * LN) * 32);
+                        const int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                        acc = q8_accum(__half2float(__ushort_as_half(wd[u])), __half2float(__ldg(xdrow + j + u * LN)),
+                                       block_dot(w0[u], w1[u], x0, x1), acc);
+                    }
+                }
+                for (; j < nb; j += LN) {
+                    const int8_t* p = wrow + (long)j * 32;
+                    const int4 w0 = ld_stream_v4(p), w1 = ld_stream_v4(p + 16);
+                    const int4* xp = (const int4*)(xrow + (long)j * 32);
+                    const int4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                    acc = q8_accum(__half2float(__ushort_as_half(ld_stream_u16(drow + j))), __half2float(__ldg(xdrow + j)),
+                                   block_dot(w0, w1, x0, x1), acc);
+                }
+            }
+#pragma unroll
+            for (int s = LN / 2; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, s, LN));
+            if (live && m == 0) Y[(long)t * M + row] = acc;
+        }
+    }
+}
+
+template <int G>
+static int launch_gemv_lanes(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, float* Y, int M,
+                             int K, int T, cudaStream_t s) {
+    const int ctas = gemv_grid(((long)M + G - 1) / G);
+    const cudaError_t e = launch_chained(k_q8_gemv_lanes<G>, dim3((unsigned)ctas), dim3(GEMV_THREADS), 0, s, Wq,
+                                         (const __half*)Wd, Xq, (const __half*)Xd, Y, M, K, T);
+    return check_launch("lt_q8_gemv_lanes", 1, e);
+}
+
 
 template <int TW>
 static int launch_gemm_wide(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd,
@@ -383,8 +457,25 @@ static int launch_gemv1(const int8_t* Wq, const uint16_t* Wd, const void* Xq, co
         st = device_status_ptr();
         LT_REQUIRE(st != nullptr, "lt_q8_gemv_allreduce: status word unavailable");
     }
-    const cudaError_t e = launch_chained(k_q8_gemv1<R, U, MODE>, dim3((unsigned)ctas), dim3(GEMV_THREADS), smem, s, Wq,
-                                         (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K, C, st);
+    cudaError_t e;
+    if (MODE == GEMV_ALLREDUCE) {
+        // warps of different ranks wait for each other's rows: every CTA must be resident, which only a
+        // cooperative launch guarantees (the grid is at most one wave by construction)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ctas);
+        cfg.blockDim = dim3(GEMV_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeCooperative;
+        at[0].val.cooperative = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, k_q8_gemv1<R, U, MODE>, Wq, (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K, C, st);
+    } else {
+        e = launch_chained(k_q8_gemv1<R, U, MODE>, dim3((unsigned)ctas), dim3(GEMV_THREADS), smem, s, Wq,
+                           (const __half*)Wd, Xq, Xd, eps, Resid, Y, M, K, C, st);
+    }
     return check_launch("lt_q8_gemv", 1, e);
 }
 
@@ -445,6 +536,24 @@ extern "C" int lt_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq
         if (rc != LT_OK) return rc;
     }
     return LT_OK;
+}
+
+extern "C" int lt_q8_gemv_lanes(const int8_t* Wq, const uint16_t* Wd, const int8_t* Xq, const uint16_t* Xd, float* Y, int M,
+                                int K, int T, int group, void* stream) {
+    LT_REQUIRE(Wq && Wd && Xq && Xd && Y, "lt_q8_gemv_lanes: null pointer");
+    LT_REQUIRE(M > 0 && T > 0, "lt_q8_gemv_lanes: M=%d T=%d must be positive", M, T);
+    LT_REQUIRE(K > 0 && K % 32 == 0, "lt_q8_gemv_lanes: K=%d must be a positive multiple of 32", K);
+    LT_REQUIRE(aligned16(Wq) && aligned16(Xq), "lt_q8_gemv_lanes: Wq and Xq must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (group) {
+        case 1: return launch_gemv_lanes<1>(Wq, Wd, Xq, Xd, Y, M, K, T, s);
+        case 2: return launch_gemv_lanes<2>(Wq, Wd, Xq, Xd, Y, M, K, T, s);
+        case 4: return launch_gemv_lanes<4>(Wq, Wd, Xq, Xd, Y, M, K, T, s);
+        case 8: return launch_gemv_lanes<8>(Wq, Wd, Xq, Xd, Y, M, K, T, s);
+        default: break;
+    }
+    set_error("lt_q8_gemv_lanes: group=%d must be 1, 2, 4 or 8", group);
+    return LT_ERR_INVALID;
 }
 
 extern "C" int lt_rmsnorm_q8_gemv(const int8_t* Wq, const uint16_t* Wd, const float* X, const float* normw, float eps,

@@ -13,6 +13,7 @@ turns off name code paths that do not exist here and are refused.
 Reference lines for each function are given in its docstring.
 """
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -710,8 +711,9 @@ def _compute_folded_logits(w, cfg, E):
 # the per-op launches and is the parity baseline.
 _FUSED_STEP = "persistent"
 # pause (ns) between two looks at hand-over words that have not arrived yet, in the one-kernel step
-_POLL_NS = 0
-_POLL_LOOKS = 1
+_POLL_NS = int(os.environ.get("LLAMATOV_POLL_NS", "0"))
+# copies of the hand-over buffers in use (each SM polls copy SM % n): 1 .. lt_decode_ws_replicas()
+_POLL_LOOKS = int(os.environ.get("LLAMATOV_WS_COPIES", "1"))
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -871,8 +873,16 @@ class GraphRunner:
         torch.cuda.synchronize()
         n0 = _lib.launch_count()
         self.fused = bool(_FUSED_STEP)
+        self._tok_in = None
         if self.fused:
-            self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv)
+            # When the embedding table is a Q8_0 table (dequantising its blocks reproduces the rows the host
+            # lookup returns), the captured step gathers the row itself from a token id in device memory: a
+            # replay then uploads 4 bytes instead of looking the row up and dequantising it on the host.
+            if self._q8_exact_table(int(tok.reshape(-1)[0])):
+                self._tok_in = torch.zeros(1, dtype=torch.int32, device="cuda")
+                self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv, tok_ptr=self._tok_in.data_ptr())
+            else:
+                self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv)
             with torch.cuda.graph(g, stream=self.stream):
                 self._step_host.launch()
         else:
@@ -885,18 +895,48 @@ class GraphRunner:
         self.graph = g
         self.captured = True
 
+    def _q8_exact_table(self, probe_tok):
+        """True if token_embd.weight is exactly representable as Q8_0 (checked on sample rows); uploads it."""
+        emb = _np(self.w["token_embd.weight"])
+        before = (frozenset(_DEV_CONST.keys()), frozenset(fd._DEV_WEIGHT_CACHE.keys()), frozenset(fd._Q8_WEIGHT_CACHE.keys()))
+        Wq, Wd, V, K = fd._quantize_weight_q8_0(emb)
+        if K != self.E:
+            return False
+        nb = K // 32
+        for t in (0, V // 2, V - 1, int(probe_tok) % V):
+            deq = (Wq[t * K:(t + 1) * K].astype(np.float32).reshape(nb, 32) *
+                   Wd[t * nb:(t + 1) * nb].astype(np.float32).reshape(nb, 1)).reshape(K)
+            if not np.array_equal(deq, _embedding_row(self.w, t, K)):
+                return False
+        _weights(emb)       # an untied table is not used by the host-row step: upload it now
+        if hasattr(self, "_weight_cache_frozen") and before == self._weight_cache_frozen:
+            self._weight_cache_frozen = (frozenset(_DEV_CONST.keys()), frozenset(fd._DEV_WEIGHT_CACHE.keys()),
+                                         frozenset(fd._Q8_WEIGHT_CACHE.keys()))
+        return True
+
+    def input_bytes_per_replay(self):
+        """Host-to-device bytes a replay uploads: the token id, or the embedding row."""
+        return 4 if getattr(self, "_tok_in", None) is not None else self.E * 4
+
     def _launch(self, tok):
         assert self.captured, "call capture() before replay"
-        row = _embedding_row(self.w, int(tok), self.E)
         if getattr(self, "_pin_row", None) is None:     # page-locked staging: the copies below are truly asynchronous
             self._pin_row = torch.empty(self.E, dtype=torch.float32).pin_memory()
             self._pin_row_np = self._pin_row.numpy()
             self._pin_idx = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._pin_idx_np = self._pin_idx.numpy()
-        np.copyto(self._pin_row_np, row)
-        with torch.cuda.stream(self.stream):
-            _memcpy_htod(_RESID_IN.ptr, self._pin_row_np, self.E * 4)
-            self.graph.replay()
+            self._pin_tok = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._pin_tok_np = self._pin_tok.numpy()
+        if self._tok_in is not None:
+            self._pin_tok_np[0] = int(tok)
+            with torch.cuda.stream(self.stream):
+                _memcpy_htod(ctypes.c_void_p(self._tok_in.data_ptr()), self._pin_tok_np, 4)
+                self.graph.replay()
+        else:
+            np.copyto(self._pin_row_np, _embedding_row(self.w, int(tok), self.E))
+            with torch.cuda.stream(self.stream):
+                _memcpy_htod(_RESID_IN.ptr, self._pin_row_np, self.E * 4)
+                self.graph.replay()
         for c in self.kv:
             c.length += 1
 
@@ -953,6 +993,13 @@ class GraphRunner:
             c.length = n
         self._assert_weight_cache_frozen()
         self.loop_graph = g
+
+    def reset_device_loop(self, first_tok):
+        """Start the device loop over: next replay consumes `first_tok`, the token history is empty."""
+        self.stream.synchronize()
+        self._tok_dev.fill_(int(first_tok))
+        self._step.zero_()
+        torch.cuda.synchronize()
 
     def replay_device(self, n):
         """n decode steps back to back on the device; no host work between them."""

@@ -103,8 +103,9 @@ def run_gemv_sweep(args):
     for (M, K) in shapes:
         nb = K // 32
         wbytes = M * nb * 34
-        # steady state: enough distinct copies of the matrix that consecutive launches cannot hit L2
-        R = int(max(1, min(64, np.ceil(2.5 * L2_BYTES / wbytes))))
+        # steady state: enough distinct copies of the matrix that consecutive launches cannot hit L2 (the copies
+        # together are 2.5 x L2 at least, however small the matrix is)
+        R = int(max(2, np.ceil(2.5 * L2_BYTES / wbytes)))
         Wq = torch.randint(-127, 128, (R, M * K), dtype=torch.int8, device="cuda")
         Wd = (torch.rand((R, M * nb), device="cuda") * 0.02).to(torch.float16).view(torch.int16)
         for T in args.batch:
@@ -121,8 +122,7 @@ def run_gemv_sweep(args):
             torch.cuda.synchronize()
             # steady state: a captured chain of launches over the rotating copies, so that the host's
             # launch rate does not enter (small shapes run for ~2 us)
-            chain = int(max(R, min(256, 2e9 // max(wbytes, 1))))
-            chain = max(R, (chain // R) * R)
+            chain = R if R >= 256 else max(R, (int(min(256, 2e9 // max(wbytes, 1))) // R) * R)
             side = torch.cuda.Stream()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
@@ -144,8 +144,23 @@ def run_gemv_sweep(args):
                 torch.cuda.synchronize()
                 cold.append(e0.elapsed_time(e1))
             del flush
+            # grouped form: ONE launch over the R distinct matrices (they lie back to back, so the launch is the
+            # GEMV of the stacked [R*M, K] matrix): what the kernel sustains on this row length when launch
+            # latency and the ramp / tail of a tiny grid do not enter
+            yg = torch.empty(T * R * M, dtype=torch.float32, device="cuda")
+
+            def run_grouped(i):
+                _lib.call("lt_q8_gemv", Wq.data_ptr(), Wd.data_ptr(), xq.data_ptr(), xd.data_ptr(), None,
+                          yg.data_ptr(), R * M, K, T, _stream())
+            for i in range(3):
+                run_grouped(i)
+            torch.cuda.synchronize()
+            gms = _event_ms(run_grouped, 5) / R
+            del yg
             b = gemv_bytes(M, K, T)
             print(json.dumps({"M": M, "K": K, "batch": T, "algorithmic_bytes": b,
+                              "grouped_us_per_matrix": gms * 1e3, "grouped_GBs": b / (gms * 1e-3) / 1e9,
+                              "grouped_frac_of_hbm": b / (gms * 1e-3) / 1e9 / hbm,
                               "steady_us": ms * 1e3, "steady_GBs": b / (ms * 1e-3) / 1e9,
                               "steady_frac_of_hbm": b / (ms * 1e-3) / 1e9 / hbm,
                               "alone_cold_us": float(np.median(cold)) * 1e3,

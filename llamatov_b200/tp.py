@@ -9,6 +9,13 @@ sequence (dev_residency.py:1381-1477) for models too large to be worth running o
                              the partial sums meet in an all-reduce (sum) of [batch, hidden] fp32;
                              rank order of the sum is fixed, every rank gets the same bits.  The
                              association differs from one GPU's single fold: tolerance class.
+  exact row split of down:   the Q8_0 blocks of the FFN dimension are dealt round-robin over the ranks
+                             (rank r: blocks b = r mod g, gate|up rows dealt to match), so a rank holds
+                             whole lanes of the GEMV contract (lane = block mod 32): its partial is the
+                             contract's lane chains plus the tree levels that stay inside the rank
+                             (lt_q8_gemv_lanes), and the all-reduce adds the partials in the order of the
+                             tree's last levels (lt_allreduce_add_tree): the bits of one GPU at the same
+                             bytes on the wire.  For up to 8 sequences per step (the GEMV path).
   attention / KV cache:      head-parallel, every rank caches only its KV heads; no exchange.
   next token:                local (max, index) per sequence, all-gather, lowest index wins ties.
 
@@ -60,6 +67,16 @@ class ShardPlan:
     def down_cols(self, rank):
         return rank * self.F_l, (rank + 1) * self.F_l
 
+    # ---- exact row split of down: Q8_0 blocks dealt round-robin
+    def ffn_blocks(self, rank):
+        """Blocks (32 FFN columns each) of rank `rank`: b = rank mod world."""
+        return list(range(rank, self.F // 32, self.world))
+
+    def gateup_rows_dealt(self, rank):
+        """Row ranges of the fused [2F, E] matrix: the gate rows, then the up rows, of the rank's blocks."""
+        bl = self.ffn_blocks(rank)
+        return [(32 * b, 32 * b + 32) for b in bl] + [(self.F + 32 * b, self.F + 32 * b + 32) for b in bl]
+
     def vocab_rows(self, rank):
         return min(self.V, rank * self.V_l), min(self.V, (rank + 1) * self.V_l)
 
@@ -75,6 +92,12 @@ def combine_argmax(vals, idxs):
 def take_rows(Wq, Wd, K, ranges):
     """Rows of a Q8_0 matrix given as tensors Wq [N, K] int8, Wd [N, K/32]."""
     return (torch.cat([Wq[a:b] for a, b in ranges]).contiguous(), torch.cat([Wd[a:b] for a, b in ranges]).contiguous())
+
+
+def take_blocks(Wq, Wd, first, step):
+    """Blocks first, first + step, ... of every row."""
+    N, K = Wq.shape
+    return (Wq.view(N, K // 32, 32)[:, first::step, :].reshape(N, -1).contiguous(), Wd[:, first::step].contiguous())
 
 
 def take_cols(Wq, Wd, k0, k1):
@@ -130,8 +153,19 @@ class P2PComm:
         _lib.call("lt_allreduce_add", ctypes.byref(self.c), part.data_ptr(), None if resid is None else resid.data_ptr(),
                   out.data_ptr(), n, _stream())
 
-    def free(self):
-        _lib.call("lt_comm_free", ctypes.byref(self.c))
+    def allreduce_add_tree(self, part, resid, out, n):
+        """The same with the partials summed in the lane tree's order (exact row split, lt_q8_gemv_lanes)."""
+        _lib.call("lt_allreduce_add_tree", ctypes.byref(self.c), part.data_ptr(), None if resid is None else resid.data_ptr(),
+                  out.data_ptr(), n, _stream())
+
+    def free(self, group=None):
+        """No kernel of any rank may still be storing into the buffers: device sync, host barrier, then free."""
+        import torch.distributed as dist
+        if self.c.local_stage:
+            torch.cuda.synchronize()
+            if dist.is_initialized() and self.c.world > 1:
+                dist.barrier(group=group)
+            _lib.call("lt_comm_free", ctypes.byref(self.c))
 
 
 class _W:
@@ -151,7 +185,7 @@ class TPDecoder:
     """
 
     def __init__(self, cfg, rank=0, world=1, batch=1, max_seq=4352, seed=0, group=None, device=None, model=None,
-                 comm="nccl", attn_split=0, chained=False, fused_allreduce=True):
+                 comm="nccl", attn_split=0, chained=False, fused_allreduce=True, exact_split=False):
         self.chained = bool(chained)
         self.fused_rope = True            # split order: rope + append inside the range kernel
         self.fused_allreduce = bool(fused_allreduce)     # comm="p2p", one sequence: all-reduce inside the GEMV
@@ -160,6 +194,8 @@ class TPDecoder:
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.plan = p = ShardPlan(cfg, world)
         E, L = p.E, cfg["n_layers"]
+        # exact row split of down (blocks dealt round-robin): world a power of two up to 8, GEMV path
+        self.exact = bool(exact_split) and world in (2, 4, 8) and self.B <= 8 and (p.F // 32) % world == 0
         f32 = dict(dtype=torch.float32, device=self.dev)
         if model is not None:
             src = self._from_model(model)
@@ -174,9 +210,9 @@ class TPDecoder:
             o = _W(*take_cols(Wq, Wd, *p.o_cols(rank)))
             fn = next(src)
             Wq, Wd = next(src)
-            gu = _W(*take_rows(Wq, Wd, E, p.gateup_rows(rank)))
+            gu = _W(*take_rows(Wq, Wd, E, p.gateup_rows_dealt(rank) if self.exact else p.gateup_rows(rank)))
             Wq, Wd = next(src)
-            down = _W(*take_cols(Wq, Wd, *p.down_cols(rank)))
+            down = _W(*(take_blocks(Wq, Wd, rank, world) if self.exact else take_cols(Wq, Wd, *p.down_cols(rank))))
             del Wq, Wd
             self.layers.append(dict(attn_norm=an, qkv=qkv, o=o, ffn_norm=fn, gateup=gu, down=down))
         self.out_norm = next(src)
@@ -197,6 +233,7 @@ class TPDecoder:
         self.tok = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self.x = torch.empty((B, E), **f32); self.x1 = torch.empty((B, E), **f32)
         self.h = torch.empty((B, E), **f32); self.part = torch.empty((B, E), **f32)
+        self.gpart = torch.empty((world, B, E), **f32) if (self.exact and comm == "nccl") else None
         self.qkv = torch.empty((B, p.nq_l + 2 * p.nk_l), **f32)
         self.att = torch.empty((B, p.nq_l), **f32)
         self.gu = torch.empty((B, 2 * p.F_l), **f32)
@@ -319,12 +356,26 @@ class TPDecoder:
             torch.distributed.all_reduce(t, group=self.group)
             self.allreduce_calls += 1
 
-    def _row_split(self, W, resid, out):
+    def _row_split(self, W, resid, out, exact=False):
         """out = resid + sum over ranks of (W_rank . x_rank): one fold on one rank (the residual rides
-        in the GEMV store, the reference's add-residual form); an all-reduce of partials otherwise."""
+        in the GEMV store, the reference's add-residual form); an all-reduce of partials otherwise.
+        exact: W holds this rank's round-robin blocks; lane partials, summed in the lane tree's order."""
         B, E = self.B, self.plan.E
         if self.world == 1:
             self._gemm(W, out, B, resid, E)
+        elif exact:
+            _lib.call("lt_q8_gemv_lanes", W.q.data_ptr(), W.d.data_ptr(), self.xq.data_ptr(), self.xd.data_ptr(),
+                      self.part.data_ptr(), W.N, W.K, B, self.world, _stream())
+            if self.comm is not None:
+                self.comm.allreduce_add_tree(self.part, resid, out, B * E)
+            else:
+                torch.distributed.all_gather_into_tensor(self.gpart.view(-1), self.part.view(-1), group=self.group)
+                s = self.world // 2
+                while s >= 1:       # p[t] + p[t + s], s = world/2 .. 1 (IEEE fp32 adds)
+                    self.gpart[:s] = self.gpart[:s] + self.gpart[s:2 * s]
+                    s //= 2
+                _lib.call("lt_add", resid.data_ptr(), self.gpart[0].data_ptr(), out.data_ptr(), B * E, _stream())
+            self.allreduce_calls += 1
         elif self.comm is not None and B == 1 and self.fused_allreduce:
             # one sequence: the partial rows are exchanged by the GEMV itself
             _lib.call("lt_q8_gemv_allreduce", ctypes.byref(self.comm.c), W.q.data_ptr(), W.d.data_ptr(),
@@ -370,7 +421,7 @@ class TPDecoder:
                 self._norm_gemm(self.x1, ly["ffn_norm"], ly["gateup"], self.gu)
                 _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
                           self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
-                self._row_split(ly["down"], self.x1, self.x)
+                self._row_split(ly["down"], self.x1, self.x, exact=self.exact)
                 continue
             _lib.call("lt_rope_append_batch", self.qkv.data_ptr(), qld, p.nh_l, p.nkv_l, hd, theta,
                       self.kc[il].data_ptr(), self.vc[il].data_ptr(), lens.data_ptr(), self.max_seq, B,
@@ -389,7 +440,7 @@ class TPDecoder:
             self._norm_gemm(self.x1, ly["ffn_norm"], ly["gateup"], self.gu)
             _lib.call("lt_silu_mul_quant_rows", self.gu.data_ptr(), self.gu.data_ptr() + p.F_l * 4, 2 * p.F_l,
                       self.xq.data_ptr(), self.xd.data_ptr(), p.F_l, B, st())
-            self._row_split(ly["down"], self.x1, self.x)
+            self._row_split(ly["down"], self.x1, self.x, exact=self.exact)
         self._norm_gemm(self.x, self.out_norm, self.lm, self.logits)
         nv = self.lm.N
         stride = _lib.lib().lt_argmax_scratch_bytes() // 4
@@ -426,7 +477,8 @@ class TPDecoder:
         return g
 
     def run(self, steps):
-        """`steps` decode steps (graph replays when captured); returns the tokens [steps, B] on the host."""
+        """`steps` decode steps (graph replays when captured); returns the tokens [steps, B] on the host.
+        Raises if a device wait gave up or a bound was hit during the run (the tokens would be garbage)."""
         out = []
         for _ in range(steps):
             if self.graph is not None:
@@ -435,4 +487,14 @@ class TPDecoder:
                 self.step()
             out.append(self.tok.clone())
         torch.cuda.synchronize()
+        st = _lib.device_status()
+        if st:
+            raise RuntimeError(f"TPDecoder.run: device status {sorted(st)} (rank {self.rank})")
         return torch.stack(out).cpu().numpy()
+
+    def close(self):
+        """Release what lives outside torch's allocator (the peer-mapped staging buffers); every rank calls it."""
+        self.graph = None
+        if self.comm is not None:
+            self.comm.free(self.group)
+            self.comm = None

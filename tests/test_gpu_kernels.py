@@ -95,6 +95,37 @@ def test_gemv_lm_head_shape(oracle):
     assert np.array_equal(bits(y), bits(want))
 
 
+@pytest.mark.parametrize("M,K", [(14336, 4096), (128256, 4096), (4096, 14336)])
+def test_gemv_llama_shapes_bit_exact(oracle, M, K):
+    """The Llama-3-8B-architecture shapes of the sweep at one column, against the CPU oracle (rows sampled for
+    the vocabulary-sized matrix so that the oracle stays within seconds; the GPU computes all rows)."""
+    Wq, Wd, x = synth.gemv_case(M, K, seed=3)
+    xq, xd = gpu_quant(x[0])
+    y = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, M, K))
+    oq, od = oracle.quant_q8(x[0])
+    nb = K // 32
+    if M > 20000:
+        rows = np.unique(np.concatenate([np.arange(0, 64), np.arange(M - 64, M),
+                                         np.random.default_rng(0).integers(0, M, size=4096)]))
+        Wq_s = np.ascontiguousarray(Wq.reshape(M, K)[rows]).reshape(-1)
+        Wd_s = np.ascontiguousarray(Wd.reshape(M, nb)[rows]).reshape(-1)
+        want = oracle.q8_gemv(Wq_s, Wd_s, oq, od, len(rows), K)
+        assert np.array_equal(bits(y[rows]), bits(want))
+    else:
+        assert np.array_equal(bits(y), bits(oracle.q8_gemv(Wq, Wd, oq, od, M, K)))
+
+
+@pytest.mark.parametrize("T", [4, 16, 64])
+def test_skinny_gemm_wide_matrix_bit_exact(oracle, T):
+    """Batches of 4, 16 and 64 columns on a 4096-row matrix (dp4a path and tensor-core path)."""
+    M, K = 4096, 4096
+    Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=40 + T)
+    xq, xd = gpu_quant(x, rows=T)
+    y = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, M, K, T=T)).reshape(T, M)
+    want = oracle.q8_gemm(Wq, Wd, host(xq), host(xd, np.uint16), M, K, T)
+    assert np.array_equal(bits(y), bits(want))
+
+
 @pytest.mark.parametrize("T", [2, 3, 4, 8, 16, 33, 64, 70])
 @pytest.mark.parametrize("M,K", [(896, 896), (300, 4864), (200, 1056)])
 def test_skinny_gemm_bit_exact(oracle, M, K, T):

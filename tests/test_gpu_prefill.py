@@ -48,6 +48,48 @@ def test_batched_prefill_equals_token_by_token(arch, T):
     assert _lib.device_status() == set()
 
 
+@pytest.mark.parametrize("batch", [1, 8])
+def test_qwen05b_prefill_2048_tokens_equals_token_by_token_on_a_sample(batch):
+    """BASELINE config 3 at its stated size: Qwen2.5-0.5B architecture (depth cut to 4 layers so that the
+    token-by-token arm, 2048 decode steps, stays within the test budget; every operator runs at the full
+    widths and the full 2048 rows), batch 1 and batch 8.  Batched prefill against the reference's way
+    (one token at a time through the decode step): last-position logits bit-equal, and 64 sampled KV rows
+    of every layer bit-equal, for the first and the last sequence of the batch."""
+    T = 2048
+    m, w, cfg = _fresh("qwen2.5-0.5b", seed=0, n_layers=4)
+    V = m["cfg"]["vocab"]
+    rng = np.random.default_rng(batch)
+    prompts = rng.integers(0, V, size=(batch, T))
+    dr._KV_MAX_SEQ = T
+    try:
+        kvs = [[None] * cfg["n_layers"] for _ in range(batch)]
+        lb = prefill.prefill_resident(w, cfg, torch.from_numpy(prompts.astype(np.int64)), kvs).reshape(batch, -1).numpy().copy() \
+            if batch > 1 else prefill_chunks(w, cfg, prompts[0], kvs[0])
+        rows = np.sort(rng.choice(T, size=64, replace=False))
+        for s in sorted({0, batch - 1}):
+            la, kva = _prefill(w, cfg, prompts[s].tolist(), batched=False, max_seq=T)
+            got = lb[s] if batch > 1 else lb
+            assert np.array_equal(bits(la), bits(got)), s
+            for ca, cb in zip(kva, kvs[s]):
+                assert ca.length == cb.length == T
+                assert np.array_equal(bits(ca.k_slice_host()[rows]), bits(cb.k_slice_host()[rows]))
+                assert np.array_equal(bits(ca.v_slice_host()[rows]), bits(cb.v_slice_host()[rows]))
+            for c in kva:
+                c.free()
+        assert _lib.device_status() == set()
+    finally:
+        dr._KV_MAX_SEQ = 256
+
+
+def prefill_chunks(w, cfg, prompt, kv):
+    """One sequence through prefill_resident in chunks of its row capacity; returns the last logits."""
+    last = None
+    for c0 in range(0, len(prompt), prefill.MAX_ROWS):
+        last = prefill.prefill_resident(w, cfg, torch.from_numpy(np.asarray(prompt[c0:c0 + prefill.MAX_ROWS], np.int64)), kv,
+                                        want_logits=c0 + prefill.MAX_ROWS >= len(prompt))
+    return last.reshape(-1).numpy().copy()
+
+
 def test_prefill_in_two_chunks_then_decode():
     # a second chunk continues from the cache of the first; decoding afterwards continues from both
     m, w, cfg = _fresh("tiny-qwen64", seed=5)

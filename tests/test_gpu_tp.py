@@ -93,6 +93,78 @@ def test_chained_launches_give_the_same_bits(attn_split):
     assert _lib.device_status() == set()
 
 
+@pytest.mark.parametrize("g", [2, 4, 8])
+@pytest.mark.parametrize("shape", [(96, 896 * 2, 1), (64, 14336, 1), (40, 4864, 3)])
+def test_exact_row_split_partials_sum_to_the_one_gpu_bits(g, shape):
+    """The exact tensor-parallel row split, all ranks' shares computed on this one GPU: rank r holds the Q8_0
+    blocks b = r mod g of every row, lt_q8_gemv_lanes folds its lanes, and the partials added in the lane
+    tree's order (p[t] + p[t + s], s = g/2 .. 1, plain fp32 adds on the host) must equal lt_q8_gemv on the
+    whole matrix bit for bit (which the kernel tests pin to the oracle)."""
+    from tests.gpu_util import dev, gpu_gemv, gpu_quant, host, stream
+    M, K, T = shape
+    nb = K // 32
+    if nb % g:
+        pytest.skip("blocks do not deal evenly")
+    Wq, Wd, x = synth.gemv_case(M, K, T=T, seed=11 + g)
+    xq, xd = gpu_quant(x, rows=T)
+    want = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, M, K, T))
+    Wq3 = Wq.reshape(M, nb, 32); Wd2 = Wd.reshape(M, nb)
+    xq3 = host(xq).reshape(T, nb, 32); xd2 = host(xd).reshape(T, nb)
+    parts = []
+    for r in range(g):
+        wq = np.ascontiguousarray(Wq3[:, r::g, :]).reshape(-1); wd = np.ascontiguousarray(Wd2[:, r::g]).reshape(-1)
+        lxq = dev(np.ascontiguousarray(xq3[:, r::g, :]).reshape(-1)); lxd = dev(np.ascontiguousarray(xd2[:, r::g]).reshape(-1))
+        y = torch.empty(T * M, dtype=torch.float32, device="cuda")
+        _lib.call("lt_q8_gemv_lanes", dev(wq).data_ptr(), dev(wd).data_ptr(), lxq.data_ptr(), lxd.data_ptr(), y.data_ptr(),
+                  M, K // g, T, g, stream())
+        parts.append(host(y).copy())
+    s = g // 2
+    while s >= 1:
+        for t_ in range(s):
+            parts[t_] = (parts[t_] + parts[t_ + s]).astype(np.float32)
+        s //= 2
+    assert np.array_equal(parts[0].view(np.uint32), want.view(np.uint32))
+    assert _lib.device_status() == set()
+
+
+def test_exchange_wait_gives_up_and_the_context_stays_usable():
+    """A rank whose peer never delivers: the bounded waits of the all-reduce kernel and of the GEMV with the
+    all-reduce epilogue run out (about a second), the kernels return, the status word says wait_timeout, the
+    exchange counters still advance (the ranks stay in step), and the GPU keeps working.  The "peer" is a second
+    rank slot that points at this rank's own staging memory, which nobody fills: no fault, no hang."""
+    import ctypes
+    from tests.gpu_util import dev, gpu_gemv, gpu_quant, host, stream
+    c = tp._CommStruct()
+    handles = (ctypes.c_ubyte * 64)()
+    n = 1024
+    _lib.call("lt_comm_alloc", 2, n, ctypes.byref(c), handles)
+    try:
+        c.rank = 0
+        c.stage[0] = c.local_stage
+        c.stage[1] = c.local_stage            # rank 1's words are expected here and never come
+        part = torch.ones(n, device="cuda"); out = torch.zeros(n, device="cuda")
+        _lib.call("lt_allreduce_add", ctypes.byref(c), part.data_ptr(), None, out.data_ptr(), n, stream())
+        torch.cuda.synchronize()
+        assert "wait_timeout" in _lib.device_status()
+        M, K = 64, 256
+        Wq, Wd, x = synth.gemv_case(M, K, seed=1)
+        xq, xd = gpu_quant(x[0])
+        y = torch.zeros(M, device="cuda")
+        ctr0 = torch.empty(0)
+        for _ in range(2):      # twice: the second call must not find the row counters out of step with its own pushes
+            _lib.call("lt_q8_gemv_allreduce", ctypes.byref(c), dev(Wq).data_ptr(), dev(Wd).data_ptr(), xq.data_ptr(),
+                      xd.data_ptr(), None, y.data_ptr(), M, K, stream())
+            torch.cuda.synchronize()
+            assert "wait_timeout" in _lib.device_status()
+        # the context is intact: an ordinary GEMV still gives the oracle-pinned bits
+        y2 = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, M, K))
+        assert np.isfinite(y2).all() and _lib.device_status() == set()
+    finally:
+        c.stage[1] = None
+        torch.cuda.synchronize()
+        _lib.call("lt_comm_free", ctypes.byref(c))
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
@@ -111,6 +183,14 @@ def test_world2_matches_world1(tmp_path):
         rt.append(ref.tok.cpu().numpy().copy()); rl.append(ref.logits.cpu().numpy().copy())
     ref.step()                        # the warm-up step of the workers' capture()
     rmore = ref.run(3)
+    # the exact row split of `down` alone: the worker ranks run TPDecoder._row_split(exact=True) on a seeded
+    # [E, F] matrix and activation; here the same product on one GPU with lt_q8_gemv (+ residual)
+    from tests.gpu_util import dev, gpu_gemv, gpu_quant, host
+    E_, F_ = m["cfg"]["n_embd"], m["cfg"]["n_ffn"]
+    Wq, Wd, xx = synth.gemv_case(E_, F_, T=1, seed=77)
+    xq, xd = gpu_quant(xx, rows=1)
+    resid = np.random.default_rng(78).standard_normal(E_).astype(np.float32)
+    want_down = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, E_, F_, 1, resid=dev(resid)))
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), os.path.join(root, "tests", "tp_worker.py"), str(tmp_path)]
@@ -127,3 +207,6 @@ def test_world2_matches_world1(tmp_path):
         assert np.array_equal(res[k]["more"], rmore), k
         assert int(res[k]["status"]) == 0
         assert int(res[k]["p2p_equals_nccl"]) == 1
+        # exact row split of down: both exchange paths give the one-GPU bits
+        for name in ("down_exact_p2p", "down_exact_nccl"):
+            assert np.array_equal(res[k][name].view(np.uint32), want_down.view(np.uint32)), (k, name)

@@ -47,12 +47,36 @@ def main():
         lg = d.logits.cpu().numpy().copy()
         d.capture()
         one[comm] = (lg, d.run(4))
+    # the exact row split of `down`: this rank's round-robin blocks of a seeded matrix and activation
+    from tests.gpu_util import dev, gpu_quant, host
+    E_, F_ = m["cfg"]["n_embd"], m["cfg"]["n_ffn"]
+    Wq, Wd, xx = synth.gemv_case(E_, F_, T=1, seed=77)
+    xq, xd = gpu_quant(xx, rows=1)
+    resid = torch.from_numpy(np.random.default_rng(78).standard_normal(E_).astype(np.float32)).cuda()
+    nb = F_ // 32
+    tWq = torch.from_numpy(Wq.reshape(E_, F_)).cuda(); tWd = torch.from_numpy(Wd.reshape(E_, nb).view(np.int16)).cuda()
+    down = {}
+    for comm in ("p2p", "nccl"):
+        d = tp.TPDecoder(m["cfg"], rank=rank, world=world, batch=1, max_seq=64, model=m, comm=comm, exact_split=True)
+        assert d.exact
+        W = tp._W(*tp.take_blocks(tWq, tWd.view(torch.float16), rank, world))
+        d.xq[:F_ // world] = xq.view(nb, 32)[rank::world].reshape(-1)
+        d.xd[:nb // world] = xd[rank::world]
+        yout = torch.empty((1, E_), dtype=torch.float32, device="cuda")
+        d._row_split(W, resid, yout, exact=True)
+        torch.cuda.synchronize()
+        down[comm] = yout.cpu().numpy().reshape(-1).copy()
+        # ... and a few whole steps with the dealt gate|up / down shards stay finite and flag nothing
+        d.fill_cache(6, seed=5); d.set_tokens([9]); d.step(); d.step()
+        torch.cuda.synchronize()
+        assert np.isfinite(d.logits.cpu().numpy()).all()
+        d.close()
     one_same = all(np.array_equal(a, b) for a, b in zip(one["nccl"], one["p2p"]))
     status = _lib.device_status()
     same = one_same and all(np.array_equal(a, b) for a, b in zip(res["nccl"], res["p2p"]))      # two ranks: one addition, same bits
     toks, logits, more = res["p2p"]
     np.savez(os.path.join(out, f"rank{rank}.npz"), toks=toks, logits=logits, more=more, status=np.int32(len(status)),
-             p2p_equals_nccl=np.int32(same))
+             p2p_equals_nccl=np.int32(same), down_exact_p2p=down["p2p"], down_exact_nccl=down["nccl"])
     dist.barrier()
     torch.cuda.synchronize()
 
