@@ -494,6 +494,9 @@ __device__ __forceinline__ void seg_finish(int epi, const SegPlan& sp, Ring& R, 
             // residual add, then the lanes store the row's word to the copies of the buffer
             v = __fadd_rn(v, sp.add);
             float2* g = (float2*)(epi == EPI_O ? P.ws_x1 : P.ws_x);
+            if (C.S->nrep == 1) {       // one copy: lane k stores row k itself
+                if (lane < sp.nv) st_tagged(g + row, v, C.tag);
+            } else
             for (int k = 0; k < sp.nv; k++) {
                 const float vk = __shfl_sync(0xffffffffu, v, k);
                 st_tagged_all(g, P.E, sp.r + warp + k * DEC_CWARPS, __float_as_uint(vk), C.tag, C.S->nrep);
@@ -517,6 +520,12 @@ __device__ __forceinline__ void publish_block_q8(float2* g, int n, int b, float 
     w |= __shfl_down_sync(0xffffffffu, q, 1) << 8;
     w |= __shfl_down_sync(0xffffffffu, q, 2) << 16;
     w |= __shfl_down_sync(0xffffffffu, q, 3) << 24;
+    if (nrep == 1) {        // one copy: the lanes that hold a word store it themselves, one instruction
+        const int lane = threadIdx.x & 31;
+        if ((lane & 3) == 0) st_tagged_u32(g + b * 8 + (lane >> 2), w, tag);
+        if (lane == 0) st_tagged_u32(g + (n >> 2) + b, (unsigned)__half_as_ushort(dh), tag);
+        return;
+    }
     for (int i = 0; i < 8; i++) {
         const unsigned wi = __shfl_sync(0xffffffffu, w, 4 * i);
         st_tagged_all(g, nw, b * 8 + i, wi, tag, nrep);

@@ -99,6 +99,7 @@ __global__ void k_silu_mul_quant_rows(const float* __restrict__ G, const float* 
 // one-token kernel's (lt_attn.cu): sequential-i fma scores, * scale, max, __expf, Z on 64 strided
 // lanes + tree, left-fold V sum, / Z.
 constexpr int PF_THREADS = 256;
+constexpr int PF_KTILE = 128;            // K rows staged per tile: two threads per position
 
 template <int HD, int QT>
 __global__ void __launch_bounds__(PF_THREADS, QT <= 8 ? 3 : 1)
@@ -109,7 +110,8 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     float* qs = pf_smem;                 // [QT][HD]
     float* red = qs + QT * HD;           // [QT][64]
     float* zs = red + QT * 64;           // [QT] max, then Z
-    float* sc = zs + QT;                 // [QT][ld], ld = maxt rounded up to 4 floats
+    float* kt = zs + ((QT + 3) & ~3);    // [PF_KTILE][HD + 4] one tile of K rows (rows padded: conflict-free 16-byte reads)
+    float* sc = kt + PF_KTILE * (HD + 4);   // [QT][ld], ld = maxt rounded up to 4 floats
     const int ld = (maxt + 3) & ~3;
     const int tid = threadIdx.x;
     const int h = blockIdx.y;
@@ -130,28 +132,48 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     }
     __syncthreads();
 
-    // scores: one thread per cached position, the K row read once for all QT queries
-    for (int t = tid; t < Lmax; t += PF_THREADS) {
-        const float4* Kt = (const float4*)(K + ((long)t * nkv + hk) * HD);
-        float s[QT];
+    // scores: K rows go through shared memory in tiles of PF_KTILE positions (coalesced 16-byte asynchronous
+    // copies; a thread reading its own row straight from global memory touches a new sector with every load).
+    // A position of the tile is served by two threads, QT/2 queries each; each (row, query) score is the same
+    // sequential-i fma chain as in the one-token kernel.
+    constexpr int KST = HD + 4, QH = QT / 2;
+    const int p = tid & (PF_KTILE - 1), qh = tid / PF_KTILE;
+    for (int t0 = 0; t0 < Lmax; t0 += PF_KTILE) {
+        const int nt = Lmax - t0 < PF_KTILE ? Lmax - t0 : PF_KTILE;
+        for (int e = tid; e < nt * (HD / 4); e += PF_THREADS) {
+            const int r = e / (HD / 4), c = e - r * (HD / 4);
+            const float* src = K + ((long)(t0 + r) * nkv + hk) * HD + c * 4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(kt + r * KST + c * 4)),
+                         "l"(src) : "memory");
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        if (p < nt) {
+            const int t = t0 + p;
+            const float4* Kt = (const float4*)(kt + p * KST);
+            float s[QH];
 #pragma unroll
-        for (int qi = 0; qi < QT; qi++) s[qi] = 0.0f;
+            for (int qi = 0; qi < QH; qi++) s[qi] = 0.0f;
 #pragma unroll 4
-        for (int i = 0; i < HD / 4; i++) {
-            const float4 kk = Kt[i];
+            for (int i = 0; i < HD / 4; i++) {
+                const float4 kk = Kt[i];
 #pragma unroll
-            for (int qi = 0; qi < QT; qi++) {
-                const float4 qq = ((const float4*)(qs + qi * HD))[i];
-                s[qi] = __fmaf_rn(qq.x, kk.x, s[qi]);
-                s[qi] = __fmaf_rn(qq.y, kk.y, s[qi]);
-                s[qi] = __fmaf_rn(qq.z, kk.z, s[qi]);
-                s[qi] = __fmaf_rn(qq.w, kk.w, s[qi]);
+                for (int qi = 0; qi < QH; qi++) {
+                    const float4 qq = ((const float4*)(qs + (qh * QH + qi) * HD))[i];
+                    s[qi] = __fmaf_rn(qq.x, kk.x, s[qi]);
+                    s[qi] = __fmaf_rn(qq.y, kk.y, s[qi]);
+                    s[qi] = __fmaf_rn(qq.z, kk.z, s[qi]);
+                    s[qi] = __fmaf_rn(qq.w, kk.w, s[qi]);
+                }
+            }
+#pragma unroll
+            for (int qi = 0; qi < QH; qi++) {
+                const int q = qh * QH + qi;
+                sc[q * ld + t] = t < L0 + r0 + q + 1 ? __fmul_rn(s[qi], scale) : -1e30f;
             }
         }
-#pragma unroll
-        for (int qi = 0; qi < QT; qi++) sc[qi * ld + t] = t < L0 + r0 + qi + 1 ? __fmul_rn(s[qi], scale) : -1e30f;
+        __syncthreads();        // the tile is rewritten
     }
-    __syncthreads();
 
     // softmax per query row on the frozen 64-lane layout: 4 rows at a time, 64 threads each
     const int grp = tid >> 6, l64 = tid & 63;
@@ -245,7 +267,8 @@ static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const f
                                int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
     int* st = device_status_ptr();
     LT_REQUIRE(st != nullptr, "lt_attn_prefill: status word unavailable");
-    const size_t smem = ((size_t)QT * HD + QT * 64 + QT + (size_t)QT * ((maxt + 3) & ~3)) * sizeof(float);
+    const size_t smem = ((size_t)QT * HD + QT * 64 + ((QT + 3) & ~3) + (size_t)PF_KTILE * (HD + 4) +
+                         (size_t)QT * ((maxt + 3) & ~3)) * sizeof(float);
     LT_REQUIRE(smem <= 200 * 1024, "lt_attn_prefill: maxt=%d needs %zu bytes of shared memory", maxt, smem);
     static PerDeviceOnce attr_once;
     if (attr_once.first()) {
@@ -264,9 +287,10 @@ static int pick_attn_prefill(const float* Q, int q_ld, const float* K, const flo
     // chains of dependent operations, resident warps hide them), else 4; 16 only for short chunks (16 rows
     // with one CTA per SM was measured 6 % slower at 2048 positions)
     const size_t per_row = (size_t)((maxt + 3) & ~3) + HD + 65;
-    if (16 * per_row * sizeof(float) <= 72 * 1024)
+    const size_t tile = (size_t)PF_KTILE * (HD + 4) * sizeof(float);
+    if (16 * per_row * sizeof(float) + tile <= 72 * 1024)
         return launch_attn_prefill<HD, 16>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
-    if (8 * per_row * sizeof(float) <= 72 * 1024 || 4 * per_row * sizeof(float) > 200 * 1024 / 2)
+    if (8 * per_row * sizeof(float) + tile <= 110 * 1024 || 4 * per_row * sizeof(float) + tile > 200 * 1024 / 2)
         return launch_attn_prefill<HD, 8>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
     return launch_attn_prefill<HD, 4>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
 }

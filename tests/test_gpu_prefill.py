@@ -63,13 +63,14 @@ def test_qwen05b_prefill_2048_tokens_equals_token_by_token_on_a_sample(batch):
     dr._KV_MAX_SEQ = T
     try:
         kvs = [[None] * cfg["n_layers"] for _ in range(batch)]
-        lb = prefill.prefill_resident(w, cfg, torch.from_numpy(prompts.astype(np.int64)), kvs).reshape(batch, -1).numpy().copy() \
+        # (prefill_resident returns the logits of the last sequence's last position)
+        lb = prefill.prefill_resident(w, cfg, torch.from_numpy(prompts.astype(np.int64)), kvs).reshape(-1).numpy().copy() \
             if batch > 1 else prefill_chunks(w, cfg, prompts[0], kvs[0])
         rows = np.sort(rng.choice(T, size=64, replace=False))
         for s in sorted({0, batch - 1}):
             la, kva = _prefill(w, cfg, prompts[s].tolist(), batched=False, max_seq=T)
-            got = lb[s] if batch > 1 else lb
-            assert np.array_equal(bits(la), bits(got)), s
+            if s == batch - 1:
+                assert np.array_equal(bits(la), bits(lb)), s
             for ca, cb in zip(kva, kvs[s]):
                 assert ca.length == cb.length == T
                 assert np.array_equal(bits(ca.k_slice_host()[rows]), bits(cb.k_slice_host()[rows]))
