@@ -272,6 +272,7 @@ def tp_decode_case(cfg, arch, rank, world, B, ctx, steps, warmup, comm="p2p", at
         t = torch.tensor([ar_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ar_ms = float(t.item())
     status = sorted(_lib.device_status())
     launches = dec.launches_per_step
+    exact_used = bool(dec.exact)
     match = None
     if check_world1 and world > 1:
         # world 1 on rank 0's GPU, teacher-forced with the sharded run's tokens: does it choose the same
@@ -315,7 +316,7 @@ def tp_decode_case(cfg, arch, rank, world, B, ctx, steps, warmup, comm="p2p", at
                    "layers": L, "launches_per_step": launches, "comm": comm if world > 1 else None,
                    "chained_launches": bool(chained),
                    "allreduce_in_gemv": bool(fused_allreduce) and world > 1 and comm == "p2p" and B == 1,
-                   "exact_down_split": bool(exact_split) and world > 1,
+                   "exact_down_split": exact_used,
                    "attention_order": f"attn_decode_split, S={attn_split}" if attn_split else "one-pass (production)"},
         "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
                      "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": hbm * world, "unit": "GB/s",

@@ -114,9 +114,11 @@ def test_exact_row_split_partials_sum_to_the_one_gpu_bits(g, shape):
     for r in range(g):
         wq = np.ascontiguousarray(Wq3[:, r::g, :]).reshape(-1); wd = np.ascontiguousarray(Wd2[:, r::g]).reshape(-1)
         lxq = dev(np.ascontiguousarray(xq3[:, r::g, :]).reshape(-1)); lxd = dev(np.ascontiguousarray(xd2[:, r::g]).reshape(-1))
+        dwq, dwd = dev(wq), dev(wd)             # (named: a temporary's memory may be handed out again before the launch runs)
         y = torch.empty(T * M, dtype=torch.float32, device="cuda")
-        _lib.call("lt_q8_gemv_lanes", dev(wq).data_ptr(), dev(wd).data_ptr(), lxq.data_ptr(), lxd.data_ptr(), y.data_ptr(),
+        _lib.call("lt_q8_gemv_lanes", dwq.data_ptr(), dwd.data_ptr(), lxq.data_ptr(), lxd.data_ptr(), y.data_ptr(),
                   M, K // g, T, g, stream())
+        torch.cuda.synchronize()
         parts.append(host(y).copy())
     s = g // 2
     while s >= 1:
@@ -150,14 +152,14 @@ def test_exchange_wait_gives_up_and_the_context_stays_usable():
         Wq, Wd, x = synth.gemv_case(M, K, seed=1)
         xq, xd = gpu_quant(x[0])
         y = torch.zeros(M, device="cuda")
-        ctr0 = torch.empty(0)
+        dWq, dWd = dev(Wq), dev(Wd)
         for _ in range(2):      # twice: the second call must not find the row counters out of step with its own pushes
-            _lib.call("lt_q8_gemv_allreduce", ctypes.byref(c), dev(Wq).data_ptr(), dev(Wd).data_ptr(), xq.data_ptr(),
+            _lib.call("lt_q8_gemv_allreduce", ctypes.byref(c), dWq.data_ptr(), dWd.data_ptr(), xq.data_ptr(),
                       xd.data_ptr(), None, y.data_ptr(), M, K, stream())
             torch.cuda.synchronize()
             assert "wait_timeout" in _lib.device_status()
         # the context is intact: an ordinary GEMV still gives the oracle-pinned bits
-        y2 = host(gpu_gemv(dev(Wq), dev(Wd), xq, xd, M, K))
+        y2 = host(gpu_gemv(dWq, dWd, xq, xd, M, K))
         assert np.isfinite(y2).all() and _lib.device_status() == set()
     finally:
         c.stage[1] = None
