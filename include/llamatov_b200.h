@@ -234,7 +234,9 @@ typedef struct lt_decode_desc {
     void* ws_part;             /* lt_decode_step: tagged workspace [2 * lt_decode_num_ctas()] for the per-CTA argmax results */
     int poll_ns;               /* lt_decode_step: pause between two looks at hand-over words that have not arrived
                                   (0 = none); with several looks in flight, their spacing */
-    int poll_looks;            /* lt_decode_step: looks in flight per waiting thread, 1..3 (0 = 1) */
+    int poll_looks;            /* lt_decode_step: copies of the hand-over workspaces in use, 1..lt_decode_ws_replicas() (0 = all) */
+    int trace_cta;             /* lt_decode_step, diagnostics: the second traced CTA (0 = the last one) */
+    int reserved_;
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);

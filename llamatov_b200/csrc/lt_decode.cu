@@ -167,14 +167,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 // pointer to a real function) lives in L2 -- which the weight stream sweeps all the time -- and every
 // access to it is a memory round trip on the critical path.  (Measured: a few hundred bytes of stack
 // per thread made the step 1.6x slower.)
+template <typename Sink>
 __device__ __forceinline__ bool poll_words(const float2* __restrict__ g, int n, int first, int stride, int nwords,
-                                        unsigned want, float2* v, Shared* S, int* status, unsigned pause_ns) {
+                                           unsigned want, Sink sink, Shared* S, int* status, unsigned pause_ns) {
+    // sink(k, payload) takes word k when it has arrived (no copy of the words is kept in registers)
     unsigned pending = 0;
 #pragma unroll
-    for (int k = 0; k < 4; k++) {       // (constant indices: v stays in registers)
-        v[k] = make_float2(0.0f, 0.0f);
+    for (int k = 0; k < 4; k++)
         if (k < nwords && first >= 0 && first + k * stride < n) pending |= 1u << k;
-    }
     if (!pending) return true;
     const long long t0 = clock64();
     unsigned spins = 0;
@@ -185,7 +185,7 @@ __device__ __forceinline__ bool poll_words(const float2* __restrict__ g, int n, 
             if (pending & (1u << k)) w[k] = __ldcg(g + first + k * stride);
 #pragma unroll
         for (int k = 0; k < 4; k++)
-            if ((pending & (1u << k)) && __float_as_uint(w[k].y) == want) { v[k] = w[k]; pending &= ~(1u << k); }
+            if ((pending & (1u << k)) && __float_as_uint(w[k].y) == want) { sink(k, w[k].x); pending &= ~(1u << k); }
         if (!pending) return true;
         if (wait_expired(t0, spins, S, status)) return false;
         if (pause_ns) __nanosleep(pause_ns);
@@ -200,8 +200,9 @@ struct Tracer {
     __device__ __forceinline__ void init(const lt_decode_desc& P) {
         buf = nullptr; n = 0;
         if (P.trace != nullptr && threadIdx.x == 0) {
+            const unsigned second = P.trace_cta > 0 ? (unsigned)P.trace_cta : gridDim.x - 1;
             if (blockIdx.x == 0) buf = P.trace;
-            else if (blockIdx.x == gridDim.x - 1) buf = P.trace + 2 * DEC_TRACE_CAP;
+            else if (blockIdx.x == second) buf = P.trace + 2 * DEC_TRACE_CAP;
         }
     }
     __device__ __forceinline__ void stamp(int id) {
@@ -645,12 +646,12 @@ __device__ __forceinline__ void fetch_x(const float2* g, unsigned want, bool fro
         if (from_smem) {
             for (int j = t; j < E; j += 256) p = __fmaf_rn(sF[j], sF[j], p);
         } else {
-            float2 v[4];
-            poll_words(g + (size_t)(blockIdx.x % S->nrep) * E, E, t, 256, DEC_XB, want, v, S, status, pause_ns);
+            poll_words(g + (size_t)(blockIdx.x % S->nrep) * E, E, t, 256, DEC_XB, want,
+                             [&](int k, float x) { sF[t + k * 256] = x; }, S, status, pause_ns);
 #pragma unroll
-            for (int k = 0; k < DEC_XB; k++) {
+            for (int k = 0; k < DEC_XB; k++) {       // the declared lane partial: this thread's words in ascending order
                 const int j = t + k * 256;
-                if (j < E) { sF[j] = v[k].x; p = __fmaf_rn(v[k].x, v[k].x, p); }
+                if (j < E) { const float x = sF[j]; p = __fmaf_rn(x, x, p); }
             }
         }
         S->sred[t] = p;
@@ -661,14 +662,12 @@ __device__ __forceinline__ void fetch_x(const float2* g, unsigned want, bool fro
 __device__ __forceinline__ void fetch_q8(const float2* g, unsigned want, int n, int8_t* sXq, __half* sXd, Shared* S, int* status,
                                       unsigned pause_ns) {
     const int nw = (n >> 2) + (n >> 5);
-    float2 v[4];
-    poll_words(g + (size_t)(blockIdx.x % S->nrep) * nw, nw, threadIdx.x, DEC_CTHREADS, 4, want, v, S, status, pause_ns);
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        const int i = threadIdx.x + k * DEC_CTHREADS;
-        if (i < (n >> 2)) ((unsigned*)sXq)[i] = __float_as_uint(v[k].x);
-        else if (i < nw) sXd[i - (n >> 2)] = __ushort_as_half((unsigned short)(__float_as_uint(v[k].x) & 0xffffu));
-    }
+    poll_words(g + (size_t)(blockIdx.x % S->nrep) * nw, nw, threadIdx.x, DEC_CTHREADS, 4, want,
+                     [&](int k, float x) {
+                         const int i = threadIdx.x + k * DEC_CTHREADS;
+                         if (i < (n >> 2)) ((unsigned*)sXq)[i] = __float_as_uint(x);
+                         else sXd[i - (n >> 2)] = __ushort_as_half((unsigned short)(__float_as_uint(x) & 0xffffu));
+                     }, S, status, pause_ns);
 }
 
 struct Areas {
@@ -828,9 +827,8 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
         // while warps 0 and 1 do the softmax
         if (room) {
             for (int j = lane; j < HD; j += 32) {
-                float2 vn[4];
-                poll_words((const float2*)P.ws_qkv, nk, hk * HD + j, 0, 1, tag, vn, S, P.status, backoff);
-                S->vn[j] = vn[0].x;
+                poll_words((const float2*)P.ws_qkv, nk, hk * HD + j, 0, 1, tag, [&](int, float x) { S->vn[j] = x; }, S,
+                           P.status, backoff);
             }
         }
         asm volatile("bar.sync 3, 96;" ::: "memory");
@@ -1140,10 +1138,11 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         float bv = -3.4e38f;
         int bi = 2147483647;
         for (int c = lane; c < G; c += 32) {
-            float2 w[4];
-            poll_words((const float2*)P.ws_part, 2 * G, 2 * c, 1, 2, ptag, w, S, P.status, backoff);
-            const float v = w[0].x;
-            const int i = (int)__float_as_uint(w[1].x);
+            float pv = -3.4e38f, pi = __uint_as_float(2147483647u);
+            poll_words((const float2*)P.ws_part, 2 * G, 2 * c, 1, 2, ptag, [&](int k, float x) { if (k == 0) pv = x; else pi = x; }, S,
+                       P.status, backoff);
+            const float v = pv;
+            const int i = (int)__float_as_uint(pi);
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
 #pragma unroll
