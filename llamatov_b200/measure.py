@@ -3,6 +3,7 @@
   python -m llamatov_b200.measure prefill [--tokens 2048] [--batch 1 8] [--arch qwen2.5-0.5b]
   python -m llamatov_b200.measure gemv-sweep [--batch 1 4 16 64]
   python -m llamatov_b200.measure gemm -m 4864 -k 896 -t 2048 [--variant 1]
+  python -m llamatov_b200.measure decode-trace [--cta N]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       -m llamatov_b200.measure tp-decode [--batch 1 32] [--ctx 4096] [--steps 128] [--check-world1]
 
@@ -199,6 +200,63 @@ def run_gemm(args):
                       "device_status": sorted(_lib.device_status()), "peak_source": src}))
 
 
+TRACE_IDS = {1: "kernel entry", 11: "attention CTA: layer input x in shared memory", 111: "... RMSNorm + quantiser done",
+             12: "... q|k rows folded", 13: "... rope, K append, scores done", 14: "... softmax, V fold, head output published",
+             20: "GEMV CTA: phase prepared (weight stages awaited, addresses, operands)",
+             21: "phase 0: x arrived", 22: "phase 1: attention output arrived", 23: "phase 2: x1 arrived",
+             24: "phase 3: silu*up arrived", 25: "phase 0 done (v rows stored) / LM head done", 26: "phase 1 done (x1 stored)",
+             27: "phase 2 done (silu*up published)", 28: "phase 3 done (x stored)", 32: "LM head: CTA's rows done",
+             99: "end (the last CTA: all partial argmax results collected)"}
+
+
+def run_decode_trace(args):
+    """SM-clock stamps inside the one-kernel decode step (lt_decode_step, trace pointer set): for CTA 0 (an
+    attention CTA) and one GEMV CTA (--cta, default the last), the mean / min / max time from the previous
+    stamp to each stamp over the layers.  One JSON line per traced CTA."""
+    if args.cta:
+        os.environ["LLAMATOV_TRACE_CTA"] = str(args.cta)
+    dr._FUSED_STEP = "persistent"
+    m = synth.make_model(args.arch, seed=0)
+    w, cfg = synth.reference_weights(m)
+    dr.reset_engine_state(); dr.apply_production_profile()
+    kv = [None] * cfg["n_layers"]
+    gr = dr.GraphRunner(w, cfg, kv)
+    prompt = np.random.default_rng(0).integers(0, m["cfg"]["vocab"], size=32).tolist()
+    lg = gr.seed(torch.tensor(prompt), torch.arange(32))
+    first = int(np.argmax(lg.reshape(-1).numpy()))
+    tokd = torch.tensor([first], dtype=torch.int32, device="cuda")
+    st = dr.FusedDecodeStep(w, cfg, kv, tok_ptr=tokd.data_ptr())
+    if st.mode != "persistent":
+        raise SystemExit("the one-kernel step does not support this architecture")
+    n = st.enable_trace()
+    for _ in range(4):
+        st.launch()
+    torch.cuda.synchronize()
+    st.trace.zero_()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(); st.launch(); e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    try:
+        mhz = float(torch.cuda.clock_rate())        # SM clock now, MHz (NVML)
+    except Exception:
+        mhz = 1965.0
+    tr = st.trace.cpu().numpy().reshape(2, n, 2)
+    for c in range(2):
+        tt = tr[c]
+        k = int(np.argmax(tt[:, 1] == 0)) if (tt[:, 1] == 0).any() else n
+        ids, clk = tt[:k, 0], tt[:k, 1]
+        rows = {}
+        for i in range(1, k):
+            rows.setdefault(int(ids[i]), []).append((clk[i] - clk[i - 1]) / mhz)
+        print(json.dumps({"cta": "0 (attention, head 0)" if c == 0 else f"{args.cta or 'last'} (GEMV)", "launch_ms_traced": ms,
+                          "sm_mhz_assumed": mhz, "total_us": float((clk[-1] - clk[0]) / mhz),
+                          "us_since_previous_stamp": {TRACE_IDS.get(i, str(i)): {"n": len(v), "mean": round(float(np.mean(v)), 2),
+                                                                                 "min": round(float(np.min(v)), 2),
+                                                                                 "max": round(float(np.max(v)), 2)}
+                                                      for i, v in sorted(rows.items())},
+                          "device_status": sorted(_lib.device_status())}), flush=True)
+
+
 def tp_arch_cfg(arch, layers=0):
     a = synth.ARCHS[arch]
     cfg = dict(n_layers=a["n_layers"], n_head=a["n_head"], n_head_kv=a["n_head_kv"], n_embd=a["n_embd"],
@@ -367,6 +425,9 @@ def main(argv=None):
     m.add_argument("-t", type=int, required=True)
     m.add_argument("--variant", type=int, default=0, help="lt_q8_gemm_tc variant; -1 = lt_q8_gemv dispatch")
     m.add_argument("--steps", type=int, default=2); m.add_argument("--warmup", type=int, default=1)
+    d = sub.add_parser("decode-trace")
+    d.add_argument("--arch", default="qwen2.5-0.5b")
+    d.add_argument("--cta", type=int, default=0, help="index of the traced GEMV CTA (0 = the last CTA)")
     t = sub.add_parser("tp-decode")
     t.add_argument("--arch", default="llama-3-8b")
     t.add_argument("--batch", type=int, nargs="+", default=[1, 32])
@@ -396,6 +457,8 @@ def main(argv=None):
         run_tp_decode(args)
     elif args.cmd == "gemm":
         run_gemm(args)
+    elif args.cmd == "decode-trace":
+        run_decode_trace(args)
     else:
         run_gemv_sweep(args)
 
