@@ -18,9 +18,11 @@
 //   * the other CTAs are GEMV CTAs.  Each owns a fixed slice of the rows of every other matrix:
 //     the v rows of q|k|v, o_proj, whole 32-row blocks of gate|up (so that silu(gate)*up is
 //     quantised where it is produced), down, and (together with the attention CTAs) the LM head.
-//     A producer warp streams the CTA's rows for the whole step through a ring of shared-memory
-//     stages with bulk async copies (no multicast), running ahead of the dependency chain across
-//     phase and layer boundaries.
+//     A producer warp fetches the CTA's rows with bulk async copies (no multicast), ahead of the
+//     dependency chain: within the layers every slice has a FIXED place in shared memory (a slot
+//     per phase, refilled with the next layer's slice as soon as this layer's has been folded, so
+//     a phase finds its rows a whole layer early and at addresses that never change); the LM head,
+//     many times the size of shared memory, streams through a ring of stages over the same area.
 //
 // Per layer:   x --(1)--> attention CTAs: q,k,attention -> a(q8)          GEMV CTAs: v rows
 //              a --(2)--> o_proj + x -> x1 --(3)--> rmsnorm, gate|up, silu*up -> v(q8)
@@ -110,9 +112,16 @@ __device__ __forceinline__ void st_tagged_all(float2* g, int n, int idx, unsigne
     if (lane < nrep) __stcg(g + (size_t)lane * n + idx, make_float2(__uint_as_float(payload), __uint_as_float(tag)));
 }
 
+struct GemvConst {
+    unsigned big;       // shared address of the big area (slot p at big + SL.off[p])
+    unsigned db[4];     // scale rows of slot p relative to the slot (p = 2: offset of a chunk's scale rows within their 16-byte window)
+    int v0, nv, e0, ne, b0, nbk;    // the CTA's slices: first v row / count, first o_proj and down row / count, first FFN block / count
+};
+
 struct Shared {
     unsigned long long full[DEC_MAX_STAGES];
     unsigned long long empty[DEC_MAX_STAGES];
+    unsigned long long sfull[4], sempty[4]; // GEMV CTA: the slots of the four layer phases
     unsigned long long wfull, wempty;       // attention CTA: the head's resident q|k rows
     unsigned long long att_done;            // attention CTA: layers finished, the big area is free for the LM ring
     float sred[256];                        // RMSNorm lane partials (the declared 256 lanes)
@@ -120,15 +129,16 @@ struct Shared {
     float sv[2][32];                        // silu(gate)*up of the FFN blocks being folded
     float bias[256];                        // attention CTA: bias of its q rows, then of its k rows
     float qk[256];                          // attention CTA: q rows then k rows before rope
-    // plans of the recurring sets, remembered per warp relative to the stage bases: [kind][warp][qrel 4 | drel 4 |
-    // chunk of row k (4 x 8 bits) | nset | nch | nv]; kinds: v rows, o_proj, down, a full LM-head set
-    unsigned memo[4][DEC_CWARPS][12];
+    // plan of a full LM-head set, remembered per warp relative to the stage bases: [warp][qrel 4 | drel 4 |
+    // chunk of row k (4 x 8 bits) | nset | nch | nv]
+    unsigned memo[DEC_CWARPS][12];
     float vn[128];                          // attention CTA: the new v row of its group
     int lens[DEC_MAX_LAYERS];               // cache lengths at kernel entry
     float best_v[DEC_CWARPS];
     int best_i[DEC_CWARPS];
     volatile int abort_flag;
     int nrep;                               // copies of the hand-over buffers in use (1..DEC_NREP)
+    GemvConst gc;                           // GEMV CTA: what does not change from layer to layer
 };
 
 __device__ __forceinline__ bool wait_expired(long long t0, unsigned& spins, Shared* S, int* status) {
@@ -235,13 +245,18 @@ __device__ __forceinline__ int rows_per_chunk_lm(int K) {
 }
 
 // producer side: rows [r0, r1) of a matrix with row length K, chunk by chunk
+// gate: the first use of stage gate_stage (and so of every later stage) waits for that barrier phase first
+// (the ring lies over memory that is still being read until then); nullptr = no gate.
 __device__ __forceinline__ bool produce_segment(Ring& R, const int8_t* Wq, const __half* Wd, int r0, int r1, int K, int RC,
-                                                Shared* S, int* status) {
+                                                Shared* S, int* status, unsigned long long* gate = nullptr,
+                                                unsigned gate_parity = 0, int gate_stage = 0) {
     const int nb = K >> 5;
     for (int r = r0; r < r1; r += RC) {
         const int n = (r1 - r < RC) ? (r1 - r) : RC;
         if (R.fill > 0) {
             if (!mbar_wait(&R.empty[R.stage], (R.fill - 1) & 1, S, status)) return false;
+        } else if (gate != nullptr && R.stage == gate_stage) {
+            if (!mbar_wait(gate, gate_parity, S, status)) return false;
         }
         unsigned char* dst = R.base + (size_t)R.stage * DEC_STAGE_STRIDE;
         const unsigned qbytes = (unsigned)n * K;
@@ -271,6 +286,34 @@ __device__ __forceinline__ void producer_drain(const Ring& R) {
         while (!mbar_try_wait(&R.full[s], parity))
             if (clock64() - t0 > DEC_DRAIN_CLOCKS) return;
     }
+}
+
+// ---- slots: where a GEMV CTA keeps its slice of the four layer matrices.  Slot p (phase p) holds rows
+// [r0, r0 + n) of a matrix as n*K quant bytes followed by the 16-byte aligned window of their scales; the
+// gate|up slot holds, block after block, the gate chunk and the up chunk (32 rows each, same format) at
+// a fixed pitch.  Offsets are the same in every CTA (sized for the largest share).
+struct DecSlots {
+    int off[4];         // byte offset of slot p in the big area
+    int chunk;          // pitch of a 32-row chunk in the gate|up slot
+};
+
+// producer: request rows [r, r + n) of a matrix into shared memory at dst; returns the bytes requested
+__device__ __forceinline__ unsigned slot_request(unsigned char* dst, const int8_t* Wq, const __half* Wd, int r, int n, int K,
+                                                 unsigned long long* bar) {
+    const int nb = K >> 5;
+    const unsigned qbytes = (unsigned)n * K;
+    const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(Wd + (size_t)r * nb));
+    const size_t d0 = a0 & ~(size_t)15;
+    const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
+    const unsigned dbytes = (unsigned)(d1 - d0);
+    bulk_g2s(dst, Wq + (size_t)r * K, qbytes, bar);
+    bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, bar);
+    return qbytes + dbytes;
+}
+__device__ __forceinline__ unsigned slot_bytes(const __half* Wd, int r, int n, int K) {
+    const int nb = K >> 5;
+    const size_t a0 = (size_t)(reinterpret_cast<uintptr_t>(Wd + (size_t)r * nb));
+    return (unsigned)n * K + (unsigned)(((a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15) - (a0 & ~(size_t)15));
 }
 
 enum { EPI_V = 0, EPI_O = 1, EPI_DOWN = 2, EPI_LOGITS = 3 };
@@ -354,12 +397,11 @@ __device__ __forceinline__ float fold_rows(const RowSetN<NR>& rs, int nb, int nv
 
 constexpr int DEC_MAXCH = 4;    // chunks of one segment that are folded together
 
-// consumer side of a segment = rows [r0, r1) of a matrix with row length K.  Up to DEC_MAXCH chunks
-// are taken together as one SET and their rows dealt to the warps (row j of the set to warp j % 15),
-// so that a short segment is one pass of all warps whatever its chunking; a warp folds up to DEC_ILP
-// rows together.  Work is split in two so that everything that does not depend on the activation
-// (waiting for the weight stages, every address, the epilogue's operand) is done BEFORE the hand-over
-// is awaited, and only the fold and the store come after it.
+// consumer side of a segment = rows [r0, r1) of a matrix with row length K, streamed through the ring (the LM
+// head).  Up to DEC_MAXCH chunks are taken together as one SET and their rows dealt to the warps (row j of
+// the set to warp j % 15); a warp folds up to DEC_ILP rows together.  Work is split in two so that everything
+// that does not depend on the activation (waiting for the weight stages, every address, the epilogue's
+// operand) is done BEFORE the hand-over is awaited, and only the fold and the store come after it.
 struct SegPlan {
     RowSet rs;
     int r;          // first row of the set
@@ -368,8 +410,8 @@ struct SegPlan {
     bool ok;
 };
 
-// memo: the plan of this set relative to its stages' base addresses does not change from layer to layer (same
-// rows, same chunking; the launcher checks that a matrix kind's scale arrays are aligned alike in every layer):
+// memo: the plan of a full set relative to its stages' base addresses is the same for every full set of the
+// segment (same chunking, and a set's scale rows start a whole number of 16-byte units after the previous set's):
 // memo_mode 1 = compute it and remember it, 2 = take it from the memo (a fraction of the arithmetic), 0 = neither.
 __device__ __forceinline__ SegPlan seg_prepare(int epi, const Ring& R, const __half* Wd, int r0, int r, int r1, int K,
                                                int RC, EpiCtx& C, unsigned* memo, int memo_mode) {
@@ -462,6 +504,37 @@ __device__ __forceinline__ SegPlan seg_prepare(int epi, const Ring& R, const __h
     return sp;
 }
 
+// The same for a slot: rows [r0, r0 + n) of the matrix lie at shared address sbase, their scale rows at dbase;
+// the set is rows i0 .. of them, dealt to the warps as above.  Nothing but a wait for the slot
+// (first set only) and a few multiplications: the addresses do not depend on the layer.
+__device__ __forceinline__ SegPlan slot_prepare(int epi, unsigned sbase, unsigned dbase, int r0, int i0, int n, int K,
+                                                unsigned long long* bar, unsigned parity, EpiCtx& C) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = K >> 5;
+    SegPlan sp;
+    sp.r = r0 + i0;
+    sp.nch = 0;
+    int m = n - i0;
+    if (m > DEC_CWARPS * DEC_ILP) m = DEC_CWARPS * DEC_ILP;
+    sp.nset = m;
+    sp.nv = m > warp ? (m - warp + DEC_CWARPS - 1) / DEC_CWARPS : 0;
+    sp.ok = (i0 > 0 || n <= 0) ? true : mbar_wait(bar, parity, C.S, C.P->status);
+#pragma unroll
+    for (int k = 0; k < DEC_ILP; k++) {
+        int i = i0 + warp + k * DEC_CWARPS;
+        if (i >= n) i = n > 0 ? n - 1 : 0;      // (unused rows point at valid memory)
+        sp.rs.q[k] = sbase + (unsigned)(i * K);
+        sp.rs.d[k] = dbase + (unsigned)(i * nb * 2);
+    }
+    sp.add = 0.0f;
+    if (lane < sp.nv) {
+        const int row = sp.r + warp + lane * DEC_CWARPS;
+        if (epi == EPI_V) { if (C.ly->qkv_bias != nullptr) sp.add = __ldg(C.ly->qkv_bias + row); }
+        else if (epi == EPI_O || epi == EPI_DOWN) sp.add = C.resid[row];
+    }
+    return sp;
+}
+
 __device__ __forceinline__ void seg_finish(int epi, const SegPlan& sp, Ring& R, int K, const int8_t* sXq, const __half* sXd,
                                            EpiCtx& C) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -534,8 +607,8 @@ __device__ __forceinline__ void publish_block_q8(float2* g, int n, int b, float 
     st_tagged_all(g, nw, (n >> 2) + b, (unsigned)__half_as_ushort(dh), tag, nrep);
 }
 
-// gate|up of up to two whole 32-row FFN blocks [b, b + nbk): the gate chunk and the up chunk of every
-// block are awaited together (before the activation is); a warp folds gate row i and up row i of two
+// gate|up of up to two whole 32-row FFN blocks [b, b + nbk) of the CTA's gate|up slot (chunk j of the slot
+// at sbase + j*pitch: gate and up of the CTA's first block, gate and up of its second, ...); a warp folds gate row i and up row i of two
 // rows of a block side by side (rows i = warp, warp+15; warps 0 and 1 then rows 30 and 31), forms
 // silu(gate)*up where both results land, and the blocks are then quantised and published by one warp each.
 struct FfnPlan {
@@ -543,26 +616,23 @@ struct FfnPlan {
     bool ok;
 };
 
-__device__ __forceinline__ FfnPlan ffn_prepare(const Ring& R, const __half* Wd, int F, int b, int nbk, int E, EpiCtx& C) {
-    const int nb = E >> 5;
+__device__ __forceinline__ FfnPlan ffn_prepare(unsigned sbase, unsigned pitch, unsigned dalign, int b0, int b, int nbk, int E) {
     FfnPlan fp;
     fp.ok = true;
-    Ring R2 = R;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
         fp.cbase[c] = 0; fp.cwd[c] = 0;
         if (c < 2 * nbk) {
-            fp.ok = mbar_wait(&R2.full[R2.stage], R2.fill & 1, C.S, C.P->status) && fp.ok;
-            const int row0 = ((c & 1) ? F : 0) + (b + (c >> 1)) * 32;      // gate chunk, then up chunk of a block
-            fp.cbase[c] = smem_u32(R2.base + (size_t)R2.stage * DEC_STAGE_STRIDE);
-            fp.cwd[c] = fp.cbase[c] + (unsigned)(32 * E) + (unsigned)(reinterpret_cast<uintptr_t>(Wd + (size_t)row0 * nb) & 15);
-            R2.advance();
+            // gate chunk, then up chunk of a block; a chunk's scale rows start a whole number of 16-byte units
+            // after the matrix's first scale (32 rows of E/32 scales, F rows more for the up chunk)
+            fp.cbase[c] = sbase + (unsigned)((b - b0) * 2 + c) * pitch;
+            fp.cwd[c] = fp.cbase[c] + (unsigned)(32 * E) + dalign;
         }
     }
     return fp;
 }
 
-__device__ __forceinline__ void ffn_finish(const FfnPlan& fp, Ring& R, int F, int b, int nbk, bool more, int E,
+__device__ __forceinline__ void ffn_finish(const FfnPlan& fp, int F, int b, int nbk, bool more, int E,
                                            const int8_t* sXq, const __half* sXd, EpiCtx& C) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = E >> 5;
@@ -582,11 +652,6 @@ __device__ __forceinline__ void ffn_finish(const FfnPlan& fp, Ring& R, int F, in
         const float v = fold_rows<6>(rs, nb, 2 * items, xq, xd);     // lanes 2j, 2j+1: gate, up of row warp + 15 j
         const float u = __shfl_down_sync(0xffffffffu, v, 1);
         if (lane < 2 * items && (lane & 1) == 0) C.S->sv[bi][warp + (lane >> 1) * DEC_CWARPS] = silu_mul(v, u);
-    }
-    __syncwarp();
-    for (int c = 0; c < 2 * nbk; c++) {
-        if (lane == 0) mbar_arrive(&R.empty[R.stage]);
-        R.advance();
     }
     consumer_sync();
     if (warp < nbk) publish_block_q8((float2*)C.P->ws_v, F, b + warp, C.S->sv[warp][lane], C.tag, C.S->nrep);
@@ -881,10 +946,104 @@ __device__ __forceinline__ void attention_layer(const lt_decode_desc& P, const l
     consumer_sync();        // the shared-memory areas of this layer may be rewritten
 }
 
+// ---------------------------------------------------------------- GEMV CTA, one phase of one layer
+
+__device__ __forceinline__ void gemv_phase(const int PH, const lt_decode_desc& P, const lt_decode_layer* lys, int il, int L, unsigned tag0,
+                                           const DecSlots& SL, const Areas& A, Shared* S, EpiCtx& C) {
+    const GemvConst& GC = S->gc;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int E = P.E, F = P.F;
+    const lt_decode_layer* ly = lys + il;
+    const unsigned tag = tag0 + (unsigned)il;
+    const unsigned backoff = (unsigned)P.poll_ns;
+    const int epi = PH == 0 ? EPI_V : (PH == 1 ? EPI_O : EPI_DOWN);
+    const int K = PH == 1 ? C.nq : (PH == 3 ? F : E);
+    const int r0 = PH == 0 ? C.nq + C.nk + GC.v0 : (PH == 2 ? GC.b0 : GC.e0);
+    const int n = PH == 0 ? GC.nv : (PH == 2 ? GC.nbk : GC.ne);
+    const unsigned sb = GC.big + (unsigned)(PH == 0 ? SL.off[0] : (PH == 1 ? SL.off[1] : (PH == 2 ? SL.off[2] : SL.off[3])));
+    const unsigned db = PH == 2 ? GC.db[2] : sb + GC.db[PH];
+    const int pitch = SL.chunk;
+    C.ly = ly; C.tag = tag;
+    if (PH == 0) {
+        const int pos = S->lens[il];
+        C.room = (pos >= 0 && pos < P.max_seq);
+        C.pos = pos;
+    }
+    if (PH == 1) C.resid = A.fa;
+    if (PH == 3) C.resid = A.fb;
+    // ---- before the hand-over is awaited: the slot of the phase, every address, the epilogue's operands,
+    // the norm weight of the next phase (into registers)
+    SegPlan sp;
+    FfnPlan fp;
+    if (PH == 2) {
+        fp = ffn_prepare(sb, (unsigned)pitch, db, r0, r0, n < 2 ? n : 2, E);
+        if (n > 0) fp.ok = mbar_wait(&S->sfull[2], (unsigned)il & 1u, S, P.status);
+    } else {
+        sp = slot_prepare(epi, sb, db, r0, 0, n, K, &S->sfull[PH], (unsigned)il & 1u, C);
+    }
+    float nwr[DEC_XB / 2];
+    if (PH & 1) {
+        const float* nw = PH == 1 ? ly->ffn_norm : (il + 1 < L ? lys[il + 1].attn_norm : P.out_norm);
+#pragma unroll
+        for (int k = 0; k < DEC_XB / 2; k++) {
+            const int j = tid + k * DEC_CTHREADS;
+            nwr[k] = j < E ? __ldg(nw + j) : 0.0f;
+        }
+    }
+    C.tr.stamp(20);
+    // ---- the hand-over, then what depends on it
+    if ((PH & 1) == 0) {
+        float* sF = PH == 0 ? A.fa : A.fb;
+        fetch_x((const float2*)(PH == 0 ? P.ws_x : P.ws_x1), PH == 0 ? tag - 1u : tag, PH == 0 && il == 0, sF, E, S, P.status, backoff);
+        consumer_sync();
+        C.tr.stamp(21 + PH);
+        norm_quant(sF, A.w, E, P.eps, A.xq0, A.xd0, S);
+        consumer_sync();
+    } else {
+        fetch_q8((const float2*)(PH == 1 ? P.ws_att : P.ws_v), tag, PH == 1 ? C.nq : F, A.xq1, A.xd1, S, P.status, backoff);
+        // the norm weight of the next phase; every read of A.w in the previous phase is past a barrier
+#pragma unroll
+        for (int k = 0; k < DEC_XB / 2; k++) {
+            const int j = tid + k * DEC_CTHREADS;
+            if (j < E) A.w[j] = nwr[k];
+        }
+        consumer_sync();
+        C.tr.stamp(21 + PH);
+    }
+    const int8_t* sXq = (PH & 1) ? A.xq1 : A.xq0;
+    const __half* sXd = (PH & 1) ? A.xd1 : A.xd0;
+    if (PH == 2) {
+        const bool ok2 = fp.ok;
+        for (int b = r0; b < r0 + n; b += 2) {
+            if (b > r0) {
+                fp = ffn_prepare(sb, (unsigned)pitch, db, r0, b, r0 + n - b < 2 ? r0 + n - b : 2, E);
+                fp.ok = ok2;
+            }
+            ffn_finish(fp, F, b, r0 + n - b < 2 ? r0 + n - b : 2, b + 2 < r0 + n, E, sXq, sXd, C);
+        }
+    } else {
+        Ring none;      // (a slot's rows are not ring stages: nothing is handed back per set)
+        none.base = nullptr; none.full = nullptr; none.empty = nullptr; none.nstages = 1; none.stage = 0; none.fill = 0;
+        for (;;) {
+            seg_finish(epi, sp, none, K, sXq, sXd, C);
+            const int i = sp.r - r0 + sp.nset;
+            if (i >= n) break;
+            const bool ok1 = sp.ok;
+            sp = slot_prepare(epi, sb, db, r0, i, n, K, &S->sfull[PH], (unsigned)il & 1u, C);
+            sp.ok = ok1;
+        }
+    }
+    // this warp no longer reads the slot: the next layer's slice may be requested
+    __syncwarp();
+    if (lane == 0 && n > 0) mbar_arrive(&S->sempty[PH]);
+    C.tr.stamp(25 + PH);
+}
+
 // ---------------------------------------------------------------- the kernel
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
-k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages_att, int vcap, int fixed_bytes) {
+k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages_att, int vcap, int fixed_bytes,
+              const DecSlots SL) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int E = P.E, F = P.F, nq = P.nh * HD, nk = P.nkv * HD, L = P.n_layers, nbE = E >> 5;
     const int kmax1 = nq > F ? nq : F;
@@ -918,6 +1077,10 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             mbar_init(&S->full[s], 1);
             mbar_init(&S->empty[s], DEC_CWARPS);
         }
+        for (int p = 0; p < 4; p++) {
+            mbar_init(&S->sfull[p], 1);
+            mbar_init(&S->sempty[p], DEC_CWARPS);
+        }
         mbar_init(&S->wfull, 1);
         mbar_init(&S->wempty, DEC_CWARPS);
         mbar_init(&S->att_done, 1);
@@ -940,15 +1103,16 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         e0 = (int)(((long long)E * g) / NG); e1 = (int)(((long long)E * (g + 1)) / NG);
         b0 = (int)(((long long)(F >> 5) * g) / NG); b1 = (int)(((long long)(F >> 5) * (g + 1)) / NG);
     }
-    const int l0 = (int)(((long long)P.V * blockIdx.x) / G), l1 = (int)(((long long)P.V * (blockIdx.x + 1)) / G);
-
-    Ring R;
-    R.base = A.big; R.full = S->full; R.empty = S->empty; R.stage = 0; R.fill = 0;
-    R.nstages = att ? nstages_att : nstages;
 
     // ------------------------------------------------------------ producer warp
     if (warp == DEC_CWARPS) {
         if (lane != 0) return;
+        // this CTA's rows of the LM head and the ring they stream through
+        const int l0 = (int)(((long long)P.V * blockIdx.x) / G), l1 = (int)(((long long)P.V * (blockIdx.x + 1)) / G);
+        Ring R;
+        R.base = A.big; R.full = S->full; R.empty = S->empty; R.stage = 0; R.fill = 0;
+        R.nstages = att ? nstages_att : nstages;
+
         bool ok = true;
         if (att) {
             const int h = blockIdx.x, hk = h / (P.nh / P.nkv);
@@ -972,19 +1136,62 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
                 while (!mbar_try_wait(&S->wfull, (unsigned)armed & 1u))
                     if (clock64() - t0 > DEC_DRAIN_CLOCKS) break;
             }
+            if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status);
         } else {
+            // the slots: slice p of layer il is requested as soon as slice p of layer il - 1 has been folded
+            int armed[4] = {-1, -1, -1, -1};
+            const int nrows[4] = {v1 - v0, e1 - e0, b1 - b0, e1 - e0};
             for (int il = 0; il < L && ok; il++) {
                 const lt_decode_layer* ly = lys + il;
-                ok = produce_segment(R, ly->qkv_q, (const __half*)ly->qkv_d, nq + nk + v0, nq + nk + v1, E, rows_per_chunk(E), S, P.status);
-                if (ok) ok = produce_segment(R, ly->o_q, (const __half*)ly->o_d, e0, e1, nq, rows_per_chunk(nq), S, P.status);
-                for (int b = b0; b < b1 && ok; b++) {
-                    ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, b * 32, b * 32 + 32, E, rows_per_chunk(E), S, P.status);
-                    if (ok) ok = produce_segment(R, ly->gu_q, (const __half*)ly->gu_d, F + b * 32, F + b * 32 + 32, E, rows_per_chunk(E), S, P.status);
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (nrows[p] <= 0 || !ok) continue;
+                    if (il > 0) ok = mbar_wait(&S->sempty[p], (unsigned)(il - 1) & 1u, S, P.status);
+                    if (!ok) continue;
+                    unsigned char* dst = A.big + SL.off[p];
+                    armed[p] = il;
+                    if (p == 0) {
+                        const __half* Wd = (const __half*)ly->qkv_d;
+                        mbar_expect_tx(&S->sfull[0], slot_bytes(Wd, nq + nk + v0, v1 - v0, E));
+                        slot_request(dst, ly->qkv_q, Wd, nq + nk + v0, v1 - v0, E, &S->sfull[0]);
+                    } else if (p == 1) {
+                        const __half* Wd = (const __half*)ly->o_d;
+                        mbar_expect_tx(&S->sfull[1], slot_bytes(Wd, e0, e1 - e0, nq));
+                        slot_request(dst, ly->o_q, Wd, e0, e1 - e0, nq, &S->sfull[1]);
+                    } else if (p == 2) {
+                        const __half* Wd = (const __half*)ly->gu_d;
+                        unsigned total = 0;
+                        for (int b = b0; b < b1; b++) total += slot_bytes(Wd, b * 32, 32, E) + slot_bytes(Wd, F + b * 32, 32, E);
+                        mbar_expect_tx(&S->sfull[2], total);
+                        for (int b = b0; b < b1; b++) {
+                            slot_request(dst + (size_t)(2 * (b - b0)) * SL.chunk, ly->gu_q, Wd, b * 32, 32, E, &S->sfull[2]);
+                            slot_request(dst + (size_t)(2 * (b - b0) + 1) * SL.chunk, ly->gu_q, Wd, F + b * 32, 32, E, &S->sfull[2]);
+                        }
+                    } else {
+                        const __half* Wd = (const __half*)ly->down_d;
+                        mbar_expect_tx(&S->sfull[3], slot_bytes(Wd, e0, e1 - e0, F));
+                        slot_request(dst, ly->down_q, Wd, e0, e1 - e0, F, &S->sfull[3]);
+                    }
                 }
-                if (ok) ok = produce_segment(R, ly->down_q, (const __half*)ly->down_d, e0, e1, F, rows_per_chunk(F), S, P.status);
+            }
+            // the LM-head ring lies over the slots: its stages below the down slot may be requested once the
+            // last layer's v, o_proj and gate|up slices have been folded, the others after its down slice
+#pragma unroll
+            for (int p = 0; p < 3; p++)
+                if (ok && nrows[p] > 0) ok = mbar_wait(&S->sempty[p], (unsigned)(L - 1) & 1u, S, P.status);
+            if (ok)
+                ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status,
+                                     nrows[3] > 0 ? &S->sempty[3] : nullptr, (unsigned)(L - 1) & 1u, SL.off[3] / DEC_STAGE_STRIDE);
+            if (!ok || S->abort_flag) {       // gave up: let the requested slices land before the CTA exits
+                const long long t0 = clock64();
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (armed[p] < 0) continue;
+                    while (!mbar_try_wait(&S->sfull[p], (unsigned)armed[p] & 1u))
+                        if (clock64() - t0 > DEC_DRAIN_CLOCKS) break;
+                }
             }
         }
-        if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status);
         if (!ok || S->abort_flag) producer_drain(R);
         return;
     }
@@ -1020,8 +1227,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
         for (int j = tid; j < E; j += DEC_CTHREADS) A.w[j] = __ldg(lys[0].attn_norm + j);
     }
 
-    // ---- weight phases, one copy of the code: four per layer for the GEMV CTAs, then the LM head for
-    // every CTA (phase 0 of a layer "L").  Phase p of layer il:
+    // ---- GEMV CTAs: four weight phases per layer.  Phase p of layer il:
     //   0  x  -> RMSNorm -> quantiser -> this CTA's v rows             (x of layer il: tag of layer il - 1)
     //   1  quantised attention output -> o_proj + x -> x1
     //   2  x1 -> RMSNorm -> quantiser -> gate|up blocks -> quantised silu(gate)*up
@@ -1029,86 +1235,51 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
     EpiCtx C;
     C.tr = tr; C.P = &P; C.S = S; C.nq = nq; C.nk = nk; C.bestv = -3.4e38f; C.besti = 2147483647;
     C.resid = A.fa; C.tag = 0; C.pos = 0; C.room = 0; C.ly = lys;
-    for (int idx = att ? 4 * L : 0; idx <= 4 * L; idx++) {
-        const int il = idx >> 2, ph = idx & 3;
-        const bool lm = (il == L);
-        const lt_decode_layer* ly = lys + (lm ? L - 1 : il);
-        const unsigned tag = tag0 + (unsigned)il;
-        C.ly = ly; C.tag = tag;
-        // ---- before the hand-over is awaited: the weight stages of the phase, every address, the
-        // epilogue's operands, the norm weight of the next phase (into registers)
-        int epi = EPI_LOGITS, r0 = l0, r1 = l1, K = E;
+    if (!att) {
+        // what a phase needs of its slot does not depend on the layer (the launcher checks that a matrix kind's
+        // scale arrays are aligned alike in every layer): computed once
+        if (tid == 0) {
+            GemvConst GC;
+            GC.big = smem_u32(A.big);
+            GC.v0 = v0; GC.nv = v1 - v0; GC.e0 = e0; GC.ne = e1 - e0; GC.b0 = b0; GC.nbk = b1 - b0;
+            GC.db[0] = (unsigned)((v1 - v0) * E) + (unsigned)(reinterpret_cast<uintptr_t>((const __half*)lys[0].qkv_d + (size_t)(nq + nk + v0) * nbE) & 15);
+            GC.db[1] = (unsigned)((e1 - e0) * nq) + (unsigned)(reinterpret_cast<uintptr_t>((const __half*)lys[0].o_d + (size_t)e0 * (nq >> 5)) & 15);
+            GC.db[2] = (unsigned)(reinterpret_cast<uintptr_t>(lys[0].gu_d) & 15);
+            GC.db[3] = (unsigned)((e1 - e0) * F) + (unsigned)(reinterpret_cast<uintptr_t>((const __half*)lys[0].down_d + (size_t)e0 * (F >> 5)) & 15);
+            S->gc = GC;
+        }
+        consumer_sync();
+        for (int idx = 0; idx < 4 * L; idx++) gemv_phase(idx & 3, P, lys, idx >> 2, L, tag0, SL, A, S, C);
+    }
+
+    // ---- the LM head, every CTA: final x -> RMSNorm (output norm) -> quantiser -> this CTA's rows of the
+    // LM-head matrix, streamed through the ring, with the running argmax
+    {
+        const int l0 = (int)(((long long)P.V * blockIdx.x) / G), l1 = (int)(((long long)P.V * (blockIdx.x + 1)) / G);
+        Ring R;
+        R.base = A.big; R.full = S->full; R.empty = S->empty; R.stage = 0; R.fill = 0;
+        R.nstages = att ? nstages_att : nstages;
+        const unsigned tag = tag0 + (unsigned)L;
+        C.ly = lys + (L - 1); C.tag = tag;
         const __half* Wd = (const __half*)P.lm_d;
-        if (!lm) {
-            if (ph == 0) {
-                const int pos = S->lens[il];
-                C.room = (pos >= 0 && pos < P.max_seq);
-                C.pos = pos;
-                epi = EPI_V; Wd = (const __half*)ly->qkv_d; r0 = nq + nk + v0; r1 = nq + nk + v1;
-            } else if (ph == 1) {
-                epi = EPI_O; Wd = (const __half*)ly->o_d; r0 = e0; r1 = e1; K = nq; C.resid = A.fa;
-            } else if (ph == 3) {
-                epi = EPI_DOWN; Wd = (const __half*)ly->down_d; r0 = e0; r1 = e1; K = F; C.resid = A.fb;
-            }
-        }
-        SegPlan sp;
-        FfnPlan fp;
-        if (ph == 2) fp = ffn_prepare(R, (const __half*)ly->gu_d, F, b0, b1 - b0 < 2 ? b1 - b0 : 2, E, C);
-        const int RC = lm ? rows_per_chunk_lm(K) : rows_per_chunk(K);
-        // recurring sets take their plan from the memo: the layer phases from the second layer on, the
-        // full sets of the LM head from its second set on
-        const int kind = lm ? 3 : (ph == 0 ? 0 : (ph == 1 ? 1 : 2));
+        const int RC = rows_per_chunk_lm(E);
+        // the full sets take their plan from the memo from the second set on
         const int full_lm = DEC_CWARPS * DEC_ILP;
-        if (ph != 2) sp = seg_prepare(epi, R, Wd, r0, r0, r1, K, RC, C, S->memo[kind][warp],
-                                      lm ? (r1 - r0 >= full_lm && 2 * RC == full_lm && (RC * (K >> 5) * 2) % 16 == 0 ? 1 : 0)
-                                         : (il == 0 ? 1 : 2));
-        float nwr[DEC_XB / 2];
-        if (ph & 1) {
-            const float* nw = ph == 1 ? ly->ffn_norm : (il + 1 < L ? lys[il + 1].attn_norm : P.out_norm);
-#pragma unroll
-            for (int k = 0; k < DEC_XB / 2; k++) {
-                const int j = tid + k * DEC_CTHREADS;
-                nwr[k] = j < E ? __ldg(nw + j) : 0.0f;
-            }
-        }
+        const bool lm_memo = l1 - l0 >= full_lm && 2 * RC == full_lm && (RC * nbE * 2) % 16 == 0;
+        SegPlan sp = seg_prepare(EPI_LOGITS, R, Wd, l0, l0, l1, E, RC, C, S->memo[warp], lm_memo ? 1 : 0);
         C.tr.stamp(20);
-        // ---- the hand-over, then what depends on it
-        if ((ph & 1) == 0) {
-            float* sF = ph == 0 ? A.fa : A.fb;
-            fetch_x((const float2*)(ph == 0 ? P.ws_x : P.ws_x1), ph == 0 ? tag - 1u : tag, idx == 0, sF, E, S, P.status, backoff);
-            consumer_sync();
-            C.tr.stamp(21 + ph);
-            norm_quant(sF, A.w, E, P.eps, A.xq0, A.xd0, S);
-            consumer_sync();
-        } else {
-            fetch_q8((const float2*)(ph == 1 ? P.ws_att : P.ws_v), tag, ph == 1 ? nq : F, A.xq1, A.xd1, S, P.status, backoff);
-            // the norm weight of the next phase; every read of A.w in the previous phase is past a barrier
-#pragma unroll
-            for (int k = 0; k < DEC_XB / 2; k++) {
-                const int j = tid + k * DEC_CTHREADS;
-                if (j < E) A.w[j] = nwr[k];
-            }
-            consumer_sync();
-            C.tr.stamp(21 + ph);
+        fetch_x((const float2*)P.ws_x, tag - 1u, false, A.fa, E, S, P.status, backoff);
+        consumer_sync();
+        C.tr.stamp(21);
+        norm_quant(A.fa, A.w, E, P.eps, A.xq0, A.xd0, S);
+        consumer_sync();
+        for (;;) {
+            seg_finish(EPI_LOGITS, sp, R, E, A.xq0, A.xd0, C);
+            const int r = sp.r + sp.nset;
+            if (r >= l1) break;
+            sp = seg_prepare(EPI_LOGITS, R, Wd, l0, r, l1, E, RC, C, S->memo[warp], (lm_memo && l1 - r >= full_lm) ? 2 : 0);
         }
-        const int8_t* sXq = (ph & 1) ? A.xq1 : A.xq0;
-        const __half* sXd = (ph & 1) ? A.xd1 : A.xd0;
-        if (ph == 2) {
-            for (int b = b0; b < b1; b += 2) {
-                if (b > b0) fp = ffn_prepare(R, (const __half*)ly->gu_d, F, b, b1 - b < 2 ? b1 - b : 2, E, C);
-                ffn_finish(fp, R, F, b, b1 - b < 2 ? b1 - b : 2, b + 2 < b1, E, sXq, sXd, C);
-            }
-        } else {
-            for (;;) {
-                seg_finish(epi, sp, R, K, sXq, sXd, C);
-                const int r = sp.r + sp.nset;
-                if (r >= r1) break;
-                sp = seg_prepare(epi, R, Wd, r0, r, r1, K, RC, C, S->memo[kind][warp],
-                                 (lm && r1 - r >= full_lm && 2 * RC == full_lm && r1 - r0 >= full_lm &&
-                                  (RC * (K >> 5) * 2) % 16 == 0) ? 2 : 0);
-            }
-        }
-        C.tr.stamp(25 + ph);
+        C.tr.stamp(25);
     }
     C.tr.stamp(32);
     float bestv = C.bestv;
@@ -1173,6 +1344,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
 }
 
 struct DecodeGeometry {
+    DecSlots slots;
     int nstages, nstages_att, vcap, fixed_bytes;
     size_t smem;
     int ctas;
@@ -1219,6 +1391,24 @@ static int decode_geometry(const lt_decode_desc* d, DecodeGeometry* g) {
         if (big < 2 * (size_t)DEC_STAGE_STRIDE) big = 2 * (size_t)DEC_STAGE_STRIDE;
     }
     if (big_att > big) big = big_att;
+    // GEMV CTA: the slots of the four layer phases, sized for the largest share of a CTA
+    {
+        const int NG = sms - d->nh > 0 ? sms - d->nh : 1;
+        const int nk = d->nkv * hd, nbE = E >> 5;
+        const size_t mV = (size_t)(nk + NG - 1) / NG, mE = (size_t)(E + NG - 1) / NG, mB = (size_t)((F >> 5) + NG - 1) / NG;
+        const size_t chunk = up128((size_t)32 * E + (size_t)32 * nbE * 2 + 32);
+        const size_t sz[4] = {up128(mV * E + mV * nbE * 2 + 32), up128(mE * nq + mE * (nq >> 5) * 2 + 32), mB * 2 * chunk,
+                              up128(mE * F + mE * (F >> 5) * 2 + 32)};
+        size_t o = 0;
+        for (int p = 0; p < 4; p++) { g->slots.off[p] = (int)o; o += sz[p]; }
+        g->slots.chunk = (int)chunk;
+        if (fixed + o > avail) {
+            set_error("lt_decode_step: a CTA's share of one layer (%zu bytes) does not fit shared memory beside %zu fixed bytes",
+                      o, fixed);
+            return LT_ERR_UNSUPPORTED;
+        }
+        if (o > big) big = o;
+    }
     g->nstages_att = nsa;
     g->fixed_bytes = (int)fixed;
     g->smem = fixed + big;
@@ -1276,9 +1466,10 @@ static int decode_check(const lt_decode_desc* d, DecodeGeometry* g) {
     LT_REQUIRE(aligned16(d->lm_q), "lt_decode_step: the LM-head matrix must be 16-byte aligned");
     for (int il = 1; il < d->n_layers; il++) {
         const lt_decode_layer *a = d->h_layers, *b = d->h_layers + il;
-        // (the kernel remembers where a warp's rows lie in a ring stage from the first layer on)
+        // (the kernel works out once, from the first layer, where the scale rows of a slice lie in its slot)
         LT_REQUIRE(((uintptr_t)a->qkv_d & 15) == ((uintptr_t)b->qkv_d & 15) && ((uintptr_t)a->o_d & 15) == ((uintptr_t)b->o_d & 15) &&
-                       ((uintptr_t)a->down_d & 15) == ((uintptr_t)b->down_d & 15) && (a->qkv_bias == nullptr) == (b->qkv_bias == nullptr),
+                       ((uintptr_t)a->down_d & 15) == ((uintptr_t)b->down_d & 15) && ((uintptr_t)a->gu_d & 15) == ((uintptr_t)b->gu_d & 15) &&
+                       (a->qkv_bias == nullptr) == (b->qkv_bias == nullptr),
                    "lt_decode_step: the scale arrays of layer %d are aligned differently from layer 0's", il);
     }
     int rc = decode_geometry(d, g);
@@ -1307,7 +1498,8 @@ extern "C" int lt_decode_step(const lt_decode_desc* d, void* stream) {
     if (P.status == nullptr) P.status = device_status_ptr();
     LT_REQUIRE(P.status != nullptr, "lt_decode_step: status word unavailable");
     int nstages = g.nstages, nsa = g.nstages_att, vcap = g.vcap, fixed = g.fixed_bytes;
-    void* args[] = {&P, &nstages, &nsa, &vcap, &fixed};
+    DecSlots slots = g.slots;
+    void* args[] = {&P, &nstages, &nsa, &vcap, &fixed, &slots};
     const void* kern = d->hd == 32 ? (const void*)k_decode_step<32> : (const void*)k_decode_step<64>;
     LT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
     // cooperative launch: all CTAs are resident together, which the data-flow waits rely on
