@@ -56,7 +56,7 @@ UNIT = "tok/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE token's launches, from an ncu capture of
 # this very command, keyed by step mode; None where not captured.
-NCU_TRAFFIC = {"pdl": 530232064, "persistent": 526927744}
+NCU_TRAFFIC = {"pdl": 530232064, "persistent": 526754816}
 
 
 def _peaks():
@@ -84,7 +84,7 @@ class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks.mem,clocks.max.mem")
 
     def __init__(self, index):
         self.index = index; self.lines = []; self.proc = None
@@ -111,7 +111,7 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, mem, memx, reasons = [], [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
@@ -124,8 +124,13 @@ class ClockSampler:
             for n, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
+            try:
+                mem.append(float(f[9])); memx.append(float(f[10]))
+            except (ValueError, IndexError):
+                pass
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "mem_mhz": float(np.median(mem)) if mem else None, "mem_max_mhz": max(memx) if memx else None}
 
 
 def cpu_decode_baseline(model, prompt, budget_s=15.0, max_tokens=16):
@@ -451,6 +456,19 @@ def main():
     torch.cuda.synchronize()
     lm_us = 1000.0 * e0.elapsed_time(e1) / 20
     lm_gbs = gemv_bytes(N_, K_) / (lm_us * 1e-6) / 1e9
+    # what this GPU's memory delivers right now: a device-to-device copy of 1 GiB (read + write counted), the same
+    # kind of figure as the measured peak; a value far below the peak means the roofline fraction above is that
+    # of a slowed GPU, not of the kernel
+    src = torch.empty(1 << 30, dtype=torch.uint8, device="cuda"); dst = torch.empty_like(src)
+    for _ in range(2):
+        dst.copy_(src)
+    c0 = torch.cuda.Event(enable_timing=True); c1 = torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(5):
+        dst.copy_(src)
+    c1.record(); torch.cuda.synchronize()
+    copy_gbs = 5 * 2 * (1 << 30) / (c0.elapsed_time(c1) * 1e-3) / 1e9
+    del src, dst
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC.get(step_mode),
                 "kernel": "decode step = %d launches per token (%s)" % (
@@ -463,6 +481,8 @@ def main():
                 "algorithmic_bytes_per_token": step_bytes,
                 "us_per_token": 1000.0 * dev_ms / K,
                 "peak_source": peak_src,
+                "hbm_copy_live": {"gbs": copy_gbs, "frac_of_peak": copy_gbs / peak,
+                                  "what": "1 GiB device-to-device copy timed in this run (read + write bytes)"},
                 "lm_head_gemv_alone": {"kernel": "lt::k_q8_gemv1<4,1>", "shape": [N_, K_], "us": lm_us,
                                        "achieved": lm_gbs, "frac": lm_gbs / peak}}
 
