@@ -374,6 +374,19 @@ int lt_allreduce_add(const lt_comm* comm, const float* part, const float* resid,
 int lt_allreduce_add_tree(const lt_comm* comm, const float* part, const float* resid, float* out, int n,
                           void* stream);
 
+/* Greedy tokens of B sequences whose logits are split by vocabulary over the ranks of a comm: this rank
+ * holds columns [v0, v0 + nv) as logits[b*ld + i].  Two launches: per-row partial maxima, then one CTA that
+ * finishes each row, pushes this rank's (maximum, global index) to every rank as two tagged words (the
+ * lt_allreduce_add exchange, elements 2b and 2b+1 of its first CTA, so the call must come at the same place
+ * of the call sequence on every rank) and keeps the maximum over the ranks, lowest index on ties (the
+ * reference's k_argmax_s1 / k_argmax_s2 rule, bpd/lib/dev_residency.py:226-271): tok[b] is the same on every
+ * rank, with no host step in between.  comm NULL or world 1: no exchange, tok[b] = v0 + local index.
+ * `partials` is caller scratch of lt_argmax_rows_scratch_bytes(B) bytes; 2*B <= 1024 and <= max_n of the comm.
+ * Bounded waits (LT_STATUS_WAIT_TIMEOUT; tok[b] is left unwritten for a row whose wait gave up). */
+int lt_argmax_rows(const lt_comm* comm, const float* logits, long ld, int nv, int v0, int B, void* partials,
+                   int* tok, void* stream);
+int lt_argmax_rows_scratch_bytes(int B);
+
 /* Partial GEMV of a tensor-parallel row split that keeps the one-GPU bits.  The `group` ranks deal the Q8_0
  * blocks of every row round-robin (rank r holds blocks b = r mod group, i.e. the blocks of the contract's
  * lanes L = r mod group, q8_0_from_facts.pl:476); Wq / Wd are this rank's blocks, K its share of the row

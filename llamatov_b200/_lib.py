@@ -16,6 +16,7 @@ STATUS_BITS = {1: "kv_overflow", 2: "bad_length", 4: "bad_token", 8: "wait_timeo
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
 _f = ctypes.c_float
+_l = ctypes.c_long
 
 # name -> argtypes (all return int unless listed in _RESTYPES)
 SIGNATURES = {
@@ -38,6 +39,7 @@ SIGNATURES = {
     "lt_attn_decode_masked": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "lt_argmax": [_vp, _i, _vp, _vp, _vp],
     "lt_argmax_scratch_bytes": [],
+    "lt_argmax_rows_scratch_bytes": [_i],
     "lt_embed_q8": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_token_record": [_vp, _vp, _vp, _i, _vp],
     "lt_embed_q8_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -56,6 +58,7 @@ SIGNATURES = {
     "lt_comm_free": [_vp],
     "lt_allreduce_add": [_vp, _vp, _vp, _vp, _i, _vp],
     "lt_allreduce_add_tree": [_vp, _vp, _vp, _vp, _i, _vp],
+    "lt_argmax_rows": [_vp, _vp, _l, _i, _i, _i, _vp, _vp, _vp],
     "lt_q8_gemv_lanes": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lt_q8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_q8_linear_static_max_k": [],

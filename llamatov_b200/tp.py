@@ -247,7 +247,7 @@ class TPDecoder:
         if self.attn_split > 0:
             n = max(n, _lib.lib().lt_attn_decode_split_scratch_floats(p.nh_l, p.hd, self.attn_split, B))
         self.scratch = torch.empty(n, **f32)
-        self.amax_part = torch.empty(_lib.lib().lt_argmax_scratch_bytes() // 4 * B, **f32)
+        self.amax_part = torch.empty(_lib.lib().lt_argmax_rows_scratch_bytes(B) // 4, **f32)
         self.loc_idx = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self.ticket = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self.pair = torch.zeros((B, 2), **f32)                   # (value, global index as float bits) per sequence
@@ -443,13 +443,15 @@ class TPDecoder:
             self._row_split(ly["down"], self.x1, self.x, exact=self.exact)
         self._norm_gemm(self.x, self.out_norm, self.lm, self.logits)
         nv = self.lm.N
-        stride = _lib.lib().lt_argmax_scratch_bytes() // 4
-        for b in range(B):
-            _lib.call("lt_argmax", self.logits[b].data_ptr(), nv, self.amax_part[b * stride:].data_ptr(),
-                      self.loc_idx[b:].data_ptr(), st())
-        if self.world == 1:
-            self.tok.copy_(self.loc_idx)
+        ld = int(self.logits.stride(0))
+        if self.world == 1 or self.comm is not None:
+            # the rows' maxima, the exchange of (maximum, global index) over the ranks and the lowest-index
+            # combine in two launches; the token lands in self.tok on every rank
+            _lib.call("lt_argmax_rows", None if self.comm is None else ctypes.byref(self.comm.c), self.logits.data_ptr(), ld, nv,
+                      self.v0, B, self.amax_part.data_ptr(), self.tok.data_ptr(), st())
         else:
+            _lib.call("lt_argmax_rows", None, self.logits.data_ptr(), ld, nv, 0, B, self.amax_part.data_ptr(),
+                      self.loc_idx.data_ptr(), st())
             idx = self.loc_idx.long()
             self.pair[:, 0] = self.logits.gather(1, idx.view(B, 1)).view(B)
             self.pair[:, 1] = (idx + self.v0).to(torch.int32).view(torch.float32)      # index carried as bits

@@ -387,6 +387,29 @@ def test_argmax_exact(oracle):
     assert int(out.item()) == oracle.argmax(v) == 2147483647
 
 
+def test_argmax_rows_exact(oracle):
+    """lt_argmax_rows without a comm: every row's argmax (lowest index on ties) plus the slice offset v0, rows
+    taken from a wider matrix (ld > nv)."""
+    rng = np.random.default_rng(1)
+    for B, nv, ld, v0 in ((1, 5, 5, 0), (3, 257, 300, 1000), (32, 16032, 16032, 16032 * 3), (40, 4097, 4100, 7),
+                          (2, 151936, 151936, 0)):
+        m = rng.standard_normal((B, ld)).astype(np.float32)
+        if nv > 300:
+            m[0, [nv - 1, 17, 200]] = 9.0                               # ties -> lowest index
+            m[B - 1, :nv] = -np.inf                                      # reference sentinel
+        if ld > nv:
+            m[:, nv:] = 100.0                                            # outside the slice: must be ignored
+        dm = dev(m)
+        part = torch.empty(_lib.lib().lt_argmax_rows_scratch_bytes(B), dtype=torch.uint8, device="cuda")
+        out = torch.full((B,), -5, dtype=torch.int32, device="cuda")
+        _lib.call("lt_argmax_rows", None, dm.data_ptr(), ld, nv, v0, B, part.data_ptr(), out.data_ptr(), stream())
+        got = host(out)
+        for b in range(B):
+            want = oracle.argmax(m[b, :nv])
+            assert int(got[b]) == (want + v0 if want != 2147483647 else want), (B, nv, b)
+    assert not _lib.device_status()
+
+
 def test_embed_gather(oracle):
     V, E = 1000, 896
     Wq, Wd, _ = synth.gemv_case(V, E, seed=5)

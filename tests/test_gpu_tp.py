@@ -212,3 +212,30 @@ def test_world2_matches_world1(tmp_path):
         # exact row split of down: both exchange paths give the one-GPU bits
         for name in ("down_exact_p2p", "down_exact_nccl"):
             assert np.array_equal(res[k][name].view(np.uint32), want_down.view(np.uint32)), (k, name)
+
+
+def _run_comm_worker(tmp_path, world):
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(root, "tests", "comm_worker.py"), str(tmp_path)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    r = subprocess.run(cmd, env=env, cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    for k in range(world):
+        res = np.load(os.path.join(str(tmp_path), f"comm{k}.npz"))
+        assert int(res["ok_sum"]) == 1, k          # all-reduce = the rank-order fp32 sum, bit for bit
+        assert int(res["ok_tok"]) == 1, k          # tokens over vocabulary slices = argmax of the whole rows
+        assert int(res["status"]) == 0, k
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_exchange_kernels_world2(tmp_path):
+    """lt_allreduce_add and lt_argmax_rows called directly on two ranks (tests/comm_worker.py)."""
+    _run_comm_worker(tmp_path, 2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_exchange_kernels_world4(tmp_path):
+    """The same on four ranks, where long vectors take the two-stage all-reduce."""
+    _run_comm_worker(tmp_path, 4)
