@@ -262,6 +262,229 @@ k_attn_prefill(const float* __restrict__ Q, int q_ld, const float* __restrict__ 
     }
 }
 
+// ---- the same attention for 16 query rows per CTA (one CTA of 512 threads per SM).  A tile of K (then V) rows
+// serves 16 query rows (half the L2 traffic of the 8-row kernel above), the next tile's asynchronous copy runs
+// while this one is used (two buffers; the copies then cost ~1 k cycles per tile, barriers included, and nothing
+// waits for them), and the first V tile is requested before the softmax.  What is left is shared-memory reads
+// per fused multiply-add, so both folds are blocked in registers: a score thread owns two positions and four
+// query rows (two K reads and four broadcast q reads per 32 FMAs), a V-sum thread two neighbouring output
+// elements of two query rows.  Every (row, head) result is the one-token kernel's, bit for bit.
+constexpr int PW_THREADS = 512;
+constexpr int PW_QT = 16;
+constexpr int PW_TILE = 128;             // positions per staged tile of K or V rows
+
+template <int HD>
+__global__ void __launch_bounds__(PW_THREADS, 1)
+k_attn_prefill_wide(const float* __restrict__ Q, int q_ld, const float* __restrict__ K, const float* __restrict__ V,
+                    const int* __restrict__ len_ptr, float* __restrict__ OUT, int out_ld, int nh, int nkv, float scale,
+                    int nrows, int maxt, int* status) {
+    constexpr int QT = PW_QT, KST = HD + 4;
+    extern __shared__ __align__(16) float pf_smem[];
+    float* qs = pf_smem;                     // [QT][HD]
+    float* red = qs + QT * HD;               // [QT][64]
+    float* zs = red + QT * 64;               // [QT] max, then Z
+    float* tiles = zs + QT;                  // [2][PW_TILE][KST]
+    float* sc = tiles + 2 * PW_TILE * KST;   // [QT][ld]
+    const int ld = (maxt + 3) & ~3;
+    const int tid = threadIdx.x;
+    const int h = blockIdx.y;
+    const int r0 = blockIdx.x * QT;
+    const int Lafter = *len_ptr;
+    if (Lafter < nrows || Lafter > maxt) {
+        if (tid == 0) atomicOr(status, (int)LT_STATUS_BAD_LENGTH);
+        return;
+    }
+    const int L0 = Lafter - nrows;
+    const int nq = nrows - r0 < QT ? nrows - r0 : QT;   // query rows of this tile
+    const int Lmax = L0 + r0 + nq;                      // positions the last row sees
+    const int hk = h / (nh / nkv);
+    const long rstride = (long)nkv * HD;                // floats between two positions of a cache
+
+    auto copy_tile = [&](const float* base, int t0, float* dst) {     // positions [t0, t0 + PW_TILE) of head hk, one commit group
+        const int nt = Lmax - t0 < PW_TILE ? Lmax - t0 : PW_TILE;
+        const float* src = base + (long)hk * HD + (long)t0 * rstride;
+        for (int e = tid; e < nt * (HD / 4); e += PW_THREADS) {
+            const int r = e / (HD / 4), c = e - r * (HD / 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst + r * KST + c * 4)),
+                         "l"(src + (long)r * rstride + c * 4) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    copy_tile(K, 0, tiles);
+    for (int i = tid; i < QT * HD; i += PW_THREADS) {
+        const int qi = i / HD, d = i - qi * HD;
+        qs[i] = qi < nq ? Q[(long)(r0 + qi) * q_ld + (long)h * HD + d] : 0.0f;
+    }
+
+    // ---- scores: a thread owns two positions of the tile (p and p + 64) and four query rows: eight chains fed by two
+    // 16-byte reads of K rows and four broadcast reads of q per four elements (half the shared-memory traffic per
+    // fused multiply-add of one position per thread); 256 threads fold, all copy
+    constexpr int QH = 4, PH = PW_TILE / 2;
+    const int p = tid & (PH - 1), qh = tid / PH;
+    for (int t0 = 0, buf = 0; t0 < Lmax; t0 += PW_TILE, buf ^= 1) {
+        const bool more = t0 + PW_TILE < Lmax;
+        if (more) copy_tile(K, t0 + PW_TILE, tiles + (buf ^ 1) * PW_TILE * KST);
+        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                    // tile t0 has landed (and, first pass, the q rows are stored)
+        const int nt = Lmax - t0 < PW_TILE ? Lmax - t0 : PW_TILE;
+        if (qh < QT / QH && p < nt) {
+            const bool two = p + PH < nt;
+            const float4* Ka = (const float4*)(tiles + buf * PW_TILE * KST + p * KST);
+            const float4* Kb = (const float4*)(tiles + buf * PW_TILE * KST + (two ? p + PH : p) * KST);
+            const float4* Qt = (const float4*)(qs + qh * QH * HD);
+            float sa[QH], sb[QH];
+#pragma unroll
+            for (int qi = 0; qi < QH; qi++) { sa[qi] = 0.0f; sb[qi] = 0.0f; }
+#pragma unroll 4
+            for (int i = 0; i < HD / 4; i++) {
+                const float4 ka = Ka[i], kb = Kb[i];
+                float4 qq[QH];
+#pragma unroll
+                for (int qi = 0; qi < QH; qi++) qq[qi] = Qt[qi * (HD / 4) + i];
+#pragma unroll
+                for (int qi = 0; qi < QH; qi++) { sa[qi] = __fmaf_rn(qq[qi].x, ka.x, sa[qi]); sb[qi] = __fmaf_rn(qq[qi].x, kb.x, sb[qi]); }
+#pragma unroll
+                for (int qi = 0; qi < QH; qi++) { sa[qi] = __fmaf_rn(qq[qi].y, ka.y, sa[qi]); sb[qi] = __fmaf_rn(qq[qi].y, kb.y, sb[qi]); }
+#pragma unroll
+                for (int qi = 0; qi < QH; qi++) { sa[qi] = __fmaf_rn(qq[qi].z, ka.z, sa[qi]); sb[qi] = __fmaf_rn(qq[qi].z, kb.z, sb[qi]); }
+#pragma unroll
+                for (int qi = 0; qi < QH; qi++) { sa[qi] = __fmaf_rn(qq[qi].w, ka.w, sa[qi]); sb[qi] = __fmaf_rn(qq[qi].w, kb.w, sb[qi]); }
+            }
+#pragma unroll
+            for (int qi = 0; qi < QH; qi++) {
+                const int q = qh * QH + qi;
+                const int ta = t0 + p, tb2 = ta + PH;
+                sc[q * ld + ta] = ta < L0 + r0 + q + 1 ? __fmul_rn(sa[qi], scale) : -1e30f;
+                if (two) sc[q * ld + tb2] = tb2 < L0 + r0 + q + 1 ? __fmul_rn(sb[qi], scale) : -1e30f;
+            }
+        }
+        __syncthreads();                    // the tile may be overwritten, the scores are visible
+    }
+    // the first V tile travels while the softmax runs
+    copy_tile(V, 0, tiles);
+
+    // ---- softmax per query row on the frozen 64-lane layout: 8 rows at a time, 64 threads each
+    const int grp = tid >> 6, l64 = tid & 63;
+    for (int qb = 0; qb < QT; qb += PW_THREADS / 64) {
+        const int qi = qb + grp;
+        float* row = sc + qi * ld;
+        float m = -1e30f;
+        for (int t = l64; t < Lmax; t += 64) m = fmaxf(m, row[t]);
+        red[qi * 64 + l64] = m;
+        __syncthreads();
+        if (l64 < 32) {
+            float v = fmaxf(red[qi * 64 + l64], red[qi * 64 + l64 + 32]);
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+            if (l64 == 0) zs[qi] = v;
+        }
+        __syncthreads();
+        const float mx = zs[qi];
+        float ls = 0.0f;
+        for (int t = l64; t < Lmax; t += 64) {      // a lane sums what it has just written: no barrier in between
+            const float e = __expf(__fsub_rn(row[t], mx));
+            row[t] = e;
+            ls = __fadd_rn(ls, e);
+        }
+        red[qi * 64 + l64] = ls;
+        __syncthreads();
+        if (l64 < 32) {
+            float v = __fadd_rn(red[qi * 64 + l64], red[qi * 64 + l64 + 32]);
+            v = warp_tree_sum(v);
+            if (l64 == 0) zs[qi] = v;
+        }
+        __syncthreads();
+    }
+
+    // ---- V sum: thread = (group of two query rows, two neighbouring output elements); 256 threads fold, all copy
+    constexpr int DV = 2, TPG = HD / DV, RPG = 2, NG = QT / RPG;
+    static_assert(NG * TPG <= PW_THREADS, "row groups");
+    const int g = tid / TPG, d = (tid - g * TPG) * DV;
+    const bool folds = g < NG;
+    float2 acc[RPG];
+    int Lr[RPG];
+#pragma unroll
+    for (int k = 0; k < RPG; k++) {
+        acc[k] = make_float2(0.0f, 0.0f);
+        const int qi = g * RPG + k;
+        Lr[k] = (folds && qi < nq) ? L0 + r0 + qi + 1 : 0;
+    }
+    // positions every row of the tile sees are folded four at a time, the probabilities as one 16-byte read
+    const int Lcommon = (L0 + r0 + 1) & ~3;
+    for (int t0 = 0, buf = 0; t0 < Lmax; t0 += PW_TILE, buf ^= 1) {
+        const bool more = t0 + PW_TILE < Lmax;
+        if (more) copy_tile(V, t0 + PW_TILE, tiles + (buf ^ 1) * PW_TILE * KST);
+        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (folds) {
+            const float* vt = tiles + buf * PW_TILE * KST + d;
+            const float* pr0 = sc + (g * RPG) * ld;
+            const int te = more ? t0 + PW_TILE : Lmax;
+            const int tv = (te < Lcommon ? te : Lcommon) & ~3;
+            int t = t0;
+            for (; t + 4 <= tv; t += 4) {
+                float2 v[4];
+                float4 pr[RPG];
+#pragma unroll
+                for (int j = 0; j < 4; j++) v[j] = *(const float2*)(vt + (t + j - t0) * KST);
+#pragma unroll
+                for (int k = 0; k < RPG; k++) pr[k] = *(const float4*)(pr0 + k * ld + t);
+#pragma unroll
+                for (int k = 0; k < RPG; k++) { acc[k].x = __fmaf_rn(pr[k].x, v[0].x, acc[k].x); acc[k].y = __fmaf_rn(pr[k].x, v[0].y, acc[k].y); }
+#pragma unroll
+                for (int k = 0; k < RPG; k++) { acc[k].x = __fmaf_rn(pr[k].y, v[1].x, acc[k].x); acc[k].y = __fmaf_rn(pr[k].y, v[1].y, acc[k].y); }
+#pragma unroll
+                for (int k = 0; k < RPG; k++) { acc[k].x = __fmaf_rn(pr[k].z, v[2].x, acc[k].x); acc[k].y = __fmaf_rn(pr[k].z, v[2].y, acc[k].y); }
+#pragma unroll
+                for (int k = 0; k < RPG; k++) { acc[k].x = __fmaf_rn(pr[k].w, v[3].x, acc[k].x); acc[k].y = __fmaf_rn(pr[k].w, v[3].y, acc[k].y); }
+            }
+            for (; t < te; t++) {   // the causal edge: row by row
+                const float2 v = *(const float2*)(vt + (t - t0) * KST);
+#pragma unroll
+                for (int k = 0; k < RPG; k++) {
+                    if (t < Lr[k]) {
+                        const float pr = pr0[k * ld + t];
+                        acc[k].x = __fmaf_rn(pr, v.x, acc[k].x);
+                        acc[k].y = __fmaf_rn(pr, v.y, acc[k].y);
+                    }
+                }
+            }
+        }
+        __syncthreads();                    // the tile may be overwritten
+    }
+#pragma unroll
+    for (int k = 0; k < RPG; k++) {
+        const int qi = g * RPG + k;
+        if (folds && qi < nq) {
+            const float z = zs[qi];
+            *(float2*)(OUT + (long)(r0 + qi) * out_ld + (long)h * HD + d) = make_float2(__fdiv_rn(acc[k].x, z), __fdiv_rn(acc[k].y, z));
+        }
+    }
+}
+
+template <int HD>
+static size_t attn_prefill_wide_smem(int maxt) {
+    return ((size_t)PW_QT * HD + PW_QT * 64 + PW_QT + (size_t)2 * PW_TILE * (HD + 4) + (size_t)PW_QT * ((maxt + 3) & ~3)) * sizeof(float);
+}
+
+template <int HD>
+static int launch_attn_prefill_wide(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
+                                    int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
+    int* st = device_status_ptr();
+    LT_REQUIRE(st != nullptr, "lt_attn_prefill: status word unavailable");
+    const size_t smem = attn_prefill_wide_smem<HD>(maxt);
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
+        LT_CUDA(cudaFuncSetAttribute(k_attn_prefill_wide<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    }
+    dim3 grid((nrows + PW_QT - 1) / PW_QT, nh);
+    k_attn_prefill_wide<HD><<<grid, PW_THREADS, smem, s>>>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, st);
+    return check_launch("lt_attn_prefill");
+}
+
 template <int HD, int QT>
 static int launch_attn_prefill(const float* Q, int q_ld, const float* K, const float* V, const int* len, float* OUT,
                                int out_ld, int nh, int nkv, float scale, int nrows, int maxt, cudaStream_t s) {
@@ -286,6 +509,9 @@ static int pick_attn_prefill(const float* Q, int q_ld, const float* K, const flo
     // query rows per tile: 8 while three CTAs of score rows fit an SM (the V sum and the softmax are
     // chains of dependent operations, resident warps hide them), else 4; 16 only for short chunks (16 rows
     // with one CTA per SM was measured 6 % slower at 2048 positions)
+    // 16 rows per CTA with double-buffered tiles where the score rows of 16 queries fit one SM beside them
+    if (nrows >= 2 * PW_QT && attn_prefill_wide_smem<HD>(maxt) <= 227 * 1024 && aligned16(V))
+        return launch_attn_prefill_wide<HD>(Q, q_ld, K, V, len, OUT, out_ld, nh, nkv, scale, nrows, maxt, s);
     const size_t per_row = (size_t)((maxt + 3) & ~3) + HD + 65;
     const size_t tile = (size_t)PF_KTILE * (HD + 4) * sizeof(float);
     if (16 * per_row * sizeof(float) + tile <= 72 * 1024)
