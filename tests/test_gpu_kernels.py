@@ -422,3 +422,22 @@ def test_embed_gather(oracle):
     dt = torch.tensor([V], dtype=torch.int32, device="cuda")
     _lib.call("lt_embed_q8", dWq.data_ptr(), dWd.data_ptr(), dt.data_ptr(), out.data_ptr(), E, V, stream())
     assert _lib.device_status() == {"bad_token"}
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_second_device_in_one_process(oracle):
+    """Function attributes and occupancy are per device: a GEMV that needs more than 48 KB of dynamic shared
+    memory on cuda:1 after the same call on cuda:0, both against the oracle."""
+    M, K = 256, 8192
+    Wq, Wd, x = synth.gemv_case(M, K, T=1, seed=31)
+    xq, xd = oracle.quant_q8(x[0])
+    want = oracle.q8_gemv(Wq, Wd, xq, xd, M, K)
+    for d in (0, 1, 0):
+        with torch.cuda.device(d):
+            dWq, dWd = dev(Wq), dev(Wd)
+            dxq, dxd = dev(xq), dev(xd)
+            y = torch.empty(M, dtype=torch.float32, device="cuda")
+            _lib.call("lt_q8_gemv", dWq.data_ptr(), dWd.data_ptr(), dxq.data_ptr(), dxd.data_ptr(), None, y.data_ptr(), M, K, 1, stream())
+            torch.cuda.synchronize()
+            assert np.array_equal(bits(host(y)), bits(want)), d
+            assert _lib.device_status() == set()

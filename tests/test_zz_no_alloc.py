@@ -70,3 +70,31 @@ def test_static_scratch_at_the_maximum_k():
     y = _static_linear(dWq, dWd, dx, M, K)
     xq, xd = gpu_quant(x[0])
     assert np.array_equal(bits(host(y)), bits(host(gpu_gemv(dWq, dWd, xq, xd, M, K))))
+
+
+def test_static_scratch_linear_inside_a_captured_graph():
+    """A caller that is recording a stream: one eager call first (function attributes, occupancy and the
+    symbol address are settled outside the capture), then the same call recorded into a CUDA graph and
+    replayed twice -- the bits of the eager result, no allocation by the entry point during capture or replay."""
+    M, K = 896, 4864
+    Wq, Wd, x = synth.gemv_case(M, K, seed=21)
+    r = np.random.default_rng(21).standard_normal(M).astype(np.float32)
+    dWq, dWd, dx, dr = dev(Wq), dev(Wd), dev(x[0]), dev(r)
+    eager = host(_static_linear(dWq, dWd, dx, M, K, resid=dr)).copy()
+    y = torch.zeros(M, dtype=torch.float32, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        rc = _lib.lib().lt_q8_linear_static(dWq.data_ptr(), dWd.data_ptr(), dx.data_ptr(), dr.data_ptr(), y.data_ptr(),
+                                            M, K, stream())
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(host(y)), bits(eager))
+    assert free_before - torch.cuda.mem_get_info()[0] <= 1 << 20
+    assert _lib.device_status() == set()
