@@ -82,12 +82,22 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "memory");
     return ok != 0;
 }
-// bulk async copy global -> this CTA's shared memory, completion counted on an mbarrier
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+// bulk async copy global -> this CTA's shared memory, completion counted on an mbarrier, with an L2 eviction
+// policy for the lines it touches.  Every weight byte passes through L2 once per
+// token: marked "evict first", the stream leaves the small hot set (hand-over words, KV rows, norm weights)
+// in L2 instead of sweeping it out (measured: 1.2-1.8 % of the step; asking L2 to KEEP a part of the LM head
+// from token to token instead was slower at every fraction tried)
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, unsigned bytes, unsigned long long* bar,
+                                              unsigned long long policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
                      smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 // 16-byte asynchronous copy global -> shared (no register staging)
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -250,6 +260,7 @@ __device__ __forceinline__ int rows_per_chunk_lm(int K) {
 __device__ __forceinline__ bool produce_segment(Ring& R, const int8_t* Wq, const __half* Wd, int r0, int r1, int K, int RC,
                                                 Shared* S, int* status, unsigned long long* gate = nullptr,
                                                 unsigned gate_parity = 0, int gate_stage = 0) {
+    const unsigned long long pol = l2_policy_evict_first();
     const int nb = K >> 5;
     for (int r = r0; r < r1; r += RC) {
         const int n = (r1 - r < RC) ? (r1 - r) : RC;
@@ -266,8 +277,8 @@ __device__ __forceinline__ bool produce_segment(Ring& R, const int8_t* Wq, const
         const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
         const unsigned dbytes = (unsigned)(d1 - d0);
         mbar_expect_tx(&R.full[R.stage], qbytes + dbytes);
-        bulk_g2s(dst, Wq + (size_t)r * K, qbytes, &R.full[R.stage]);
-        bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &R.full[R.stage]);
+        bulk_g2s_hint(dst, Wq + (size_t)r * K, qbytes, &R.full[R.stage], pol);
+        bulk_g2s_hint(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, &R.full[R.stage], pol);
         R.advance();
     }
     return true;
@@ -306,8 +317,9 @@ __device__ __forceinline__ unsigned slot_request(unsigned char* dst, const int8_
     const size_t d0 = a0 & ~(size_t)15;
     const size_t d1 = (a0 + (size_t)n * nb * 2 + 15) & ~(size_t)15;
     const unsigned dbytes = (unsigned)(d1 - d0);
-    bulk_g2s(dst, Wq + (size_t)r * K, qbytes, bar);
-    bulk_g2s(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, bar);
+    const unsigned long long pol = l2_policy_evict_first();
+    bulk_g2s_hint(dst, Wq + (size_t)r * K, qbytes, bar, pol);
+    bulk_g2s_hint(dst + qbytes, reinterpret_cast<const void*>(d0), dbytes, bar, pol);
     return qbytes + dbytes;
 }
 __device__ __forceinline__ unsigned slot_bytes(const __half* Wd, int r, int n, int K) {
@@ -1124,11 +1136,12 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
                 if (!ok) break;
                 armed = il;
                 mbar_expect_tx(&S->wfull, 2 * (qb + db));
-                bulk_g2s(A.big, ly->qkv_q + (size_t)h * HD * E, qb, &S->wfull);
-                bulk_g2s(A.big + qb, ly->qkv_q + ((size_t)nq + (size_t)hk * HD) * E, qb, &S->wfull);
-                bulk_g2s(A.big + 2 * (size_t)qb, (const __half*)ly->qkv_d + (size_t)h * HD * nbE, db, &S->wfull);
-                bulk_g2s(A.big + 2 * (size_t)qb + db, (const __half*)ly->qkv_d + ((size_t)nq + (size_t)hk * HD) * nbE, db,
-                         &S->wfull);
+                const unsigned long long pol = l2_policy_evict_first();
+                bulk_g2s_hint(A.big, ly->qkv_q + (size_t)h * HD * E, qb, &S->wfull, pol);
+                bulk_g2s_hint(A.big + qb, ly->qkv_q + ((size_t)nq + (size_t)hk * HD) * E, qb, &S->wfull, pol);
+                bulk_g2s_hint(A.big + 2 * (size_t)qb, (const __half*)ly->qkv_d + (size_t)h * HD * nbE, db, &S->wfull, pol);
+                bulk_g2s_hint(A.big + 2 * (size_t)qb + db, (const __half*)ly->qkv_d + ((size_t)nq + (size_t)hk * HD) * nbE, db,
+                              &S->wfull, pol);
             }
             if (ok) ok = mbar_wait(&S->att_done, 0u, S, P.status);
             if ((!ok || S->abort_flag) && armed >= 0) {     // gave up: let the requested rows land before the CTA exits
