@@ -1047,7 +1047,7 @@ __device__ __forceinline__ void gemv_phase(const int PH, const lt_decode_desc& P
     }
     // this warp no longer reads the slot: the next layer's slice may be requested
     __syncwarp();
-    if (lane == 0 && n > 0) mbar_arrive(&S->sempty[PH]);
+    if (lane == 0 && (n > 0 || PH == 0)) mbar_arrive(&S->sempty[PH]);     // (phase 0 is also the producer's cue: always)
     C.tr.stamp(25 + PH);
 }
 
@@ -1151,7 +1151,10 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             }
             if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status);
         } else {
-            // the slots: slice p of layer il is requested as soon as slice p of layer il - 1 has been folded
+            // the slots: the v and o_proj slices of layer il are requested as soon as those of layer il - 1 have been
+            // folded; the two large ones (gate|up, down) wait until phase 0 of layer il has been folded as well, i.e.
+            // until the GEMV CTAs start waiting for the attention CTAs: requested right after their own fold, all
+            // CTAs' refills (18 MB) would travel through L2 exactly while x and silu(gate)*up are handed over
             int armed[4] = {-1, -1, -1, -1};
             const int nrows[4] = {v1 - v0, e1 - e0, b1 - b0, e1 - e0};
             for (int il = 0; il < L && ok; il++) {
@@ -1160,6 +1163,7 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
                 for (int p = 0; p < 4; p++) {
                     if (nrows[p] <= 0 || !ok) continue;
                     if (il > 0) ok = mbar_wait(&S->sempty[p], (unsigned)(il - 1) & 1u, S, P.status);
+                    if (ok && il > 0 && p >= 1) ok = mbar_wait(&S->sempty[0], (unsigned)il & 1u, S, P.status);
                     if (!ok) continue;
                     unsigned char* dst = A.big + SL.off[p];
                     armed[p] = il;
