@@ -236,7 +236,10 @@ typedef struct lt_decode_desc {
                                   (0 = none); with several looks in flight, their spacing */
     int poll_looks;            /* lt_decode_step: copies of the hand-over workspaces in use, 1..lt_decode_ws_replicas() (0 = all) */
     int trace_cta;             /* lt_decode_step, diagnostics: the second traced CTA (0 = the last one) */
-    int reserved_;
+    int trace_layer;           /* lt_decode_step, diagnostics: with `trace` set and trace_layer = l >= 0, thread 0 of every
+                                * CTA stores the global timer (ns) at the arrival of the input of each of layer l's four
+                                * phases and at the end of each phase, in the last 8 * lt_decode_num_ctas() entries of the
+                                * trace buffer ([cta][arrival 0..3, end 0..3]); negative = off */
 } lt_decode_desc;
 
 int lt_decode_step(const lt_decode_desc* h_desc, void* stream);

@@ -230,6 +230,17 @@ struct Tracer {
     }
 };
 
+// Diagnostics, second form: with a trace buffer and trace_layer = l >= 0, thread 0 of EVERY CTA stores the
+// global timer at the arrival of each phase's input (slots 0..3) and at the end of each phase (slots 4..7) of
+// layer l, in the last 8 * gridDim.x entries of the trace buffer: one layer's hand-overs on one clock.
+__device__ __forceinline__ void layer_timeline(const lt_decode_desc& P, int il, int slot) {
+    if (P.trace != nullptr && threadIdx.x == 0 && il == P.trace_layer) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+        P.trace[4 * DEC_TRACE_CAP - 8 * (int)gridDim.x + 8 * (int)blockIdx.x + slot] = (long long)gt;
+    }
+}
+
 // ---------------------------------------------------------------- weight ring
 struct Ring {
     unsigned char* base;
@@ -1045,6 +1056,7 @@ __device__ __forceinline__ void gemv_phase(const int PH, const lt_decode_desc& P
         consumer_sync();
         C.tr.stamp(21 + PH);
     }
+    layer_timeline(P, il, PH);
     const int8_t* sXq = (PH & 1) ? A.xq1 : A.xq0;
     const __half* sXd = (PH & 1) ? A.xd1 : A.xd0;
     if (PH == 2) {
@@ -1072,6 +1084,7 @@ __device__ __forceinline__ void gemv_phase(const int PH, const lt_decode_desc& P
     __syncwarp();
     if (lane == 0 && (n > 0 || PH == 0)) mbar_arrive(&S->sempty[PH]);     // (phase 0 is also the producer's cue: always)
     C.tr.stamp(25 + PH);
+    layer_timeline(P, il, 4 + PH);
 }
 
 // ---------------------------------------------------------------- the kernel

@@ -733,7 +733,7 @@ class _DecDesc(ctypes.Structure):
                [(n, ctypes.c_void_p) for n in (
                    "layers", "out_norm", "lm_q", "lm_d", "emb_q", "emb_d", "x", "ws_x", "ws_x1", "ws_qkv", "ws_att",
                    "ws_v", "logits", "tok", "out_tok", "history", "step", "sync", "epoch", "part_val", "part_idx",
-                   "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("poll_looks", ctypes.c_int), ("trace_cta", ctypes.c_int), ("reserved_", ctypes.c_int)]
+                   "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("poll_looks", ctypes.c_int), ("trace_cta", ctypes.c_int), ("trace_layer", ctypes.c_int)]
 
 
 class FusedDecodeStep:
@@ -796,7 +796,7 @@ class FusedDecodeStep:
                              None if history is None else int(history), None if step is None else int(step),
                              self.sync.data_ptr(), self.epoch.data_ptr(), self.part_val.data_ptr(),
                              self.part_idx.data_ptr(), None, None, ctypes.addressof(self._layers_host),
-                             self.ws_part.data_ptr(), int(_POLL_NS), int(_POLL_LOOKS), int(os.environ.get("LLAMATOV_TRACE_CTA", "0")), 0)
+                             self.ws_part.data_ptr(), int(_POLL_NS), int(_POLL_LOOKS), int(os.environ.get("LLAMATOV_TRACE_CTA", "0")), int(os.environ.get("LLAMATOV_TRACE_LAYER", "-1")))
         self.mode = "persistent" if _FUSED_STEP is True else _FUSED_STEP
         if self.mode == "persistent" and not _lib.lib().lt_decode_step_supported(ctypes.byref(self.desc)):
             self.mode = "pdl"       # the one-kernel step keeps 2*hd rows of q|k|v resident per SM: small models only

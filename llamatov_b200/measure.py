@@ -215,6 +215,8 @@ def run_decode_trace(args):
     stamp to each stamp over the layers.  One JSON line per traced CTA."""
     if args.cta:
         os.environ["LLAMATOV_TRACE_CTA"] = str(args.cta)
+    if args.layer >= 0:
+        os.environ["LLAMATOV_TRACE_LAYER"] = str(args.layer)
     dr._FUSED_STEP = "persistent"
     m = synth.make_model(args.arch, seed=0)
     w, cfg = synth.reference_weights(m)
@@ -240,6 +242,22 @@ def run_decode_trace(args):
         mhz = float(torch.cuda.clock_rate())        # SM clock now, MHz (NVML)
     except Exception:
         mhz = 1965.0
+    if args.layer >= 0:
+        # one layer on the global timer: [cta][arrival of phase 0..3, end of phase 0..3], ns
+        G = _lib.lib().lt_decode_num_ctas()
+        nh = m["cfg"]["n_head"]
+        a = st.trace.cpu().numpy().reshape(-1)[4 * n - 8 * G:].reshape(G, 8).astype(np.int64)[nh:]      # the GEMV CTAs
+        a = (a - a[:, 0].min()) / 1000.0
+        names = ["x arrived", "attention output arrived", "x1 arrived", "silu*up arrived", "phase 0 done (v rows stored)",
+                 "phase 1 done (x1 stored)", "phase 2 done (silu*up published)", "phase 3 done (next x stored)"]
+        nblk = m["cfg"]["n_ffn"] // 32
+        two = [c for c in range(G - nh) if (nblk * (c + 1)) // (G - nh) - (nblk * c) // (G - nh) >= 2]
+        rows = {names[j]: {"earliest": round(float(a[:, j].min()), 2), "median": round(float(np.median(a[:, j])), 2),
+                           "latest": round(float(a[:, j].max()), 2)} for j in (0, 4, 1, 5, 2, 6, 3, 7)}
+        if two:
+            rows["phase 2 done, CTAs with two or more gate|up blocks"] = {"median": round(float(np.median(a[two, 6])), 2),
+                                                                          "latest": round(float(a[two, 6].max()), 2)}
+        print(json.dumps({"layer": args.layer, "gemv_ctas": G - nh, "us_from_first_arrival_of_x": rows}), flush=True)
     tr = st.trace.cpu().numpy().reshape(2, n, 2)
     for c in range(2):
         tt = tr[c]
@@ -428,6 +446,8 @@ def main(argv=None):
     d = sub.add_parser("decode-trace")
     d.add_argument("--arch", default="qwen2.5-0.5b")
     d.add_argument("--cta", type=int, default=0, help="index of the traced GEMV CTA (0 = the last CTA)")
+    d.add_argument("--layer", type=int, default=-1,
+                   help="also print the timeline of this layer on the global timer: every GEMV CTA's arrival and end of each phase")
     t = sub.add_parser("tp-decode")
     t.add_argument("--arch", default="llama-3-8b")
     t.add_argument("--batch", type=int, nargs="+", default=[1, 32])
