@@ -435,6 +435,12 @@ int lt_q8_linear_static_max_k(void);
  * lets a captured step feed its own argmax to the next replay and keeps the token trace. */
 int lt_token_record(const int* tok, int* history, int* step, int capacity, void* stream);
 
+/* Host-side helper for a loop that feeds every token back from the host (the reference's
+ * GraphRunner.replay_token, bpd/lib/dev_residency.py:1626 ff.): copies the 4-byte token id from page-locked
+ * h_tok to d_tok, launches graph_exec (a cudaGraphExec_t whose step reads d_tok and leaves the chosen token in
+ * d_out), copies d_out to page-locked h_out and waits for the stream.  One call per token. */
+int lt_graph_replay_token(void* graph_exec, void* stream, const int* h_tok, int* d_tok, const int* d_out, int* h_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,7 @@ SIGNATURES = {
     "lt_argmax_rows_scratch_bytes": [_i],
     "lt_embed_q8": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lt_token_record": [_vp, _vp, _vp, _i, _vp],
+    "lt_graph_replay_token": [_vp, _vp, _vp, _vp, _vp, _vp],
     "lt_embed_q8_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lt_rope_rows": [_vp, _i, _vp, _i, _i, _i, _f, _vp],
     "lt_append_kv_rows": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],

@@ -264,6 +264,20 @@ __global__ void k_token_record(const int* __restrict__ tok, int* __restrict__ hi
 
 using namespace lt;
 
+// One token through a captured step, for a host loop that feeds every token back itself: the token id from
+// page-locked memory -> the graph -> the chosen token back into page-locked memory -> one wait.  Four runtime
+// calls behind one entry point: the caller's per-token cost is this call, not four trips through its binding.
+extern "C" int lt_graph_replay_token(void* graph_exec, void* stream, const int* h_tok, int* d_tok, const int* d_out,
+                                     int* h_out) {
+    LT_REQUIRE(graph_exec && h_tok && d_tok && d_out && h_out, "lt_graph_replay_token: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    LT_CUDA(cudaMemcpyAsync(d_tok, h_tok, sizeof(int), cudaMemcpyHostToDevice, s));
+    LT_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, s));
+    LT_CUDA(cudaMemcpyAsync(h_out, d_out, sizeof(int), cudaMemcpyDeviceToHost, s));
+    LT_CUDA(cudaStreamSynchronize(s));
+    return LT_OK;
+}
+
 extern "C" int lt_token_record(const int* tok, int* history, int* step, int capacity, void* stream) {
     LT_REQUIRE(tok && history && step && capacity > 0, "lt_token_record: bad argument");
     k_token_record<<<1, 32, 0, (cudaStream_t)stream>>>(tok, history, step, capacity);

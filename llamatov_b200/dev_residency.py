@@ -918,8 +918,7 @@ class GraphRunner:
         """Host-to-device bytes a replay uploads: the token id, or the embedding row."""
         return 4 if getattr(self, "_tok_in", None) is not None else self.E * 4
 
-    def _launch(self, tok):
-        assert self.captured, "call capture() before replay"
+    def _ensure_pinned(self):
         if getattr(self, "_pin_row", None) is None:     # page-locked staging: the copies below are truly asynchronous
             self._pin_row = torch.empty(self.E, dtype=torch.float32).pin_memory()
             self._pin_row_np = self._pin_row.numpy()
@@ -927,6 +926,10 @@ class GraphRunner:
             self._pin_idx_np = self._pin_idx.numpy()
             self._pin_tok = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._pin_tok_np = self._pin_tok.numpy()
+
+    def _launch(self, tok):
+        assert self.captured, "call capture() before replay"
+        self._ensure_pinned()
         if self._tok_in is not None:
             self._pin_tok_np[0] = int(tok)
             with torch.cuda.stream(self.stream):
@@ -1020,9 +1023,28 @@ class GraphRunner:
         self.stream.synchronize()
         return torch.from_numpy(_LOGITS_BUF.to_host()).reshape(1, 1, _LOGITS_BUF.n)
 
+    def _raw_exec(self):
+        """The cudaGraphExec_t of the captured step, if this torch exposes it (else None: the calls go one by one)."""
+        if getattr(self, "_exec_ptr", None) is None:
+            try:
+                self._exec_ptr = int(self.graph.raw_cuda_graph_exec())
+            except Exception:
+                self._exec_ptr = 0
+        return self._exec_ptr or None
+
     def replay_token(self, tok):
         """Replay, device argmax, 4 bytes back to the host."""
         assert _LOGITS_BUF is not None, "replay_token requires device logits"
+        if self.fused and self._tok_in is not None and self.captured and self._raw_exec() is not None:
+            # token id up, graph, chosen token down, one wait: one call into the library
+            self._ensure_pinned()
+            self._pin_tok_np[0] = int(tok)
+            _lib.call("lt_graph_replay_token", ctypes.c_void_p(self._exec_ptr), ctypes.c_void_p(self.stream.cuda_stream),
+                      self._pin_tok_np.ctypes.data, ctypes.c_void_p(self._tok_in.data_ptr()), _vp(_ensure_argmax_buf()),
+                      self._pin_idx_np.ctypes.data)
+            for c in self.kv:
+                c.length += 1
+            return int(self._pin_idx_np[0])
         self._launch(tok)
         ab = _ensure_argmax_buf()
         if not self.fused:          # the fused step already left the argmax in the buffer
