@@ -486,6 +486,13 @@ def main():
                 "lm_head_gemv_alone": {"kernel": "lt::k_q8_gemv1<4,1>", "shape": [N_, K_], "us": lm_us,
                                        "achieved": lm_gbs, "frac": lm_gbs / peak}}
 
+    # where the hand-over workspaces of the one-kernel step were put (chosen by timing a few steps per candidate
+    # position before the graphs were captured; not part of the timed regions)
+    placement = None
+    pu = getattr(getattr(gr, "_step_dev", None), "placement_us", None)
+    if pu:
+        placement = {"chosen": int(gr._step_dev.placement), "candidates": len(pu), "us_per_step_best": round(min(pu.values()), 1),
+                     "us_per_step_worst": round(max(pu.values()), 1)}
     value = world * K / (dev_ms * 1e-3)
     e2e_val = world * K / (e2e_ms * 1e-3)
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -496,7 +503,8 @@ def main():
                       "parallelism": "replicas only" if world > 1 else "1 GPU",
                       "l2": "inputs larger than L2 (525 MB of weights streamed per token vs 126 MB L2)",
                       "step_mode": step_mode, "timing": f"median of {R} timed regions of {K} steps",
-                      "tokens_device_loop_equal_host_loop": tokens_match, "device_status": sorted(status)},
+                      "tokens_device_loop_equal_host_loop": tokens_match, "device_status": sorted(status),
+                      "workspace_placement": placement},
            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": gr.input_bytes_per_replay(), "d2h_bytes_per_step": 4,
                    "ms_per_step": e2e_ms / K, "value_min": world * K / (max(e2e_runs) * 1e-3),
                    "value_max": world * K / (min(e2e_runs) * 1e-3)},

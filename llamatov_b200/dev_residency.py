@@ -714,6 +714,8 @@ _FUSED_STEP = "persistent"
 _POLL_NS = int(os.environ.get("LLAMATOV_POLL_NS", "0"))
 # copies of the hand-over buffers in use (each SM polls copy SM % n): 1 .. lt_decode_ws_replicas()
 _POLL_LOOKS = int(os.environ.get("LLAMATOV_WS_COPIES", "1"))
+_WS_TUNE = os.environ.get("LLAMATOV_WS_TUNE", "1") != "0"          # time the step at several workspace positions, keep the fastest
+_WS_CANDIDATES = int(os.environ.get("LLAMATOV_WS_CANDIDATES", "24"))
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -776,9 +778,15 @@ class FusedDecodeStep:
         nct = max(_lib.lib().lt_decode_num_ctas(), _lib.lib().lt_decode_pdl_num_parts())
         f32 = dict(dtype=torch.float32, device="cuda")
         # tagged workspaces: {value, tag} pairs, zero tags = "never written"
-        rep = _lib.lib().lt_decode_ws_replicas()
-        self.ws = [torch.zeros(2 * n, **f32) for n in (rep * E, rep * E, nq + 2 * nk, rep * nq, rep * F)]
-        self.ws_part = torch.zeros(4 * nct, **f32)
+        rep = _lib.lib().lt_decode_ws_replicas() if _POLL_LOOKS != 1 else 1      # copies of four of the vectors in use
+        # the hand-over workspaces (five tagged vectors and the argmax slots) live side by side in one arena; where
+        # in it is chosen by tune_placement()
+        self._ws_sizes = [2 * n for n in (rep * E, rep * E, nq + 2 * nk, rep * nq, rep * F)] + [4 * nct]
+        self._ws_span = sum(((n + 63) // 64) * 64 for n in self._ws_sizes)       # floats, every vector 256-byte aligned
+        self._ws_window = ((self._ws_span * 4 + 65536 + 131071) // 131072) * 131072 // 4    # floats per candidate window
+        self._ws_arena = torch.zeros(self._ws_window * _WS_CANDIDATES, **f32)
+        self._kv = kv
+        self._place(0)
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
         self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.part_val = torch.zeros(nct, **f32); self.part_idx = torch.zeros(nct, dtype=torch.int32, device="cuda")
@@ -800,6 +808,66 @@ class FusedDecodeStep:
         self.mode = "persistent" if _FUSED_STEP is True else _FUSED_STEP
         if self.mode == "persistent" and not _lib.lib().lt_decode_step_supported(ctypes.byref(self.desc)):
             self.mode = "pdl"       # the one-kernel step keeps 2*hd rows of q|k|v resident per SM: small models only
+
+    def _place(self, cand):
+        """Point the workspaces at candidate window `cand` of the arena: window start + a sub-offset that differs
+        from window to window (multiples of 4 KB and of 1 KB), so that the candidates fall on different L2 slices."""
+        sub = ((cand * 4096 + (cand % 4) * 1024) % 65536) // 4
+        o = cand * self._ws_window + sub
+        views = []
+        for n in self._ws_sizes:
+            views.append(self._ws_arena[o:o + n])
+            o += ((n + 63) // 64) * 64
+        self.ws = views[:5]
+        self.ws_part = views[5]
+        if getattr(self, "desc", None) is not None:
+            d = self.desc
+            d.ws_x, d.ws_x1, d.ws_qkv, d.ws_att, d.ws_v = (v.data_ptr() for v in self.ws)
+            d.ws_part = self.ws_part.data_ptr()
+        self.placement = cand
+
+    def tune_placement(self, steps=6):
+        """Choose where the hand-over workspaces live.  The one-kernel step is bound by the latency of small vectors
+        handed from every SM to every SM through L2, and that latency depends on which L2 slices the vectors'
+        lines fall on: the same kernel ran between 365 and 423 us per token on one GPU with nothing changed but the
+        workspaces' addresses.  So a few steps are timed at each candidate position of the arena (device state that
+        a step advances -- cache lengths, token, history -- is put back afterwards; the cache rows written past
+        the length are overwritten by the real steps) and the fastest stays.  Returns {candidate: us per step}."""
+        if self.mode != "persistent" or not _WS_TUNE or _WS_CANDIDATES < 2:
+            return {}
+        if any(c.length + steps > c.max_seq for c in self._kv):
+            return {}
+        d = self.desc
+        lens = [c._len.clone() for c in self._kv]
+        saved = (d.tok, d.out_tok, d.history, d.step)
+        tok = torch.zeros(1, dtype=torch.int32, device="cuda"); out = torch.zeros(1, dtype=torch.int32, device="cuda")
+        d.tok = tok.data_ptr() if saved[0] else None
+        d.out_tok = out.data_ptr(); d.history = None; d.step = None
+        res = {}
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        try:
+            for cand in range(_WS_CANDIDATES):
+                self._place(cand)
+                for c, l in zip(self._kv, lens):
+                    c._len.copy_(l)
+                tok.zero_()
+                for i in range(steps):
+                    if i == 2:
+                        e0.record(torch.cuda.current_stream())
+                    self.launch()
+                e1.record(torch.cuda.current_stream())
+                e1.synchronize()
+                res[cand] = e0.elapsed_time(e1) * 1e3 / (steps - 2)
+        finally:
+            for c, l in zip(self._kv, lens):
+                c._len.copy_(l)
+            d.tok, d.out_tok, d.history, d.step = saved
+            torch.cuda.synchronize()
+        if _lib.device_status():
+            raise RuntimeError("lt_decode_step: a wait ran out while the workspace placement was being chosen")
+        self._place(min(res, key=res.get))
+        self.placement_us = res
+        return res
 
     def enable_trace(self):
         """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""
@@ -883,6 +951,10 @@ class GraphRunner:
                 self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv, tok_ptr=self._tok_in.data_ptr())
             else:
                 self._step_host = FusedDecodeStep(self.w, self.cfg, self.kv)
+            with torch.cuda.stream(self.stream):
+                self._step_host.tune_placement()
+            torch.cuda.synchronize()
+            n0 = _lib.launch_count()
             with torch.cuda.graph(g, stream=self.stream):
                 self._step_host.launch()
         else:
@@ -979,6 +1051,10 @@ class GraphRunner:
             self._step_dev = FusedDecodeStep(self.w, self.cfg, self.kv, tok_ptr=self._tok_dev.data_ptr(),
                                              history=self._hist.data_ptr(), step=self._step.data_ptr(),
                                              hist_cap=capacity)
+            with torch.cuda.stream(self.stream):
+                self._step_dev.tune_placement()
+            torch.cuda.synchronize()
+            n0 = _lib.launch_count()
             with torch.cuda.graph(g, stream=self.stream):
                 self._step_dev.launch()
         else:
