@@ -491,8 +491,8 @@ def main():
     placement = None
     pu = getattr(getattr(gr, "_step_dev", None), "placement_us", None)
     if pu:
-        placement = {"chosen": int(gr._step_dev.placement), "candidates": len(pu), "us_per_step_best": round(min(pu.values()), 1),
-                     "us_per_step_worst": round(max(pu.values()), 1)}
+        placement = {"chosen": list(gr._step_dev.placement), "tried": len(pu), "us_per_step_best": round(min(u for _, u in pu), 1),
+                     "us_per_step_worst": round(max(u for _, u in pu), 1), "us_per_step_first": round(pu[0][1], 1)}
     value = world * K / (dev_ms * 1e-3)
     e2e_val = world * K / (e2e_ms * 1e-3)
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,

@@ -715,7 +715,7 @@ _POLL_NS = int(os.environ.get("LLAMATOV_POLL_NS", "0"))
 # copies of the hand-over buffers in use (each SM polls copy SM % n): 1 .. lt_decode_ws_replicas()
 _POLL_LOOKS = int(os.environ.get("LLAMATOV_WS_COPIES", "1"))
 _WS_TUNE = os.environ.get("LLAMATOV_WS_TUNE", "1") != "0"          # time the step at several workspace positions, keep the fastest
-_WS_CANDIDATES = int(os.environ.get("LLAMATOV_WS_CANDIDATES", "24"))
+_WS_CANDIDATES = int(os.environ.get("LLAMATOV_WS_CANDIDATES", "12"))
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -782,9 +782,11 @@ class FusedDecodeStep:
         # the hand-over workspaces (five tagged vectors and the argmax slots) live side by side in one arena; where
         # in it is chosen by tune_placement()
         self._ws_sizes = [2 * n for n in (rep * E, rep * E, nq + 2 * nk, rep * nq, rep * F)] + [4 * nct]
-        self._ws_span = sum(((n + 63) // 64) * 64 for n in self._ws_sizes)       # floats, every vector 256-byte aligned
-        self._ws_window = ((self._ws_span * 4 + 65536 + 131071) // 131072) * 131072 // 4    # floats per candidate window
-        self._ws_arena = torch.zeros(self._ws_window * _WS_CANDIDATES, **f32)
+        self._ws_pitch = [(((n * 4 + 255) // 256) | 1) * 64 for n in self._ws_sizes]      # floats: odd multiples of 256 bytes
+        self._ws_region = [0]
+        for pch in self._ws_pitch[:-1]:
+            self._ws_region.append(self._ws_region[-1] + pch * _WS_CANDIDATES + 1024)
+        self._ws_arena = torch.zeros(self._ws_region[-1] + self._ws_pitch[-1] * _WS_CANDIDATES + 1024, **f32)
         self._kv = kv
         self._place(0)
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
@@ -809,55 +811,70 @@ class FusedDecodeStep:
         if self.mode == "persistent" and not _lib.lib().lt_decode_step_supported(ctypes.byref(self.desc)):
             self.mode = "pdl"       # the one-kernel step keeps 2*hd rows of q|k|v resident per SM: small models only
 
-    def _place(self, cand):
-        """Point the workspaces at candidate window `cand` of the arena: window start + a sub-offset that differs
-        from window to window (multiples of 4 KB and of 1 KB), so that the candidates fall on different L2 slices."""
-        sub = ((cand * 4096 + (cand % 4) * 1024) % 65536) // 4
-        o = cand * self._ws_window + sub
+    def _place(self, cands):
+        """Point workspace i at candidate position cands[i] of its own region of the arena (an int = the same for
+        all): region start + candidate * pitch, the pitch an odd number of 256-byte units, so that the candidates
+        of a vector fall on different L2 slices line by line."""
+        if isinstance(cands, int):
+            cands = [cands] * len(self._ws_sizes)
         views = []
-        for n in self._ws_sizes:
+        for i, n in enumerate(self._ws_sizes):
+            o = self._ws_region[i] + cands[i] * self._ws_pitch[i]
             views.append(self._ws_arena[o:o + n])
-            o += ((n + 63) // 64) * 64
         self.ws = views[:5]
         self.ws_part = views[5]
         if getattr(self, "desc", None) is not None:
             d = self.desc
             d.ws_x, d.ws_x1, d.ws_qkv, d.ws_att, d.ws_v = (v.data_ptr() for v in self.ws)
             d.ws_part = self.ws_part.data_ptr()
-        self.placement = cand
+        self.placement = list(cands)
 
     def tune_placement(self, steps=6):
         """Choose where the hand-over workspaces live.  The one-kernel step is bound by the latency of small vectors
-        handed from every SM to every SM through L2, and that latency depends on which L2 slices the vectors'
-        lines fall on: the same kernel ran between 365 and 423 us per token on one GPU with nothing changed but the
-        workspaces' addresses.  So a few steps are timed at each candidate position of the arena (device state that
-        a step advances -- cache lengths, token, history -- is put back afterwards; the cache rows written past
-        the length are overwritten by the real steps) and the fastest stays.  Returns {candidate: us per step}."""
+        handed from every SM to every SM through L2; a hand-over is complete when its LAST line has arrived, and how
+        long a line takes depends on the L2 slice its address falls on: the same kernel ran between 365 and 423 us
+        per token on one GPU with nothing changed but the workspaces' addresses.  So a few steps are timed with each
+        vector at each candidate position of its region (one vector after the other, the best position kept), and
+        the fastest combination stays.  Device state that a step advances -- cache lengths, token, history -- is put
+        back afterwards; the cache rows written past the length are overwritten by the real steps.
+        Returns the list of (placement, us per step) tried."""
         if self.mode != "persistent" or not _WS_TUNE or _WS_CANDIDATES < 2:
-            return {}
+            return []
         if any(c.length + steps > c.max_seq for c in self._kv):
-            return {}
+            return []
         d = self.desc
         lens = [c._len.clone() for c in self._kv]
         saved = (d.tok, d.out_tok, d.history, d.step)
         tok = torch.zeros(1, dtype=torch.int32, device="cuda"); out = torch.zeros(1, dtype=torch.int32, device="cuda")
         d.tok = tok.data_ptr() if saved[0] else None
         d.out_tok = out.data_ptr(); d.history = None; d.step = None
-        res = {}
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        tried = []
+
+        def time_at(cands):
+            self._place(cands)
+            for c, l in zip(self._kv, lens):
+                c._len.copy_(l)
+            tok.zero_()
+            for i in range(steps):
+                if i == 2:
+                    e0.record(torch.cuda.current_stream())
+                self.launch()
+            e1.record(torch.cuda.current_stream())
+            e1.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (steps - 2)
+            tried.append((list(cands), us))
+            return us
+
         try:
-            for cand in range(_WS_CANDIDATES):
-                self._place(cand)
-                for c, l in zip(self._kv, lens):
-                    c._len.copy_(l)
-                tok.zero_()
-                for i in range(steps):
-                    if i == 2:
-                        e0.record(torch.cuda.current_stream())
-                    self.launch()
-                e1.record(torch.cuda.current_stream())
-                e1.synchronize()
-                res[cand] = e0.elapsed_time(e1) * 1e3 / (steps - 2)
+            best = [0] * len(self._ws_sizes)
+            best_us = time_at(best)
+            for i in range(len(self._ws_sizes)):            # one vector after the other
+                for cand in range(1, _WS_CANDIDATES):
+                    trial = list(best); trial[i] = cand
+                    us = time_at(trial)
+                    if us < best_us:
+                        best, best_us = trial, us
         finally:
             for c, l in zip(self._kv, lens):
                 c._len.copy_(l)
@@ -865,9 +882,9 @@ class FusedDecodeStep:
             torch.cuda.synchronize()
         if _lib.device_status():
             raise RuntimeError("lt_decode_step: a wait ran out while the workspace placement was being chosen")
-        self._place(min(res, key=res.get))
-        self.placement_us = res
-        return res
+        self._place(best)
+        self.placement_us = tried
+        return tried
 
     def enable_trace(self):
         """Diagnostics: SM-clock stamps of CTA 0 and of the last CTA at every phase boundary."""
