@@ -842,6 +842,10 @@ class FusedDecodeStep:
             return []
         if any(c.length + steps > c.max_seq for c in self._kv):
             return []
+        pending = _lib.device_status()      # (read and cleared: say so rather than swallow it)
+        if pending:
+            import warnings
+            warnings.warn(f"device status {sorted(pending)} was pending when the decode step's workspaces were placed")
         d = self.desc
         lens = [c._len.clone() for c in self._kv]
         saved = (d.tok, d.out_tok, d.history, d.step)
@@ -880,7 +884,7 @@ class FusedDecodeStep:
                 c._len.copy_(l)
             d.tok, d.out_tok, d.history, d.step = saved
             torch.cuda.synchronize()
-        if _lib.device_status():
+        if "wait_timeout" in _lib.device_status():
             raise RuntimeError("lt_decode_step: a wait ran out while the workspace placement was being chosen")
         self._place(best)
         self.placement_us = tried
