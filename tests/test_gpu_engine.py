@@ -131,6 +131,40 @@ def test_graph_replay_equals_eager_bit_exact(fused, arch):
     assert dr._lib.device_status() == set()
 
 
+def test_workspace_placement_is_chosen_by_timing_and_changes_no_bits():
+    """The one-kernel step places its hand-over workspaces by timing a few steps per candidate position before
+    the graph is captured: the trials leave no trace (lengths back, tokens and logits equal to an engine whose
+    workspaces stay at the first position)."""
+    old = (dr._FUSED_STEP, dr._WS_TUNE)
+    runs = {}
+    try:
+        for tune in (True, False):
+            dr._FUSED_STEP, dr._WS_TUNE = "persistent", tune
+            m, w, cfg = _fresh("tiny-qwen64", seed=5)
+            prompt = _prompt(m["cfg"]["vocab"], 5, seed=2)
+            dr.reset_engine_state(); dr.apply_production_profile()
+            kv = [None] * cfg["n_layers"]
+            gr = dr.GraphRunner(w, cfg, kv)
+            lg = gr.seed(torch.tensor(prompt), torch.arange(len(prompt)))
+            nxt = int(np.argmax(lg.reshape(-1).numpy()))
+            gr.capture(torch.tensor([nxt]), torch.tensor([len(prompt)]))
+            assert gr._step_host.mode == "persistent"
+            assert all(int(c._len.item()) == len(prompt) for c in kv)
+            tried = getattr(gr._step_host, "placement_us", [])
+            assert (len(tried) > 1) == tune
+            out = []
+            for _ in range(8):
+                lgt = gr.replay_logits(nxt).reshape(-1).numpy().copy()
+                nxt = int(np.argmax(lgt))
+                out.append((nxt, bits(lgt)))
+            runs[tune] = out
+            assert dr._lib.device_status() == set()
+    finally:
+        dr._FUSED_STEP, dr._WS_TUNE = old
+    for (ta, la), (tb, lb) in zip(runs[True], runs[False]):
+        assert ta == tb and np.array_equal(la, lb)
+
+
 @pytest.mark.parametrize("arch", ["tiny", "tiny-llama"])
 def test_device_token_loop_equals_host_driven_loop(fused, arch):
     m, w, cfg = _fresh(arch, seed=6)
