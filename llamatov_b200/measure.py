@@ -230,6 +230,7 @@ def run_decode_trace(args):
     st = dr.FusedDecodeStep(w, cfg, kv, tok_ptr=tokd.data_ptr())
     if st.mode != "persistent":
         raise SystemExit("the one-kernel step does not support this architecture")
+    st.tune_placement()          # the workspaces where the engine would put them
     n = st.enable_trace()
     for _ in range(4):
         st.launch()
