@@ -1187,10 +1187,10 @@ k_decode_step(const __grid_constant__ lt_decode_desc P, int nstages, int nstages
             }
             if (ok) ok = produce_segment(R, P.lm_q, (const __half*)P.lm_d, l0, l1, E, rows_per_chunk_lm(E), S, P.status);
         } else {
-            // the slots: the v and o_proj slices of layer il are requested as soon as those of layer il - 1 have been
-            // folded; the two large ones (gate|up, down) wait until phase 0 of layer il has been folded as well, i.e.
-            // until the GEMV CTAs start waiting for the attention CTAs: requested right after their own fold, all
-            // CTAs' refills (18 MB) would travel through L2 exactly while x and silu(gate)*up are handed over
+            // the slots: the v slice of layer il is requested as soon as that of layer il - 1 has been folded; the
+            // others (o_proj, gate|up, down) wait until phase 0 of layer il has been folded as well, i.e. until the
+            // GEMV CTAs start waiting for the attention CTAs: requested right after their own fold, all CTAs'
+            // refills (18 MB) would travel through L2 exactly while x1, silu(gate)*up and x are handed over
             int armed[4] = {-1, -1, -1, -1};
             const int nrows[4] = {v1 - v0, e1 - e0, b1 - b0, e1 - e0};
             for (int il = 0; il < L && ok; il++) {
