@@ -20,9 +20,11 @@
 //     quantised where it is produced), down, and (together with the attention CTAs) the LM head.
 //     A producer warp fetches the CTA's rows with bulk async copies (no multicast), ahead of the
 //     dependency chain: within the layers every slice has a FIXED place in shared memory (a slot
-//     per phase, refilled with the next layer's slice as soon as this layer's has been folded, so
-//     a phase finds its rows a whole layer early and at addresses that never change); the LM head,
-//     many times the size of shared memory, streams through a ring of stages over the same area.
+//     per phase, refilled with the next layer's slice once this layer's has been folded -- the
+//     large ones while the attention CTAs work, so that the refills do not travel through L2
+//     during a hand-over -- so a phase finds its rows early and at addresses that never change);
+//     the LM head, many times the size of shared memory, streams through a ring of stages over
+//     the same area.  All weight copies are marked "evict first" in L2.
 //
 // Per layer:   x --(1)--> attention CTAs: q,k,attention -> a(q8)          GEMV CTAs: v rows
 //              a --(2)--> o_proj + x -> x1 --(3)--> rmsnorm, gate|up, silu*up -> v(q8)
