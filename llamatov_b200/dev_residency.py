@@ -716,6 +716,7 @@ _POLL_NS = int(os.environ.get("LLAMATOV_POLL_NS", "0"))
 _POLL_LOOKS = int(os.environ.get("LLAMATOV_WS_COPIES", "1"))
 _WS_TUNE = os.environ.get("LLAMATOV_WS_TUNE", "1") != "0"          # time the step at several workspace positions, keep the fastest
 _WS_CANDIDATES = int(os.environ.get("LLAMATOV_WS_CANDIDATES", "12"))
+_WS_ROUNDS = int(os.environ.get("LLAMATOV_WS_ROUNDS", "1"))          # sweeps over the vectors
 
 # A prompt of several tokens runs as one batched pass (prefill.prefill_resident) when the
 # architecture allows it; False keeps the reference's token-by-token recursion.  Both give the
@@ -873,12 +874,15 @@ class FusedDecodeStep:
         try:
             best = [0] * len(self._ws_sizes)
             best_us = time_at(best)
-            for i in range(len(self._ws_sizes)):            # one vector after the other
-                for cand in range(1, _WS_CANDIDATES):
-                    trial = list(best); trial[i] = cand
-                    us = time_at(trial)
-                    if us < best_us:
-                        best, best_us = trial, us
+            for rnd in range(_WS_ROUNDS):
+                for i in range(len(self._ws_sizes)):        # one vector after the other
+                    for cand in range(_WS_CANDIDATES):
+                        if cand == best[i]:
+                            continue
+                        trial = list(best); trial[i] = cand
+                        us = time_at(trial)
+                        if us < best_us:
+                            best, best_us = trial, us
         finally:
             for c, l in zip(self._kv, lens):
                 c._len.copy_(l)
