@@ -739,6 +739,18 @@ class _DecDesc(ctypes.Structure):
                    "status", "trace", "h_layers", "ws_part")] + [("poll_ns", ctypes.c_int), ("poll_looks", ctypes.c_int), ("trace_cta", ctypes.c_int), ("trace_layer", ctypes.c_int)]
 
 
+def _ws_layout(sizes, candidates):
+    """Arena layout of the hand-over workspaces, in floats: vector i (sizes[i] floats) may sit at
+    region[i] + c * pitch[i], c < candidates.  The pitch is an odd number of 256-byte units at least as long as
+    the vector (candidate windows of a vector never overlap, and they shift line by line against the L2 slice
+    interleave); regions follow each other with 4 KB between them.  Returns (pitch, region, total)."""
+    pitch = [(((n * 4 + 255) // 256) | 1) * 64 for n in sizes]
+    region = [0]
+    for pch in pitch[:-1]:
+        region.append(region[-1] + pch * candidates + 1024)
+    return pitch, region, region[-1] + pitch[-1] * candidates + 1024
+
+
 class FusedDecodeStep:
     """Descriptor + workspace of lt_decode_step for one model and its KV caches.  Every weight
     pointer comes from the same upload caches the per-op path uses (no second copy)."""
@@ -783,11 +795,8 @@ class FusedDecodeStep:
         # the hand-over workspaces (five tagged vectors and the argmax slots) live side by side in one arena; where
         # in it is chosen by tune_placement()
         self._ws_sizes = [2 * n for n in (rep * E, rep * E, nq + 2 * nk, rep * nq, rep * F)] + [4 * nct]
-        self._ws_pitch = [(((n * 4 + 255) // 256) | 1) * 64 for n in self._ws_sizes]      # floats: odd multiples of 256 bytes
-        self._ws_region = [0]
-        for pch in self._ws_pitch[:-1]:
-            self._ws_region.append(self._ws_region[-1] + pch * _WS_CANDIDATES + 1024)
-        self._ws_arena = torch.zeros(self._ws_region[-1] + self._ws_pitch[-1] * _WS_CANDIDATES + 1024, **f32)
+        self._ws_pitch, self._ws_region, total = _ws_layout(self._ws_sizes, _WS_CANDIDATES)
+        self._ws_arena = torch.zeros(total, **f32)
         self._kv = kv
         self._place(0)
         self.sync = torch.zeros(2, dtype=torch.int32, device="cuda")
