@@ -168,7 +168,7 @@ def run_reference(args, rank):
         o.set_threads(len(os.sched_getaffinity(0)))     # all host cores, whatever the launcher exported
     except AttributeError:
         o.set_threads(os.cpu_count() or 1)
-    eng = o.OracleEngine(synth.oracle_model(model), max_seq=256)
+    eng = o.OracleEngine(synth.oracle_model(model), max_seq=max(256, PROMPT_LEN + args.warmup + args.steps + 8))
     for tk in prompt:               # the same 32-token prompt as the GPU arm, token by token (untimed)
         _, nxt = eng.step(tk)
     for _ in range(args.warmup):
@@ -350,6 +350,11 @@ def main():
     dr.reset_engine_state(); dr.apply_production_profile()
     if args.step_mode is not None:
         dr._FUSED_STEP = False if args.step_mode == "per-op" else args.step_mode
+    # room in the KV caches for the prompt, the warm-up and the timed steps (the engine's default of 256
+    # positions holds the default run; a longer run gets longer caches)
+    need = PROMPT_LEN + args.steps + args.warmup + 8
+    if need > dr._KV_MAX_SEQ:
+        dr._KV_MAX_SEQ = ((need + 63) // 64) * 64
     w, cfg = synth.reference_weights(model)
 
     # ---- prompt (eager, token by token, as the reference does) + capture
